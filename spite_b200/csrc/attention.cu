@@ -1,0 +1,196 @@
+// Attention over the paged cache, general kernels (any head size that is a
+// multiple of 2 up to 256, any number of heads and groups, both element types).
+//
+//  * qk_prepare: position encoding of q and k, weightless per-head norm, the
+//    temperature factor of layers without rotation, and the append of k and v to
+//    their pages, in one pass over the projection's output.
+//  * paged_attention: one warp per (token, query head) walks the visible keys in
+//    tiles of 32, keeps a running maximum and sum (all in float32) and gathers the
+//    values.  It serves prompt portions and decoded tokens alike, since every key of
+//    the step is in the cache before it runs.
+#include "attention.cuh"
+
+namespace {
+
+// grid (tokens, ceil(heads_total / 4)), block 128: one warp per head of q, k or v.
+template <typename T>
+__global__ void __launch_bounds__(128) qk_prepare_kernel(const QkPrepareParams p, const StepTokens b,
+                                                         const PagedCache c) {
+    const int t = blockIdx.x;
+    const int lane = threadIdx.x & 31;
+    const int head = blockIdx.y * 4 + (threadIdx.x >> 5);
+    const int nq = p.num_heads, nkv = c.num_kv_heads, hd = c.head_dim;
+    if (head >= nq + 2 * nkv) return;
+    const int pos = b.positions[t];
+    const T* in = (const T*)p.qkv + (size_t)t * (nq + 2 * nkv) * hd + (size_t)head * hd;
+    const bool is_q = head < nq, is_v = head >= nq + nkv;
+
+    T* dst;
+    if (is_q) {
+        dst = (T*)p.q_out + ((size_t)t * nq + head) * hd;
+    } else {
+        if (!p.write_cache) return;
+        const int seg = b.seg_of_token[t];
+        const int page = b.block_table[(size_t)seg * b.table_width + pos / c.page_size];
+        if (page < 0 || page >= c.n_pages) return;       // the host never lets this happen
+        const int kvh = is_v ? head - nq - nkv : head - nq;
+        dst = (T*)c.kv + (is_v ? c.v_offset : 0) +
+              (((size_t)page * nkv + kvh) * c.page_size + pos % c.page_size) * hd;
+    }
+    if (is_v) {
+        for (int i = lane; i < hd; i += 32) dst[i] = in[i];
+        return;
+    }
+    // q or k: rotate neighbouring pairs (2i, 2i+1) by pos * inv_freq[i]
+    // (rotation: crates/spite-rope/src/lib.rs:83-91; norm after it: llama4.rs:161-176)
+    constexpr int MAXP = 4;                                  // pairs per lane: head_dim <= 256
+    float x0[MAXP], x1[MAXP];
+    float ss = 0.f;
+#pragma unroll
+    for (int r = 0; r < MAXP; ++r) {
+        const int i = lane + 32 * r;
+        x0[r] = x1[r] = 0.f;
+        if (2 * i < hd) {
+            float a = to_f32(in[2 * i]), bb = to_f32(in[2 * i + 1]);
+            if (p.inv_freq) {
+                float sn, cs;
+                sincosf((float)pos * p.inv_freq[i], &sn, &cs);
+                const float ra = a * cs - bb * sn, rb = a * sn + bb * cs;
+                a = ra; bb = rb;
+            }
+            x0[r] = a; x1[r] = bb;
+            ss += a * a + bb * bb;
+        }
+    }
+    float mul = 1.f;
+    if (p.qk_norm_eps > 0.f) {
+        ss = warp_sum(ss);
+        mul = 1.0f / sqrtf(ss / (float)hd + p.qk_norm_eps);
+    }
+    if (is_q && p.temperature_floor > 0) {                   // llama4.rs:177-183
+        const float fl = (float)((pos + 1) / p.temperature_floor);
+        mul *= logf(fl + 1.0f) * p.temperature_scale + 1.0f;
+    }
+#pragma unroll
+    for (int r = 0; r < MAXP; ++r) {
+        const int i = lane + 32 * r;
+        if (2 * i < hd) {
+            dst[2 * i] = from_f32<T>(x0[r] * mul);
+            dst[2 * i + 1] = from_f32<T>(x1[r] * mul);
+        }
+    }
+}
+
+// grid (tokens, ceil(nq / 4)), block 128: one warp per (token, query head).
+// crates/spite-compute/src/flash_attn.rs:111-156 with the maximum and the sum kept
+// as running values over tiles of 32 keys.
+template <typename T>
+__global__ void __launch_bounds__(128) paged_attention_kernel(const AttentionParams p, const StepTokens b,
+                                                              const PagedCache c) {
+    __shared__ float q_s[4][256];
+    const int t = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int h = blockIdx.y * 4 + warp;
+    const int nq = p.num_heads, nkv = c.num_kv_heads, hd = c.head_dim;
+    if (h >= nq) return;
+    const int kvh = h / (nq / nkv);
+    const int pos = b.positions[t];
+    const int seg = b.seg_of_token[t];
+    const int* table = b.block_table + (size_t)seg * b.table_width;
+    const int lo = window_lowest(p.window_kind, p.window_size, pos);
+
+    const T* q = (const T*)p.q + ((size_t)t * nq + h) * hd;
+    for (int i = lane; i < hd; i += 32) q_s[warp][i] = to_f32(q[i]);
+    __syncwarp();
+
+    const T* kbase = (const T*)c.kv;
+    const T* vbase = (const T*)c.kv + c.v_offset;
+    constexpr int MAXD = 8;                                  // head_dim <= 256
+    float acc[MAXD];
+#pragma unroll
+    for (int r = 0; r < MAXD; ++r) acc[r] = 0.f;
+    float m = -INFINITY, l = 0.f;
+
+    for (int j0 = lo; j0 <= pos; j0 += 32) {
+        const int j = j0 + lane;
+        float s = -INFINITY;
+        long long row = -1;
+        if (j <= pos) {
+            const int page = table[j / c.page_size];
+            row = (((long long)page * nkv + kvh) * c.page_size + j % c.page_size) * hd;
+            const T* k = kbase + row;
+            float dot = 0.f;
+            for (int d = 0; d < hd; ++d) dot = fmaf(q_s[warp][d], to_f32(k[d]), dot);
+            s = dot * p.softmax_scale;
+        }
+        const float m_new = fmaxf(m, warp_max(s));
+        const float corr = expf(m - m_new);                  // 0 on the first tile (m = -inf)
+        const float pj = (j <= pos) ? expf(s - m_new) : 0.f;
+        l = l * corr + warp_sum(pj);
+#pragma unroll
+        for (int r = 0; r < MAXD; ++r) acc[r] *= corr;
+        const int n_valid = min(32, pos - j0 + 1);
+        for (int jj = 0; jj < n_valid; ++jj) {
+            const float pw = __shfl_sync(0xffffffffu, pj, jj);
+            const long long vrow = __shfl_sync(0xffffffffu, row, jj);
+            const T* v = vbase + vrow;
+#pragma unroll
+            for (int r = 0; r < MAXD; ++r) {
+                const int d = lane + 32 * r;
+                if (d < hd) acc[r] = fmaf(pw, to_f32(v[d]), acc[r]);
+            }
+        }
+        m = m_new;
+    }
+    const float inv = 1.0f / fmaxf(l, 1e-30f);
+    T* out = (T*)p.out + ((size_t)t * nq + h) * hd;
+#pragma unroll
+    for (int r = 0; r < MAXD; ++r) {
+        const int d = lane + 32 * r;
+        if (d < hd) out[d] = from_f32<T>(acc[r] * inv);
+    }
+}
+
+int check_common(const StepTokens* b, const PagedCache* c, int num_heads) {
+    if (!b || !c || !b->positions || !b->seg_of_token || !b->block_table || !c->kv) return SPITE_BAD_ARG;
+    if (b->n_tokens < 0 || b->table_width < 1 || c->n_pages < 1 || c->page_size < 1) return SPITE_BAD_ARG;
+    if (num_heads < 1 || c->num_kv_heads < 1 || num_heads % c->num_kv_heads) return SPITE_BAD_ARG;
+    if (c->head_dim < 2 || c->head_dim % 2) return SPITE_BAD_ARG;
+    if (c->head_dim > 256) return SPITE_UNSUPPORTED;
+    return SPITE_OK;
+}
+
+}  // namespace
+
+SPITE_API int spite_qk_prepare(int dtype, const QkPrepareParams* p, const StepTokens* b,
+                               const PagedCache* c, void* stream) {
+    if (!p || !p->qkv || !p->q_out) return SPITE_BAD_ARG;
+    const int chk = check_common(b, c, p->num_heads);
+    if (chk != SPITE_OK) return chk;
+    if (b->n_tokens == 0) return SPITE_OK;
+    const int heads = p->num_heads + 2 * c->num_kv_heads;
+    dim3 grid(b->n_tokens, (heads + 3) / 4);
+    if (grid.y > 65535) return SPITE_UNSUPPORTED;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (dtype == SPITE_DT_F32) qk_prepare_kernel<float><<<grid, 128, 0, st>>>(*p, *b, *c);
+    else if (dtype == SPITE_DT_BF16) qk_prepare_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>(*p, *b, *c);
+    else return SPITE_BAD_ARG;
+    return spite_launch_status();
+}
+
+SPITE_API int spite_paged_attention(int dtype, const AttentionParams* p, const StepTokens* b,
+                                    const PagedCache* c, void* stream) {
+    if (!p || !p->q || !p->out) return SPITE_BAD_ARG;
+    const int chk = check_common(b, c, p->num_heads);
+    if (chk != SPITE_OK) return chk;
+    if (p->window_kind < 0 || p->window_kind > 2) return SPITE_BAD_ARG;
+    if (p->window_kind != SPITE_WINDOW_FULL && p->window_size < 1) return SPITE_BAD_ARG;
+    if (b->n_tokens == 0) return SPITE_OK;
+    dim3 grid(b->n_tokens, (p->num_heads + 3) / 4);
+    if (grid.y > 65535) return SPITE_UNSUPPORTED;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (dtype == SPITE_DT_F32) paged_attention_kernel<float><<<grid, 128, 0, st>>>(*p, *b, *c);
+    else if (dtype == SPITE_DT_BF16) paged_attention_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>(*p, *b, *c);
+    else return SPITE_BAD_ARG;
+    return spite_launch_status();
+}

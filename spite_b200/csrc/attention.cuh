@@ -1,0 +1,55 @@
+// Argument blocks of the attention kernels.
+#pragma once
+#include "common.cuh"
+
+#define SPITE_WINDOW_FULL 0      // keys 0..pos
+#define SPITE_WINDOW_CHUNK 1     // keys of the query's chunk: floor(pos/size)*size .. pos
+#define SPITE_WINDOW_SLIDING 2   // the last `size` keys: max(0, pos-size+1) .. pos
+
+// The tokens of one step, flattened.  Token t belongs to segment seg_of_token[t]
+// (one segment per request in the step) and sits at absolute position positions[t].
+// block_table[seg * table_width + p / page_size] is the page that holds position p.
+struct StepTokens {
+    const int* positions;
+    const int* seg_of_token;
+    const int* block_table;
+    int table_width;
+    int n_tokens;
+};
+
+// One cache: keys at kv, values at kv + v_offset (elements); a page holds, for every
+// kv head, page_size rows of head_dim elements: [pages][kv heads][page_size][head_dim].
+struct PagedCache {
+    void* kv;
+    long long v_offset;
+    int n_pages;
+    int page_size;
+    int num_kv_heads;
+    int head_dim;
+};
+
+struct QkPrepareParams {
+    const void* qkv;            // [tokens, (nq + 2 nkv) * head_dim]: q heads, k heads, v heads
+    void* q_out;                // [tokens, nq * head_dim]
+    const float* inv_freq;      // [head_dim / 2] rotation frequencies, or null: no rotation
+    float qk_norm_eps;          // > 0: weightless RMS norm of every q and k head after the rotation
+    int temperature_floor;      // > 0: q *= ln(floor((pos+1)/floor) + 1) * temperature_scale + 1
+    float temperature_scale;
+    int num_heads;
+    int write_cache;            // append k and v to the cache
+};
+
+struct AttentionParams {
+    const void* q;              // [tokens, nq * head_dim]
+    void* out;                  // [tokens, nq * head_dim]
+    int num_heads;
+    int window_kind;
+    int window_size;
+    float softmax_scale;
+};
+
+__device__ __forceinline__ int window_lowest(int kind, int size, int pos) {
+    if (kind == SPITE_WINDOW_CHUNK) return (pos / size) * size;
+    if (kind == SPITE_WINDOW_SLIDING) return max(0, pos - size + 1);
+    return 0;
+}

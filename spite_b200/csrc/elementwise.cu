@@ -1,0 +1,66 @@
+// Embedding gather and RMS norm.  Both are bound by memory traffic: one read of
+// the row, one write.  The residual stream is float32; the norm writes the
+// model's activation type.
+#include "common.cuh"
+
+// h[m, :] = table[token[m], :]            (crates/spite-models/src/llama/llama4.rs:118-119)
+template <typename T>
+__global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ tokens,
+                             float* __restrict__ h, int d, int vocab) {
+    const int m = blockIdx.x;
+    const int tok = tokens[m];
+    float* out = h + (size_t)m * d;
+    if (tok < 0 || tok >= vocab) {          // the host rejects such ids before the launch
+        for (int i = threadIdx.x; i < d; i += blockDim.x) out[i] = 0.f;
+        return;
+    }
+    const T* row = table + (size_t)tok * d;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) out[i] = to_f32(row[i]);
+}
+
+// y[i, :] = x[r, :] * rsqrt(mean(x[r]^2) + eps) * gain      r = rows ? rows[i] : i
+// (crates/spite-models/src/dense.rs:175-181; the sum runs in float32)
+template <typename T>
+__global__ void rms_norm_kernel(const float* __restrict__ x, const float* __restrict__ gain,
+                                const int* __restrict__ rows, T* __restrict__ y, int d, float eps) {
+    __shared__ float scratch[33];
+    const int i = blockIdx.x;
+    const int r = rows ? rows[i] : i;
+    const float* in = x + (size_t)r * d;
+    float s = 0.f;
+    for (int c = threadIdx.x; c < d; c += blockDim.x) { float v = in[c]; s += v * v; }
+    s = block_sum(s, scratch);
+    const float scale = 1.0f / sqrtf(s / (float)d + eps);
+    T* out = y + (size_t)i * d;
+    for (int c = threadIdx.x; c < d; c += blockDim.x) out[c] = from_f32<T>(in[c] * scale * gain[c]);
+}
+
+SPITE_API int spite_embed(int dtype, const void* table, const int* tokens, float* h,
+                          int n_tokens, int d, int vocab, void* stream) {
+    if (!table || !tokens || !h || n_tokens < 0 || d <= 0 || vocab <= 0) return SPITE_BAD_ARG;
+    if (n_tokens == 0) return SPITE_OK;
+    cudaStream_t st = (cudaStream_t)stream;
+    const int threads = d >= 1024 ? 256 : 128;
+    if (dtype == SPITE_DT_F32)
+        embed_kernel<float><<<n_tokens, threads, 0, st>>>((const float*)table, tokens, h, d, vocab);
+    else if (dtype == SPITE_DT_BF16)
+        embed_kernel<__nv_bfloat16><<<n_tokens, threads, 0, st>>>((const __nv_bfloat16*)table, tokens, h, d, vocab);
+    else
+        return SPITE_BAD_ARG;
+    return spite_launch_status();
+}
+
+SPITE_API int spite_rms_norm(int out_dtype, const float* x, const float* gain, const int* rows,
+                             void* y, int n_rows, int d, float eps, void* stream) {
+    if (!x || !gain || !y || n_rows < 0 || d <= 0 || !(eps > 0.f)) return SPITE_BAD_ARG;
+    if (n_rows == 0) return SPITE_OK;
+    cudaStream_t st = (cudaStream_t)stream;
+    const int threads = d >= 2048 ? 512 : (d >= 512 ? 256 : 128);
+    if (out_dtype == SPITE_DT_F32)
+        rms_norm_kernel<float><<<n_rows, threads, 0, st>>>(x, gain, rows, (float*)y, d, eps);
+    else if (out_dtype == SPITE_DT_BF16)
+        rms_norm_kernel<__nv_bfloat16><<<n_rows, threads, 0, st>>>(x, gain, rows, (__nv_bfloat16*)y, d, eps);
+    else
+        return SPITE_BAD_ARG;
+    return spite_launch_status();
+}

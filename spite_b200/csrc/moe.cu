@@ -1,0 +1,120 @@
+// Router of a mixture-of-experts feed-forward and the ordering of tokens by expert.
+//
+// route: logits = Wr x in float32 (crates/spite-models/src/moe.rs:65-66); the k
+//   largest raw logits are chosen, equal logits preferring the lower expert id
+//   (moe.rs:110-116, a stable descending sort); the weight is sigmoid(logit)
+//   (moe.rs:120).  No softmax, no renormalisation.
+// Choices are stored slot-major: expert_ids[slot][token], weights[slot][token].
+// sort: for every choice slot a stable counting sort of the tokens by expert:
+//   offsets[slot][e] .. offsets[slot][e+1] are the places of expert e's tokens in
+//   sorted_rows[slot][:], in ascending token order.  No host round trip: the grouped
+//   products read these arrays on the device.
+#include "common.cuh"
+
+namespace {
+
+constexpr int MAX_EXPERTS = 1024;
+
+// grid ceil(tokens/4), block 128: one warp per token.
+template <typename T>
+__global__ void __launch_bounds__(128) route_kernel(const T* __restrict__ x, const float* __restrict__ wr,
+                                                    int n_tokens, int d, int n_experts, int top_k,
+                                                    int* __restrict__ expert_ids, float* __restrict__ weights,
+                                                    float* __restrict__ logits_out) {
+    extern __shared__ float logits_s[];                      // [4][n_experts]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * 4 + warp;
+    if (t >= n_tokens) return;
+    float* lg = logits_s + (size_t)warp * n_experts;
+    const T* xr = x + (size_t)t * d;
+    for (int e = 0; e < n_experts; ++e) {
+        const float* w = wr + (size_t)e * d;
+        float s = 0.f;
+        for (int k = lane; k < d; k += 32) s = fmaf(to_f32(xr[k]), w[k], s);
+        s = warp_sum(s);
+        if (lane == 0) {
+            lg[e] = s;
+            if (logits_out) logits_out[(size_t)t * n_experts + e] = s;
+        }
+    }
+    __syncwarp();
+    for (int slot = 0; slot < top_k; ++slot) {
+        float best = -INFINITY;
+        int best_e = 0x7fffffff;
+        for (int e = lane; e < n_experts; e += 32) {
+            const float v = lg[e];
+            if (v > best || (v == best && e < best_e)) { best = v; best_e = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+            if (ov > best || (ov == best && oe < best_e)) { best = ov; best_e = oe; }
+        }
+        if (best_e == 0x7fffffff) best_e = 0;                // all logits NaN: still a valid id
+        if (lane == 0) {
+            expert_ids[(size_t)slot * n_tokens + t] = best_e;
+            weights[(size_t)slot * n_tokens + t] = 1.0f / (1.0f + expf(-best));
+            lg[best_e] = -INFINITY;
+        }
+        __syncwarp();
+    }
+}
+
+// grid top_k, block 1024: block `slot` sorts the tokens by their slot-th expert.
+__global__ void __launch_bounds__(1024) sort_by_expert_kernel(const int* __restrict__ expert_ids, int n_tokens,
+                                                              int n_experts, int top_k,
+                                                              int* __restrict__ offsets,
+                                                              int* __restrict__ sorted_rows) {
+    __shared__ int counts[MAX_EXPERTS + 1];
+    const int slot = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    for (int e = threadIdx.x; e <= n_experts; e += blockDim.x) counts[e] = 0;
+    __syncthreads();
+    for (int t = threadIdx.x; t < n_tokens; t += blockDim.x)
+        atomicAdd(&counts[expert_ids[(size_t)slot * n_tokens + t] + 1], 1);
+    __syncthreads();
+    if (threadIdx.x == 0)
+        for (int e = 0; e < n_experts; ++e) counts[e + 1] += counts[e];
+    __syncthreads();
+    int* off = offsets + (size_t)slot * (n_experts + 1);
+    for (int e = threadIdx.x; e <= n_experts; e += blockDim.x) off[e] = counts[e];
+    int* rows = sorted_rows + (size_t)slot * n_tokens;
+    for (int e = warp; e < n_experts; e += nwarps) {
+        int base = counts[e];
+        if (counts[e + 1] == base) continue;
+        for (int t0 = 0; t0 < n_tokens; t0 += 32) {
+            const int t = t0 + lane;
+            const bool mine = t < n_tokens && expert_ids[(size_t)slot * n_tokens + t] == e;
+            const unsigned mask = __ballot_sync(0xffffffffu, mine);
+            if (mine) rows[base + __popc(mask & ((1u << lane) - 1u))] = t;
+            base += __popc(mask);
+        }
+    }
+}
+
+}  // namespace
+
+SPITE_API int spite_moe_route(int dtype, const void* x, const float* w_router, int n_tokens, int d,
+                              int n_experts, int top_k, int* expert_ids, float* weights,
+                              float* logits_out, int* offsets, int* sorted_rows, void* stream) {
+    if (!x || !w_router || !expert_ids || !weights || !offsets || !sorted_rows) return SPITE_BAD_ARG;
+    if (n_tokens < 0 || d <= 0 || n_experts < 1 || top_k < 1 || top_k > n_experts) return SPITE_BAD_ARG;
+    if (n_experts > MAX_EXPERTS) return SPITE_UNSUPPORTED;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (n_tokens > 0) {
+        const int grid = (n_tokens + 3) / 4;
+        const size_t smem = (size_t)4 * n_experts * sizeof(float);
+        if (dtype == SPITE_DT_F32)
+            route_kernel<float><<<grid, 128, smem, st>>>((const float*)x, w_router, n_tokens, d, n_experts,
+                                                         top_k, expert_ids, weights, logits_out);
+        else if (dtype == SPITE_DT_BF16)
+            route_kernel<__nv_bfloat16><<<grid, 128, smem, st>>>((const __nv_bfloat16*)x, w_router, n_tokens, d,
+                                                                 n_experts, top_k, expert_ids, weights, logits_out);
+        else
+            return SPITE_BAD_ARG;
+        if (cudaGetLastError() != cudaSuccess) return SPITE_LAUNCH_FAILED;
+    }
+    sort_by_expert_kernel<<<top_k, 1024, 0, st>>>(expert_ids, n_tokens, n_experts, top_k, offsets, sorted_rows);
+    return spite_launch_status();
+}

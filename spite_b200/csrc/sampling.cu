@@ -1,0 +1,274 @@
+// Token sampling on the device, one block per row of logits.
+//
+// The pipeline and its order are those of giveen/spite's sampler
+// (crates/spite-sampling/src/lib.rs:273-296): repetition penalty over the distinct
+// tokens of the trailing context (lib.rs:208-231), temperature (117-125), min-p
+// (178-189), top-k (128-143), top-p (146-174), then the argmax when temperature <= 0
+// (236-243; of equal maxima the highest index wins, as Rust's `max_by` returns the
+// last) or a multinomial draw against unnormalised masses exp(l - max) with the
+// 64-bit LCG of lib.rs:343-348 (first index whose running sum reaches u * total,
+// 247-265).  Sums are float32; a block adds in a fixed order, so a row's result does
+// not depend on the other rows.
+#include "common.cuh"
+
+namespace {
+
+constexpr int THREADS = 1024;
+
+__device__ __forceinline__ unsigned order_key(float v) {
+    const unsigned u = __float_as_uint(v);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    v = warp_max(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < (THREADS >> 5) ? scratch[lane] : -INFINITY;
+        t = warp_max(t);
+        if (lane == 0) scratch[32] = t;
+    }
+    __syncthreads();
+    return scratch[32];
+}
+
+// Largest index holding the maximum (argmax with ties to the highest index).
+__device__ int block_argmax_last(const float* l, int n, float* fscratch, int* iscratch) {
+    float best = -INFINITY;
+    int idx = -1;
+    for (int i = threadIdx.x; i < n; i += THREADS) {
+        const float v = l[i];
+        if (v > best || (v == best && i > idx) || idx < 0) { best = v; idx = i; }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+        if (oi >= 0 && (idx < 0 || ov > best || (ov == best && oi > idx))) { best = ov; idx = oi; }
+    }
+    __syncthreads();
+    if (lane == 0) { fscratch[warp] = best; iscratch[warp] = idx; }
+    __syncthreads();
+    if (warp == 0) {
+        best = lane < (THREADS >> 5) ? fscratch[lane] : -INFINITY;
+        idx = lane < (THREADS >> 5) ? iscratch[lane] : -1;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+            if (oi >= 0 && (idx < 0 || ov > best || (ov == best && oi > idx))) { best = ov; idx = oi; }
+        }
+        if (lane == 0) iscratch[32] = idx;
+    }
+    __syncthreads();
+    return iscratch[32];
+}
+
+// First index i (ascending) at which the running sum of f(0..i) reaches `target`;
+// -1 if it never does.  Every thread owns a contiguous range of indices.
+template <typename F>
+__device__ int block_first_reaching(int n, float target, F f, float* fscratch, int* iscratch) {
+    const int chunk = (n + THREADS - 1) / THREADS;
+    const int lo = min(n, (int)threadIdx.x * chunk), hi = min(n, lo + chunk);
+    float mine = 0.f;
+    for (int i = lo; i < hi; ++i) mine += f(i);
+    // exclusive scan of the per-thread sums: within a warp by shuffles, across warps serially
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float incl = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const float t = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += t;
+    }
+    __syncthreads();
+    if (lane == 31) fscratch[warp] = incl;
+    if (threadIdx.x == 0) iscratch[32] = 0x7fffffff;
+    __syncthreads();
+    float before = 0.f;
+    for (int w = 0; w < warp; ++w) before += fscratch[w];
+    float run = before + (incl - mine);
+    if (threadIdx.x == 0 || run < target) {
+        // the crossing may lie in this range: walk it
+        for (int i = lo; i < hi; ++i) {
+            run += f(i);
+            if (run >= target) { atomicMin(&iscratch[32], i); break; }
+        }
+    } else if (lo < hi) {
+        // the sum before this range has reached the target already; if rounding kept the
+        // owner of the crossing from seeing it, this range's first index stands in
+        atomicMin(&iscratch[32], lo);
+    }
+    __syncthreads();
+    const int r = iscratch[32];
+    __syncthreads();
+    return r == 0x7fffffff ? -1 : r;
+}
+
+struct SampleParams {
+    const float* logits;          // [rows, vocab], not modified
+    float* work;                  // [rows, vocab] scratch
+    const float* temperature;     // per row; <= 0: argmax
+    const int* top_k;             // per row; 0: off
+    const float* top_p;           // per row; >= 1: off
+    const float* min_p;           // per row; <= 0: off
+    const float* repetition_penalty;  // per row; 1: off
+    const int* context;           // tokens of all rows, row r at [context_offsets[r], context_offsets[r+1])
+    const int* context_offsets;   // the window (`repeat_last_n`) is applied by the caller
+    unsigned long long* rng_state;    // per row, advanced once per multinomial draw
+    int* out_tokens;              // [rows]
+    int vocab;
+};
+
+__global__ void __launch_bounds__(THREADS) sample_kernel(const SampleParams p) {
+    __shared__ float fs[33];
+    __shared__ int is[33];
+    __shared__ int hist[256];
+    const int r = blockIdx.x;
+    const int V = p.vocab;
+    const float* in = p.logits + (size_t)r * V;
+    float* l = p.work + (size_t)r * V;
+    const float T = p.temperature[r];
+
+    for (int i = threadIdx.x; i < V; i += THREADS) l[i] = in[i];
+    __syncthreads();
+    const float pen = p.repetition_penalty ? p.repetition_penalty[r] : 1.f;
+    if (fabsf(pen - 1.f) >= 1.1920929e-07f && p.context) {
+        // every occurrence writes the same function of the unmodified logit
+        for (int i = p.context_offsets[r] + threadIdx.x; i < p.context_offsets[r + 1]; i += THREADS) {
+            const int tok = p.context[i];
+            if (tok >= 0 && tok < V) { const float v = in[tok]; l[tok] = v > 0.f ? v / pen : v * pen; }
+        }
+        __syncthreads();
+    }
+    if (T > 0.f)
+        for (int i = threadIdx.x; i < V; i += THREADS) l[i] = l[i] / T;
+    __syncthreads();
+
+    const float minp = p.min_p ? p.min_p[r] : 0.f;
+    if (minp > 0.f) {
+        float mx = -INFINITY;
+        for (int i = threadIdx.x; i < V; i += THREADS) mx = fmaxf(mx, l[i]);
+        mx = block_max(mx, fs);
+        const float thresh = mx + logf(minp);
+        for (int i = threadIdx.x; i < V; i += THREADS) if (l[i] < thresh) l[i] = -INFINITY;
+        __syncthreads();
+    }
+
+    const int k = p.top_k ? p.top_k[r] : 0;
+    if (k > 0 && k < V) {
+        // k-th largest key by radix selection, 8 bits a pass
+        unsigned prefix = 0, mask = 0;
+        int remaining = k;
+        for (int shift = 24; shift >= 0; shift -= 8) {
+            for (int b = threadIdx.x; b < 256; b += THREADS) hist[b] = 0;
+            __syncthreads();
+            for (int i = threadIdx.x; i < V; i += THREADS) {
+                const unsigned key = order_key(l[i]);
+                if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 255], 1);
+            }
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                int b = 255, rem = remaining;
+                for (; b > 0; --b) { if (hist[b] >= rem) break; rem -= hist[b]; }
+                is[0] = b; is[1] = rem;
+            }
+            __syncthreads();
+            prefix |= (unsigned)is[0] << shift;
+            mask |= 255u << shift;
+            remaining = is[1];
+            __syncthreads();
+        }
+        for (int i = threadIdx.x; i < V; i += THREADS) if (order_key(l[i]) < prefix) l[i] = -INFINITY;
+        __syncthreads();
+    }
+
+    float mx = -INFINITY;
+    for (int i = threadIdx.x; i < V; i += THREADS) mx = fmaxf(mx, l[i]);
+    mx = block_max(mx, fs);
+
+    const float topp = p.top_p ? p.top_p[r] : 1.f;
+    if (topp < 1.f && mx > -INFINITY) {
+        float tot = 0.f;
+        for (int i = threadIdx.x; i < V; i += THREADS) tot += expf(l[i] - mx);
+        tot = block_sum(tot, fs);
+        const float want = topp * tot;
+        // largest key K with mass(key >= K) >= want, by bisection on the key bits
+        unsigned K = 0;
+        for (int bit = 31; bit >= 0; --bit) {
+            const unsigned cand = K | (1u << bit);
+            float m = 0.f;
+            for (int i = threadIdx.x; i < V; i += THREADS) if (order_key(l[i]) >= cand) m += expf(l[i] - mx);
+            m = block_sum(m, fs);
+            if (m >= want) K = cand;
+        }
+        float above = 0.f, tie_mass = 0.f, ties = 0.f;
+        for (int i = threadIdx.x; i < V; i += THREADS) {
+            const unsigned key = order_key(l[i]);
+            if (key > K) above += expf(l[i] - mx);
+            else if (key == K) { ties += 1.f; tie_mass = expf(l[i] - mx); }
+        }
+        above = block_sum(above, fs);
+        ties = block_sum(ties, fs);
+        tie_mass = block_max(tie_mass, fs);
+        // of equal logits at the cut, the sorted order keeps the lower indices first
+        float keep = tie_mass > 0.f ? ceilf((want - above) / tie_mass) : ties;
+        keep = fminf(fmaxf(keep, 1.f), ties);
+        int last_tie = V;
+        if (keep < ties) {
+            auto is_tie = [&](int i) { return order_key(l[i]) == K ? 1.f : 0.f; };
+            last_tie = block_first_reaching(V, keep, is_tie, fs, is);
+        }
+        for (int i = threadIdx.x; i < V; i += THREADS) {
+            const unsigned key = order_key(l[i]);
+            if (key < K || (key == K && i > last_tie)) l[i] = -INFINITY;
+        }
+        __syncthreads();
+    }
+
+    int token;
+    if (T <= 0.f) {
+        token = block_argmax_last(l, V, fs, is);
+    } else {
+        unsigned long long s = p.rng_state[r];
+        s = s * 6364136223846793005ull + 1442695040888963407ull;
+        const float u = (float)(s >> 33) / 2147483648.0f;
+        float tot = 0.f;
+        for (int i = threadIdx.x; i < V; i += THREADS) tot += expf(l[i] - mx);
+        tot = block_sum(tot, fs);
+        const float target = u * tot;
+        auto mass = [&](int i) { return expf(l[i] - mx); };
+        token = block_first_reaching(V, target, mass, fs, is);
+        if (token < 0) token = block_argmax_last(l, V, fs, is);
+        if (threadIdx.x == 0) p.rng_state[r] = s;
+    }
+    if (threadIdx.x == 0) p.out_tokens[r] = token;
+}
+
+__global__ void __launch_bounds__(THREADS) argmax_kernel(const float* logits, int vocab, int* out) {
+    __shared__ float fs[33];
+    __shared__ int is[33];
+    const int idx = block_argmax_last(logits + (size_t)blockIdx.x * vocab, vocab, fs, is);
+    if (threadIdx.x == 0) out[blockIdx.x] = idx;
+}
+
+}  // namespace
+
+SPITE_API int spite_argmax(const float* logits, int rows, int vocab, int* out, void* stream) {
+    if (!logits || !out || rows < 0 || vocab < 1) return SPITE_BAD_ARG;
+    if (rows == 0) return SPITE_OK;
+    argmax_kernel<<<rows, THREADS, 0, (cudaStream_t)stream>>>(logits, vocab, out);
+    return spite_launch_status();
+}
+
+SPITE_API int spite_sample(const SampleParams* p, int rows, void* stream) {
+    if (!p || !p->logits || !p->work || !p->temperature || !p->rng_state || !p->out_tokens) return SPITE_BAD_ARG;
+    if (rows < 0 || p->vocab < 1) return SPITE_BAD_ARG;
+    if (p->context && !p->context_offsets) return SPITE_BAD_ARG;
+    if (rows == 0) return SPITE_OK;
+    sample_kernel<<<rows, THREADS, 0, (cudaStream_t)stream>>>(*p);
+    return spite_launch_status();
+}

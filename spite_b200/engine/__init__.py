@@ -1,0 +1,6 @@
+from .batch import Segment, StepBatch, build_step_batch
+from .executor import ContextOverflow, Engine, StepEntry, StepError
+from .model import Model, resolve_dtype
+
+__all__ = ["Segment", "StepBatch", "build_step_batch", "ContextOverflow", "Engine", "StepEntry",
+           "StepError", "Model", "resolve_dtype"]

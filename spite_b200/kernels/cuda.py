@@ -1,0 +1,257 @@
+"""`CudaKernels`: the product kernel set.  Hand-written CUDA for sm_100a under
+`spite_b200/csrc`, compiled in-tree and called through ctypes on the current
+torch stream.  There is no other implementation in the package: without a CUDA
+device or without the compiled libraries every call raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import build
+from .api import KernelError, KernelSet, Routing
+
+_DT = {torch.float32: 0, torch.bfloat16: 1}
+_STATUS = {-1: "malformed argument", -2: "size not supported by this kernel", -3: "launch failed"}
+
+EPI_STORE, EPI_STORE_F32, EPI_ADD_F32, EPI_SWIGLU = 0, 1, 2, 3
+_WINDOW = {"full": 0, "chunk": 1, "sliding": 2}
+
+
+class GemmParams(C.Structure):
+    _fields_ = [("A", C.c_void_p), ("W", C.c_void_p), ("C", C.c_void_p),
+                ("a_rows", C.c_void_p), ("c_rows", C.c_void_p), ("group_offsets", C.c_void_p),
+                ("row_scale", C.c_void_p),
+                ("lda", C.c_longlong), ("ldc", C.c_longlong), ("w_group_stride", C.c_longlong),
+                ("n_groups", C.c_int), ("M", C.c_int), ("N", C.c_int), ("K", C.c_int),
+                ("epilogue", C.c_int), ("scale_by_a_row", C.c_int)]
+
+
+class StepTokens(C.Structure):
+    _fields_ = [("positions", C.c_void_p), ("seg_of_token", C.c_void_p), ("block_table", C.c_void_p),
+                ("table_width", C.c_int), ("n_tokens", C.c_int)]
+
+
+class PagedCache(C.Structure):
+    _fields_ = [("kv", C.c_void_p), ("v_offset", C.c_longlong), ("n_pages", C.c_int),
+                ("page_size", C.c_int), ("num_kv_heads", C.c_int), ("head_dim", C.c_int)]
+
+
+class QkPrepareParams(C.Structure):
+    _fields_ = [("qkv", C.c_void_p), ("q_out", C.c_void_p), ("inv_freq", C.c_void_p),
+                ("qk_norm_eps", C.c_float), ("temperature_floor", C.c_int),
+                ("temperature_scale", C.c_float), ("num_heads", C.c_int), ("write_cache", C.c_int)]
+
+
+class AttentionParams(C.Structure):
+    _fields_ = [("q", C.c_void_p), ("out", C.c_void_p), ("num_heads", C.c_int),
+                ("window_kind", C.c_int), ("window_size", C.c_int), ("softmax_scale", C.c_float)]
+
+
+class SampleParams(C.Structure):
+    _fields_ = [("logits", C.c_void_p), ("work", C.c_void_p), ("temperature", C.c_void_p),
+                ("top_k", C.c_void_p), ("top_p", C.c_void_p), ("min_p", C.c_void_p),
+                ("repetition_penalty", C.c_void_p), ("context", C.c_void_p),
+                ("context_offsets", C.c_void_p), ("rng_state", C.c_void_p),
+                ("out_tokens", C.c_void_p), ("vocab", C.c_int)]
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def _check(status, what):
+    if status != 0:
+        raise KernelError(f"{what}: {_STATUS.get(status, f'status {status}')}")
+
+
+class CudaKernels(KernelSet):
+    def __init__(self, dtype: torch.dtype, device="cuda:0"):
+        if dtype not in _DT:
+            raise KernelError(f"no kernel set for {dtype}; use torch.bfloat16 or torch.float32")
+        if not torch.cuda.is_available():
+            raise KernelError("spite_b200 needs a CUDA device (sm_100a); there is no CPU path")
+        self.dtype = dtype
+        self.device = torch.device(device)
+        self._dt = _DT[dtype]
+        self._libs = {}
+
+    # ------------------------------------------------------------------ helpers
+    def _lib(self, name):
+        lib = self._libs.get(name)
+        if lib is None:
+            lib = self._libs[name] = build.load(name)
+        return lib
+
+    @staticmethod
+    def _stream():
+        return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def _t(self, t, dtype=None, name="tensor"):
+        if t.device.type != "cuda" or not t.is_contiguous():
+            raise KernelError(f"{name} must be a contiguous CUDA tensor")
+        if dtype is not None and t.dtype != dtype:
+            raise KernelError(f"{name} must be {dtype}, is {t.dtype}")
+        return t
+
+    # ------------------------------------------------------------------ elementwise
+    def embed(self, table, token_ids, out_h):
+        self._t(table, self.dtype, "table"); self._t(token_ids, torch.int32, "token_ids")
+        self._t(out_h, torch.float32, "out_h")
+        V, d = table.shape
+        st = self._lib("elementwise").spite_embed(
+            self._dt, C.c_void_p(table.data_ptr()), C.c_void_p(token_ids.data_ptr()),
+            C.c_void_p(out_h.data_ptr()), token_ids.numel(), d, V, self._stream())
+        _check(st, "embed")
+
+    def rms_norm(self, h, gain, eps, out, rows=None):
+        self._t(h, torch.float32, "h"); self._t(gain, torch.float32, "gain"); self._t(out, None, "out")
+        if rows is not None:
+            self._t(rows, torch.int32, "rows")
+        n, d = out.shape
+        st = self._lib("elementwise").spite_rms_norm(
+            _DT[out.dtype], C.c_void_p(h.data_ptr()), C.c_void_p(gain.data_ptr()),
+            C.c_void_p(_ptr(rows)), C.c_void_p(out.data_ptr()), n, d, C.c_float(eps), self._stream())
+        _check(st, "rms_norm")
+
+    # ------------------------------------------------------------------ matrix products
+    def _gemm(self, p: GemmParams, what):
+        st = self._lib("gemm_simt").spite_gemm_simt(self._dt, C.byref(p), self._stream())
+        _check(st, what)
+
+    def linear(self, x, w, out, *, accumulate=False, row_scale=None):
+        self._t(x, self.dtype, "x"); self._t(w, self.dtype, "w"); self._t(out, None, "out")
+        M, K = x.shape
+        N = w.shape[0]
+        if w.shape[1] != K or tuple(out.shape) != (M, N):
+            raise KernelError(f"linear: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} do not fit")
+        if accumulate:
+            if out.dtype != torch.float32:
+                raise KernelError("linear(accumulate=True) needs a float32 output")
+            epi = EPI_ADD_F32
+        elif out.dtype == torch.float32 and self.dtype != torch.float32:
+            epi = EPI_STORE_F32
+        elif out.dtype == self.dtype:
+            epi = EPI_STORE
+        else:
+            raise KernelError(f"linear: output type {out.dtype} not supported")
+        p = GemmParams(A=x.data_ptr(), W=w.data_ptr(), C=out.data_ptr(), a_rows=None, c_rows=None,
+                       group_offsets=None, row_scale=_ptr(row_scale), lda=K, ldc=N, w_group_stride=0,
+                       n_groups=1, M=M, N=N, K=K, epilogue=epi, scale_by_a_row=0)
+        self._gemm(p, "linear")
+
+    def linear_swiglu(self, x, w_gate_up, out, *, row_scale=None):
+        self._t(x, self.dtype, "x"); self._t(w_gate_up, self.dtype, "w"); self._t(out, self.dtype, "out")
+        M, K = x.shape
+        F = w_gate_up.shape[0] // 2
+        if w_gate_up.shape != (2 * F, K) or tuple(out.shape) != (M, F):
+            raise KernelError("linear_swiglu: shapes do not fit")
+        p = GemmParams(A=x.data_ptr(), W=w_gate_up.data_ptr(), C=out.data_ptr(), a_rows=None, c_rows=None,
+                       group_offsets=None, row_scale=_ptr(row_scale), lda=K, ldc=F, w_group_stride=0,
+                       n_groups=1, M=M, N=F, K=K, epilogue=EPI_SWIGLU, scale_by_a_row=0)
+        self._gemm(p, "linear_swiglu")
+
+    def grouped_linear_swiglu(self, x, w_gate_up, sorted_rows, offsets, row_scale, out):
+        self._t(x, self.dtype, "x"); self._t(w_gate_up, self.dtype, "w"); self._t(out, self.dtype, "out")
+        self._t(sorted_rows, torch.int32, "sorted_rows"); self._t(offsets, torch.int32, "offsets")
+        M, K = x.shape
+        E, F2, K2 = w_gate_up.shape
+        F = F2 // 2
+        if K2 != K or tuple(out.shape) != (M, F) or offsets.numel() != E + 1 or sorted_rows.numel() != M:
+            raise KernelError("grouped_linear_swiglu: shapes do not fit")
+        p = GemmParams(A=x.data_ptr(), W=w_gate_up.data_ptr(), C=out.data_ptr(),
+                       a_rows=sorted_rows.data_ptr(), c_rows=None, group_offsets=offsets.data_ptr(),
+                       row_scale=_ptr(row_scale), lda=K, ldc=F, w_group_stride=F2 * K,
+                       n_groups=E, M=M, N=F, K=K, epilogue=EPI_SWIGLU, scale_by_a_row=1)
+        self._gemm(p, "grouped_linear_swiglu")
+
+    def grouped_linear_accumulate(self, a, w_down, sorted_rows, offsets, h):
+        self._t(a, self.dtype, "a"); self._t(w_down, self.dtype, "w"); self._t(h, torch.float32, "h")
+        M, F = a.shape
+        E, d, F2 = w_down.shape
+        if F2 != F or h.shape[1] != d or offsets.numel() != E + 1 or sorted_rows.numel() != M:
+            raise KernelError("grouped_linear_accumulate: shapes do not fit")
+        p = GemmParams(A=a.data_ptr(), W=w_down.data_ptr(), C=h.data_ptr(), a_rows=None,
+                       c_rows=sorted_rows.data_ptr(), group_offsets=offsets.data_ptr(), row_scale=None,
+                       lda=F, ldc=d, w_group_stride=d * F, n_groups=E, M=M, N=d, K=F,
+                       epilogue=EPI_ADD_F32, scale_by_a_row=0)
+        self._gemm(p, "grouped_linear_accumulate")
+
+    # ------------------------------------------------------------------ attention
+    def _step_tokens(self, batch, group):
+        bt = batch.block_tables[group]
+        return StepTokens(positions=batch.positions.data_ptr(), seg_of_token=batch.seg_of_token.data_ptr(),
+                          block_table=bt.data_ptr(), table_width=bt.shape[1], n_tokens=batch.n_tokens)
+
+    def _paged(self, cache):
+        kv = cache.kv                       # [2, pages, nkv, page_size, hd]
+        self._t(kv, self.dtype, "cache")
+        return PagedCache(kv=kv.data_ptr(), v_offset=kv.stride(0), n_pages=kv.shape[1],
+                          page_size=kv.shape[3], num_kv_heads=kv.shape[2], head_dim=kv.shape[4])
+
+    def qk_prepare(self, qkv, q_out, batch, cache, *, num_heads, inv_freq, qk_norm_eps, temperature):
+        self._t(qkv, self.dtype, "qkv"); self._t(q_out, self.dtype, "q_out")
+        if inv_freq is not None:
+            self._t(inv_freq, torch.float32, "inv_freq")
+        floor, scale = (int(temperature[0]), float(temperature[1])) if temperature else (0, 0.0)
+        p = QkPrepareParams(qkv=qkv.data_ptr(), q_out=q_out.data_ptr(), inv_freq=_ptr(inv_freq),
+                            qk_norm_eps=float(qk_norm_eps or 0.0), temperature_floor=floor,
+                            temperature_scale=scale, num_heads=num_heads, write_cache=int(cache.write))
+        b, c = self._step_tokens(batch, cache.group), self._paged(cache)
+        st = self._lib("attention").spite_qk_prepare(self._dt, C.byref(p), C.byref(b), C.byref(c), self._stream())
+        _check(st, "qk_prepare")
+
+    def paged_attention(self, q, out, batch, cache, *, num_heads, window, softmax_scale):
+        self._t(q, self.dtype, "q"); self._t(out, self.dtype, "out")
+        p = AttentionParams(q=q.data_ptr(), out=out.data_ptr(), num_heads=num_heads,
+                            window_kind=_WINDOW[window.kind], window_size=int(window.size),
+                            softmax_scale=float(softmax_scale))
+        b, c = self._step_tokens(batch, cache.group), self._paged(cache)
+        st = self._lib("attention").spite_paged_attention(self._dt, C.byref(p), C.byref(b), C.byref(c),
+                                                          self._stream())
+        _check(st, "paged_attention")
+
+    # ------------------------------------------------------------------ mixture of experts
+    def moe_route(self, x, w_router, top_k, want_logits=False) -> Routing:
+        self._t(x, self.dtype, "x"); self._t(w_router, torch.float32, "w_router")
+        M, d = x.shape
+        E = w_router.shape[0]
+        dev = x.device
+        ids = torch.empty((top_k, M), dtype=torch.int32, device=dev)
+        wts = torch.empty((top_k, M), dtype=torch.float32, device=dev)
+        offsets = torch.empty((top_k, E + 1), dtype=torch.int32, device=dev)
+        rows = torch.empty((top_k, M), dtype=torch.int32, device=dev)
+        logits = torch.empty((M, E), dtype=torch.float32, device=dev) if want_logits else None
+        st = self._lib("moe").spite_moe_route(
+            self._dt, C.c_void_p(x.data_ptr()), C.c_void_p(w_router.data_ptr()), M, d, E, top_k,
+            C.c_void_p(ids.data_ptr()), C.c_void_p(wts.data_ptr()), C.c_void_p(_ptr(logits)),
+            C.c_void_p(offsets.data_ptr()), C.c_void_p(rows.data_ptr()), self._stream())
+        _check(st, "moe_route")
+        return Routing(ids, wts, offsets, rows, logits)
+
+    # ------------------------------------------------------------------ sampling
+    def argmax(self, logits):
+        self._t(logits, torch.float32, "logits")
+        R, V = logits.shape
+        out = torch.empty(R, dtype=torch.int32, device=logits.device)
+        st = self._lib("sampling").spite_argmax(C.c_void_p(logits.data_ptr()), R, V,
+                                                C.c_void_p(out.data_ptr()), self._stream())
+        _check(st, "argmax")
+        return out
+
+    def sample(self, logits, *, temperature, top_k=None, top_p=None, min_p=None, repetition_penalty=None,
+               context=None, context_offsets=None, rng_state):
+        self._t(logits, torch.float32, "logits"); self._t(temperature, torch.float32, "temperature")
+        self._t(rng_state, torch.int64, "rng_state")
+        R, V = logits.shape
+        work = torch.empty_like(logits)
+        out = torch.empty(R, dtype=torch.int32, device=logits.device)
+        p = SampleParams(logits=logits.data_ptr(), work=work.data_ptr(), temperature=temperature.data_ptr(),
+                         top_k=_ptr(top_k), top_p=_ptr(top_p), min_p=_ptr(min_p),
+                         repetition_penalty=_ptr(repetition_penalty), context=_ptr(context),
+                         context_offsets=_ptr(context_offsets), rng_state=rng_state.data_ptr(),
+                         out_tokens=out.data_ptr(), vocab=V)
+        st = self._lib("sampling").spite_sample(C.byref(p), R, self._stream())
+        _check(st, "sample")
+        return out

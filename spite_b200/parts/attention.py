@@ -1,0 +1,76 @@
+"""Grouped-query attention over the paged cache.
+
+One part serves every attention layer: the window rule (all keys, the keys of
+the query's chunk, the last W keys), the position encoding, the weightless
+per-head norm and the temperature factor are constructor parameters.
+
+Formulas: crates/spite-models/src/llama/llama4.rs:126-207 (projections, rotation
+then norm, temperature factor on layers without rotation, append to the cache,
+attention, output projection added to the residual stream) and
+crates/spite-compute/src/flash_attn.rs:111-156 (scores, mask, softmax, values).
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from ..cache import PagedKV, Window
+from ..config.specs import ConfigError, PartSpec
+from .base import Mixer, ParamSpec, build_part, register_mixer
+
+
+@register_mixer("paged_attention")
+class PagedAttention(Mixer):
+    kernel_libraries = ("gemm_simt", "attention")
+
+    def __init__(self, ctx, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
+                 position: PartSpec, window=("full", 0), qk_norm_eps=None, temperature_tuning=None,
+                 softmax_scale=None):
+        super().__init__(ctx)
+        if num_heads % num_kv_heads:
+            raise ConfigError(f"{num_heads} query heads cannot share {num_kv_heads} kv heads evenly")
+        if head_dim % 2 or head_dim > 256:
+            raise ConfigError(f"head_dim {head_dim} must be even and at most 256")
+        self.d, self.nq, self.nkv, self.hd = int(hidden_size), int(num_heads), int(num_kv_heads), int(head_dim)
+        self.window = window if isinstance(window, Window) else Window(window[0], int(window[1]))
+        self.position = build_part("position", position, ctx)
+        self.qk_norm_eps = None if qk_norm_eps is None else float(qk_norm_eps)
+        if temperature_tuning is not None:
+            floor, scale = temperature_tuning
+            if float(floor) != int(floor) or int(floor) < 1:
+                raise ConfigError(f"temperature floor_scale {floor} must be a positive integer")
+            temperature_tuning = (int(floor), float(scale))
+        self.temperature = temperature_tuning
+        self.softmax_scale = float(softmax_scale) if softmax_scale else 1.0 / math.sqrt(self.hd)
+        self.wqkv = self.wo = None
+
+    def param_specs(self):
+        d, nq, nkv, hd = self.d, self.nq, self.nkv, self.hd
+        return {"q_proj": ParamSpec((nq * hd, d)), "k_proj": ParamSpec((nkv * hd, d)),
+                "v_proj": ParamSpec((nkv * hd, d)), "o_proj": ParamSpec((d, nq * hd))}
+
+    def bind(self, params):
+        dt = self.ctx.dtype
+        # q, k and v rows in one matrix: one product per layer instead of three
+        self.wqkv = torch.cat([params["q_proj"].to(dt), params["k_proj"].to(dt), params["v_proj"].to(dt)], 0).contiguous()
+        self.wo = params["o_proj"].to(dt).contiguous()
+
+    def weight_bytes(self):
+        return (self.wqkv.numel() + self.wo.numel()) * self.wqkv.element_size()
+
+    def cache_request(self):
+        return PagedKV(self.window, self.nkv, self.hd), None
+
+    def forward(self, x, h, batch, cache):
+        M = x.shape[0]
+        k = self.k
+        qkv = torch.empty((M, (self.nq + 2 * self.nkv) * self.hd), dtype=x.dtype, device=x.device)
+        k.linear(x, self.wqkv, qkv)
+        q = torch.empty((M, self.nq * self.hd), dtype=x.dtype, device=x.device)
+        k.qk_prepare(qkv, q, batch, cache, num_heads=self.nq, inv_freq=self.position.frequencies(),
+                     qk_norm_eps=self.qk_norm_eps, temperature=self.temperature)
+        o = torch.empty_like(q)
+        k.paged_attention(q, o, batch, cache, num_heads=self.nq, window=self.window,
+                          softmax_scale=self.softmax_scale)
+        k.linear(o, self.wo, h, accumulate=True)
