@@ -236,13 +236,13 @@ def routed_experts(x, ids, weights, gate_up, down):
     T, d = x.shape
     f = down.shape[1]
     out = torch.zeros(T, d)
-    for t in range(T):
-        for slot in range(ids.shape[1]):
-            e = int(ids[t, slot])
-            xw = x[t] * weights[t, slot]
+    for slot in range(ids.shape[1]):
+        for e in ids[:, slot].unique().tolist():
+            rows = torch.nonzero(ids[:, slot] == e).flatten()
+            xw = x[rows] * weights[rows, slot][:, None]
             gu = xw @ gate_up[e].float()
-            a = gu[f:] * silu(gu[:f])
-            out[t] += a @ down[e].float()
+            a = gu[:, f:] * silu(gu[:, :f])
+            out[rows] += a @ down[e].float()
     return out
 
 
@@ -353,10 +353,9 @@ def lcg_next(state: int):
     return state, float(state >> 33) / 2147483648.0
 
 
-def sample_plain(logits, context, *, temperature, top_k=0, top_p=1.0, min_p=0.0,
-                 repetition_penalty=1.0, repeat_last_n=64, state=0):
-    """lib.rs:273-296 — penalty, temperature, min_p, top_k, top_p, then argmax
-    (temperature <= 0) or a multinomial draw (lib.rs:247-265).  Returns (token, state)."""
+def process_logits_plain(logits, context, *, temperature, top_k=0, top_p=1.0, min_p=0.0,
+                         repetition_penalty=1.0, repeat_last_n=64):
+    """lib.rs:273-279 — penalty, temperature, min_p, top_k, top_p, in this order."""
     l = logits.clone().float()
     if abs(repetition_penalty - 1.0) >= 1.1920929e-07:                   # lib.rs:208-231
         window = context if repeat_last_n == 0 or repeat_last_n >= len(context) else context[-repeat_last_n:]
@@ -377,6 +376,13 @@ def sample_plain(logits, context, *, temperature, top_k=0, top_p=1.0, min_p=0.0,
         cum = torch.cumsum(mass, 0) / total
         kept = int(torch.nonzero(cum >= top_p)[0]) + 1 if bool((cum >= top_p).any()) else l.numel()
         l[order.indices[max(kept, 1):]] = float("-inf")
+    return l
+
+
+def sample_plain(logits, context, *, temperature, state=0, **processors):
+    """lib.rs:283-296 — the processors, then argmax (temperature <= 0) or a multinomial
+    draw against unnormalised masses (lib.rs:247-265).  Returns (token, state)."""
+    l = process_logits_plain(logits, context, temperature=temperature, **processors)
     if temperature <= 0:
         return greedy_pick(l), state
     state, u = lcg_next(state)

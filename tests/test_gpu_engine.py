@@ -1,0 +1,139 @@
+"""The engine on the GPU, in float32 and in bfloat16, against the plain
+implementation: each request alone and whole; most of it in one step and the last
+32 tokens one by one; portions of changing size down to two tokens; mixed batches
+of up to four live requests with so few pages that they are used again; long
+decoding; the first tokens of a sequence; and `bin/trace_run` as a program."""
+import json
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+import helpers as H
+
+pytestmark = pytest.mark.gpu
+
+ROOT = Path(__file__).resolve().parent.parent
+# float32: sums in another order than the plain implementation's.  bfloat16: 8 bits of
+# mantissa at some thirty rounding points between the embedding and the logits.
+TOL = {"float32": 2e-5, "bfloat16": 4e-2}
+MARGIN = {"A": 0.012, "B": 0.03}      # router logit margin that bfloat16 rounding cannot flip
+
+
+@pytest.fixture(scope="module", params=["A", "B"])
+def folder(request, tmp_path_factory):
+    return H.write_model(tmp_path_factory.mktemp(f"model{request.param}"), request.param), request.param
+
+
+@pytest.fixture(scope="module", params=["float32", "bfloat16"])
+def setup(request, folder):
+    from spite_b200.engine import Model
+    path, name = folder
+    dtype = request.param
+    model = Model.from_folder(path, dtype=dtype, device="cuda:0")
+    vocab = model.plan.vocab_size
+    lengths = {"a": 83, "b": 40, "c": 37, "d": 66, "e": 21}
+    if dtype == "float32":
+        requests = {r: H.random_tokens(vocab, n, i) for i, (r, n) in enumerate(lengths.items())}
+    else:
+        requests = {r: H.decisive_tokens(path, n, i, MARGIN[name]) for i, (r, n) in enumerate(lengths.items())}
+    return path, model, requests, TOL[dtype]
+
+
+def _engine(model, steps, page_size):
+    from spite_b200.engine import Engine
+    return Engine(model, cache_tokens=H.max_tokens_of(steps), page_size=page_size, max_requests=4)
+
+
+@pytest.mark.parametrize("page_size", [16, 64])
+def test_whole(setup, page_size):
+    path, model, requests, tol = setup
+    steps = H.steps_whole(requests)
+    H.compare_with_plain(H.run_steps(_engine(model, steps, page_size), steps), path, requests, tol)
+
+
+def test_last_32_tokens_one_by_one(setup):
+    path, model, requests, tol = setup
+    steps = H.steps_last_decoded(requests, 32)
+    H.compare_with_plain(H.run_steps(_engine(model, steps, 16), steps), path, requests, tol)
+
+
+@pytest.mark.parametrize("seed", [0, 1])
+def test_portions_down_to_two_tokens(setup, seed):
+    path, model, requests, tol = setup
+    steps = H.steps_portions(requests, seed)
+    assert min(len(e["tokens"]) for s in steps for e in s["entries"]) == 2
+    H.compare_with_plain(H.run_steps(_engine(model, steps, 16), steps), path, requests, tol)
+
+
+@pytest.mark.parametrize("seed,page_size", [(0, 16), (1, 16), (2, 64)])
+def test_mixed_batches_reusing_pages(setup, seed, page_size):
+    path, model, requests, tol = setup
+    n_prompt = {r: max(2, len(t) - 12) for r, t in requests.items()}
+    steps = H.steps_mixed(requests, n_prompt, seed)
+    eng = _engine(model, steps, page_size)
+    assert eng.n_pages * page_size < sum(H._round64(len(t)) for t in requests.values())
+    H.compare_with_plain(H.run_steps(eng, steps), path, requests, tol)
+    assert eng.cache.free_pages() == [eng.n_pages] * len(eng.cache.pools)
+
+
+def test_first_tokens_of_a_sequence(setup):
+    """Positions 0..3 alone: one key, the first rotation angles, a page's first rows."""
+    path, model, requests, tol = setup
+    toks = requests["a"][:4]
+    steps = [{"step": i, "entries": [{"id": "s", "tokens": [t], "want": [0]}], "end": []}
+             for i, t in enumerate(toks)]
+    steps[-1]["end"] = ["s"]
+    H.compare_with_plain(H.run_steps(_engine(model, steps, 16), steps), path, {"s": toks}, tol)
+
+
+def test_long_decoding(setup):
+    """A short prompt, then 200 tokens one by one: several chunks and many pages pass."""
+    path, model, requests, tol = setup
+    vocab = model.plan.vocab_size
+    if tol < 1e-3:
+        toks = H.random_tokens(vocab, 216, 77)
+    else:
+        name = "A" if vocab == H.CONFIG_A["vocab_size"] else "B"
+        toks = H.decisive_tokens(path, 216, 77, MARGIN[name])
+    steps =[{"entries": [{"id": "l", "tokens": toks[:16], "want": list(range(16))}], "end": []}]
+    steps += [{"entries": [{"id": "l", "tokens": [t], "want": [0]}], "end": []} for t in toks[16:]]
+    steps[-1]["end"] = ["l"]
+    for i, s in enumerate(steps):
+        s["step"] = i
+    H.compare_with_plain(H.run_steps(_engine(model, steps, 16), steps), path, {"l": toks}, tol)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_program(folder, dtype, tmp_path):
+    """`bin/trace_run` as a user runs it: JSON lines in, `done <step>` lines and .f32 files out."""
+    path, name = folder
+    cfg = json.loads((Path(path) / "config.json").read_text())
+    vocab = cfg["vocab_size"]
+    if dtype == "float32":
+        reqs = {"p": H.random_tokens(vocab, 45, 5), "q": H.random_tokens(vocab, 30, 6)}
+    else:
+        reqs = {"p": H.decisive_tokens(path, 45, 5, MARGIN[name]), "q": H.decisive_tokens(path, 30, 6, MARGIN[name])}
+    steps = H.steps_mixed(reqs, {"p": 40, "q": 20}, seed=4)
+    out = tmp_path / "out"
+    proc = subprocess.run(
+        [sys.executable, str(ROOT / "bin" / "trace_run"), "--model", str(path), "--dtype", dtype,
+         "--out", str(out), "--max-tokens", str(H.max_tokens_of(steps))],
+        input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert [l for l in proc.stdout.split("\n") if l.startswith("done")] == [f"done {s['step']}" for s in steps]
+    pos, results = {}, {}
+    for s in steps:
+        n_want = sum(len(e["want"]) for e in s["entries"])
+        data = np.fromfile(out / f"{s['step']}.f32", dtype="<f4").reshape(n_want, vocab)
+        row = 0
+        for e in s["entries"]:
+            for w in e["want"]:
+                results[(e["id"], pos.get(e["id"], 0) + w)] = torch.from_numpy(data[row].copy())
+                row += 1
+            pos[e["id"]] = pos.get(e["id"], 0) + len(e["tokens"])
+    H.compare_with_plain(results, path, reqs, TOL[dtype])

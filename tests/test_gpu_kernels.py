@@ -1,0 +1,309 @@
+"""Each CUDA kernel alone against its plain torch restatement (float64 sums),
+at sizes other than the engine tests': widths and vocabularies that are no power
+of two, head sizes in steps of 16, odd numbers of heads and groups, empty
+experts, pages used out of order.  Inputs are built so that a fault shows: one
+far key among hundreds carries the attention, windows end inside pages."""
+import math
+
+import pytest
+import torch
+
+from reference_kernels import TorchReferenceKernels
+from spite_b200.cache import LayerCache, Window
+from spite_b200.engine.batch import Segment, build_step_batch
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+TOL = {torch.float32: 1e-5, torch.bfloat16: 1.2e-2}
+
+
+@pytest.fixture(scope="module", params=DTYPES, ids=["f32", "bf16"])
+def ks(request):
+    from spite_b200.kernels.cuda import CudaKernels
+    return CudaKernels(request.param, DEV)
+
+
+def ref_set(dtype):
+    return TorchReferenceKernels(dtype, "cpu", acc=torch.float64)
+
+
+def rnd(shape, dtype, seed, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to(dtype)
+
+
+def close(out, ref, tol, what=""):
+    out, ref = out.detach().cpu().double(), ref.detach().cpu().double()
+    assert torch.isfinite(out).all(), f"{what}: non-finite output"
+    err = float((out - ref).abs().max()) / max(float(ref.abs().max()), 1e-30)
+    assert err <= tol, f"{what}: error {err:.3e} of the output scale exceeds {tol:.1e}"
+
+
+# ---------------------------------------------------------------------------- elementwise
+@pytest.mark.parametrize("V,d,M", [(37, 48, 5), (1000, 200, 33)])
+def test_embed(ks, V, d, M):
+    table = rnd((V, d), ks.dtype, 1)
+    toks = torch.randint(0, V, (M,), dtype=torch.int32)
+    toks[0], toks[-1] = 0, V - 1
+    out = torch.full((M, d), 7.0, dtype=torch.float32, device=DEV)
+    ks.embed(table.to(DEV), toks.to(DEV), out)
+    assert torch.equal(out.cpu(), table[toks.long()].float())
+
+
+@pytest.mark.parametrize("M,d,eps", [(7, 48, 1e-5), (3, 5120, 1e-6), (19, 200, 1e-2)])
+def test_rms_norm(ks, M, d, eps):
+    h = rnd((M, d), torch.float32, 2, 3.0)
+    gain = rnd((d,), torch.float32, 3) + 1.0
+    out = torch.empty((M, d), dtype=ks.dtype, device=DEV)
+    ks.rms_norm(h.to(DEV), gain.to(DEV), eps, out)
+    ref = torch.empty((M, d), dtype=torch.float64)
+    ref_set(ks.dtype).rms_norm(h, gain, eps, ref)
+    close(out, ref, TOL[ks.dtype], "rms_norm")
+    rows = torch.tensor([M - 1, 0, M // 2], dtype=torch.int32)
+    out2 = torch.empty((3, d), dtype=ks.dtype, device=DEV)
+    ks.rms_norm(h.to(DEV), gain.to(DEV), eps, out2, rows.to(DEV))
+    assert torch.equal(out2.cpu(), out.cpu()[rows.long()])
+
+
+# ---------------------------------------------------------------------------- matrix products
+@pytest.mark.parametrize("M,N,K", [(1, 40, 48), (5, 1000, 96), (130, 72, 200), (64, 64, 64), (67, 129, 33)])
+def test_linear(ks, M, N, K):
+    x, w = rnd((M, K), ks.dtype, 4), rnd((N, K), ks.dtype, 5, 0.2)
+    r = ref_set(ks.dtype)
+    out = torch.empty((M, N), dtype=ks.dtype, device=DEV)
+    ks.linear(x.to(DEV), w.to(DEV), out)
+    ref = torch.empty((M, N), dtype=torch.float64)
+    r.linear(x, w, ref)
+    close(out, ref, TOL[ks.dtype], "linear")
+    # float32 output (logits) and accumulation into the residual stream with a row scale
+    out32 = torch.empty((M, N), dtype=torch.float32, device=DEV)
+    ks.linear(x.to(DEV), w.to(DEV), out32)
+    close(out32, ref, 1e-5 if ks.dtype == torch.float32 else 1e-5 * K, "linear f32 out")
+    h = rnd((M, N), torch.float32, 6)
+    scale = rnd((M,), torch.float32, 7)
+    hd = h.to(DEV).clone()
+    ks.linear(x.to(DEV), w.to(DEV), hd, accumulate=True, row_scale=scale.to(DEV))
+    ref_h = h.double().clone()
+    r.linear(x, w, ref_h, accumulate=True, row_scale=scale)
+    close(hd, ref_h, 2e-5, "linear accumulate")
+
+
+@pytest.mark.parametrize("M,F,K", [(3, 24, 48), (70, 100, 96)])
+def test_linear_swiglu(ks, M, F, K):
+    x, w = rnd((M, K), ks.dtype, 8), rnd((2 * F, K), ks.dtype, 9, 0.3)
+    scale = torch.rand(M) + 0.5
+    out = torch.empty((M, F), dtype=ks.dtype, device=DEV)
+    ks.linear_swiglu(x.to(DEV), w.to(DEV), out, row_scale=scale.to(DEV))
+    ref = torch.empty((M, F), dtype=torch.float64)
+    ref_set(ks.dtype).linear_swiglu(x, w, ref, row_scale=scale)
+    close(out, ref, TOL[ks.dtype], "linear_swiglu")
+
+
+@pytest.mark.parametrize("M,E,F,K", [(1, 3, 24, 48), (9, 5, 40, 96), (150, 7, 72, 64)])
+def test_grouped_products(ks, M, E, F, K):
+    """Tokens sorted by expert, some experts empty; SwiGLU in, scatter-add out."""
+    g = torch.Generator().manual_seed(10)
+    ids = torch.randint(0, E, (M,), generator=g)
+    ids[ids == 1] = 0                                   # expert 1 stays empty
+    order = torch.sort(ids, stable=True)
+    rows = order.indices.to(torch.int32)
+    offsets = torch.zeros(E + 1, dtype=torch.int32)
+    offsets[1:] = torch.cumsum(torch.bincount(ids, minlength=E), 0)
+    x = rnd((M, K), ks.dtype, 11)
+    w_gu, w_d = rnd((E, 2 * F, K), ks.dtype, 12, 0.3), rnd((E, K, F), ks.dtype, 13, 0.3)
+    scale = torch.rand(M, generator=g) + 0.5
+    r = ref_set(ks.dtype)
+    a = torch.zeros((M, F), dtype=ks.dtype, device=DEV)
+    ks.grouped_linear_swiglu(x.to(DEV), w_gu.to(DEV), rows.to(DEV), offsets.to(DEV), scale.to(DEV), a)
+    a_ref = torch.zeros((M, F), dtype=torch.float64)
+    r.grouped_linear_swiglu(x, w_gu, rows, offsets, scale, a_ref)
+    close(a, a_ref, TOL[ks.dtype], "grouped_linear_swiglu")
+    h = rnd((M, K), torch.float32, 14)
+    hd = h.to(DEV).clone()
+    ks.grouped_linear_accumulate(a, w_d.to(DEV), rows.to(DEV), offsets.to(DEV), hd)
+    h_ref = h.double().clone()
+    r.grouped_linear_accumulate(a.cpu(), w_d, rows, offsets, h_ref)
+    close(hd, h_ref, 2e-5 if ks.dtype == torch.float32 else 2e-3, "grouped_linear_accumulate")
+
+
+# ---------------------------------------------------------------------------- attention
+def make_batch(seg_specs, page_size, n_pages, seed, device):
+    """seg_specs: [(start_pos, n_tokens)]; pages are dealt out of order."""
+    g = torch.Generator().manual_seed(seed)
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    segs, tables, toks, off = [], [], [], 0
+    for s, (start, n) in enumerate(seg_specs):
+        n_pg = -(-(start + n) // page_size)
+        tables.append([perm.pop() for _ in range(n_pg)])
+        segs.append(Segment(s, s, start, n, off, start == 0))
+        toks.append([0] * n)
+        off += n
+    return build_step_batch(segs, toks, [[] for _ in segs], [tables], device), tables
+
+
+def fill_cache(kv, tables, seg_specs, k_all, v_all, page_size):
+    """Write keys/values of positions [0, start) of every segment (the earlier steps)."""
+    for s, (start, n) in enumerate(seg_specs):
+        for p in range(start):
+            page = tables[s][p // page_size]
+            kv[0, page, :, p % page_size, :] = k_all[s][p]
+            kv[1, page, :, p % page_size, :] = v_all[s][p]
+
+
+@pytest.mark.parametrize("nq,nkv,hd,rope,norm,temp", [
+    (4, 2, 16, True, True, False), (6, 1, 32, True, False, False), (5, 5, 48, False, False, True),
+    (40, 8, 128, True, True, False), (3, 1, 256, False, False, False)])
+def test_qk_prepare(ks, nq, nkv, hd, rope, norm, temp):
+    P, n_pages = 16, 12
+    specs = [(0, 19), (30, 1), (15, 3)]
+    batch, tables = make_batch(specs, P, n_pages, 20, DEV)
+    cpu_batch, _ = make_batch(specs, P, n_pages, 20, "cpu")
+    M = batch.n_tokens
+    qkv = rnd((M, (nq + 2 * nkv) * hd), ks.dtype, 21)
+    inv_freq = torch.tensor([10000.0 ** (-2.0 * i / hd) for i in range(hd // 2)], dtype=torch.float32) if rope else None
+    args = dict(num_heads=nq, inv_freq=None, qk_norm_eps=1e-5 if norm else None,
+                temperature=(8, 0.25) if temp else None)
+    kv = torch.zeros((2, n_pages, nkv, P, hd), dtype=ks.dtype, device=DEV)
+    q = torch.empty((M, nq * hd), dtype=ks.dtype, device=DEV)
+    ks.qk_prepare(qkv.to(DEV), q, batch, LayerCache(0, kv, None, P, True),
+                  **dict(args, inv_freq=None if inv_freq is None else inv_freq.to(DEV)))
+    kv_ref = torch.zeros((2, n_pages, nkv, P, hd), dtype=torch.float64)
+    q_ref = torch.empty((M, nq * hd), dtype=torch.float64)
+    ref_set(ks.dtype).qk_prepare(qkv, q_ref, cpu_batch, LayerCache(0, kv_ref, None, P, True),
+                                 **dict(args, inv_freq=inv_freq))
+    close(q, q_ref, TOL[ks.dtype], "q")
+    close(kv, kv_ref, TOL[ks.dtype], "cache")
+    # a run that only reads the cache writes nothing
+    kv2 = torch.zeros_like(kv)
+    ks.qk_prepare(qkv.to(DEV), q, batch, LayerCache(0, kv2, None, P, False),
+                  **dict(args, inv_freq=None if inv_freq is None else inv_freq.to(DEV)))
+    assert not kv2.any()
+
+
+@pytest.mark.parametrize("nq,nkv,hd,window,P", [
+    (4, 2, 16, ("full", 0), 16), (6, 1, 32, ("chunk", 16), 16), (5, 5, 48, ("chunk", 40), 16),
+    (40, 8, 128, ("full", 0), 64), (10, 2, 128, ("chunk", 96), 64), (3, 1, 256, ("sliding", 37), 16),
+    (8, 2, 64, ("full", 0), 16)])
+def test_paged_attention(ks, nq, nkv, hd, window, P):
+    """Segments of different kinds in one call: a long prompt portion that crosses
+    window and page edges, single tokens deep in a context, a first token."""
+    win = Window(*window)
+    specs = [(0, 70), (300, 1), (95, 34), (0, 1), (63, 2)]
+    n_pages = sum(-(-(s + n) // P) for s, n in specs) + 3
+    batch, tables = make_batch(specs, P, n_pages, 30, DEV)
+    cpu_batch, _ = make_batch(specs, P, n_pages, 30, "cpu")
+    M = batch.n_tokens
+    g = torch.Generator().manual_seed(31)
+    k_all = [torch.randn((s + n, nkv, hd), generator=g) for s, n in specs]
+    v_all = [torch.randn((s + n, nkv, hd), generator=g) for s, n in specs]
+    q = torch.randn((M, nq, hd), generator=g)
+    # one far key carries the attention of the deep single token: its query is aligned with it
+    far = 7 if win.kind == "full" else win.lowest_visible(300) + 1
+    q[70] = 0.0
+    q[70, :, :] = k_all[1][far, 0, :] * (16.0 / math.sqrt(hd))
+    kv_ref = torch.zeros((2, n_pages, nkv, P, hd), dtype=ks.dtype)
+    fill = [(s + n, 0) for s, n in specs]                 # all keys of the step are cached before it runs
+    fill_cache(kv_ref, tables, fill, [k.to(ks.dtype) for k in k_all], [v.to(ks.dtype) for v in v_all], P)
+    qd = q.reshape(M, nq * hd).to(ks.dtype)
+    out = torch.empty((M, nq * hd), dtype=ks.dtype, device=DEV)
+    scale = 1.0 / math.sqrt(hd)
+    ks.paged_attention(qd.to(DEV), out, batch, LayerCache(0, kv_ref.to(DEV), None, P, False),
+                       num_heads=nq, window=win, softmax_scale=scale)
+    ref = torch.empty((M, nq * hd), dtype=torch.float64)
+    ref_set(ks.dtype).paged_attention(qd, ref, cpu_batch, LayerCache(0, kv_ref, None, P, False),
+                                      num_heads=nq, window=win, softmax_scale=scale)
+    close(out, ref, TOL[ks.dtype], f"attention {window}")
+    # the far key must dominate row 70 of head 0, else the test would not see a lost key
+    w_far = torch.softmax((k_all[1][win.lowest_visible(300):301, 0].to(ks.dtype).double()
+                           @ qd[70, :hd].double()) * scale, 0)
+    assert float(w_far[far - win.lowest_visible(300)]) > 0.5
+
+
+# ---------------------------------------------------------------------------- router
+@pytest.mark.parametrize("M,d,E,k", [(1, 48, 3, 1), (37, 96, 8, 1), (200, 200, 16, 2), (5, 64, 128, 4)])
+def test_moe_route(ks, M, d, E, k):
+    x = rnd((M, d), ks.dtype, 40)
+    w = rnd((E, d), torch.float32, 41, 0.3)
+    if E >= 3:
+        w[2] = w[0]                                      # equal logits: the lower expert id wins
+    got = ks.moe_route(x.to(DEV), w.to(DEV), k, want_logits=True)
+    ref = ref_set(ks.dtype).moe_route(x, w, k, want_logits=True)
+    close(got.logits, ref.logits, 1e-5, "router logits")
+    # compare choices where float32 rounding cannot change the order
+    srt = torch.sort(ref.logits.double(), dim=-1, descending=True).values
+    clear = ((srt[:, :-1] - srt[:, 1:])[:, :k].min(dim=1).values > 1e-4) if E > 1 else torch.ones(M, dtype=torch.bool)
+    ties = (ref.expert_ids.T.long() == 0).any(1) | (ref.expert_ids.T.long() == 2).any(1)
+    keep = clear | ties
+    assert torch.equal(got.expert_ids.cpu().T[keep], ref.expert_ids.T[keep])
+    assert not (got.expert_ids.cpu() == 2).any() or k > 1
+    close(got.weights, ref.weights, 1e-5, "router weights")
+    for s in range(k):
+        ids = got.expert_ids[s].cpu().long()
+        order = torch.sort(ids, stable=True)
+        assert torch.equal(got.sorted_rows[s].cpu().long(), order.indices)
+        assert got.offsets[s].cpu().tolist() == [0] + torch.cumsum(torch.bincount(ids, minlength=E), 0).tolist()
+
+
+# ---------------------------------------------------------------------------- sampling
+def test_argmax_prefers_the_highest_index(ks):
+    if ks.dtype != torch.float32:
+        pytest.skip("logits are float32 in both sets")
+    V = 1000
+    l = rnd((6, V), torch.float32, 50)
+    l[0, 17] = l[0, 600] = 9.0
+    l[1, V - 1] = 9.0
+    l[2, 0] = 9.0
+    l[3] = 0.0
+    got = ks.argmax(l.to(DEV)).cpu()
+    ref = ref_set(torch.float32).argmax(l)
+    assert got.tolist() == ref.tolist()
+    assert got[0] == 600 and got[1] == V - 1 and got[2] == 0 and got[3] == V - 1
+
+
+@pytest.mark.parametrize("V", [512, 1000, 202048])
+def test_sample_matches_the_plain_sampler(ks, V):
+    if ks.dtype != torch.float32:
+        pytest.skip("logits are float32 in both sets")
+    from plain_llama4 import lcg_next, process_logits_plain, sample_plain
+    R = 8
+    l = rnd((R, V), torch.float32, 51, 2.0)
+    cases = [dict(temperature=0.0), dict(temperature=0.7), dict(temperature=1.0, top_k=5),
+             dict(temperature=0.9, top_p=0.8), dict(temperature=1.3, min_p=0.05),
+             dict(temperature=0.8, repetition_penalty=1.3), dict(temperature=0.0, repetition_penalty=1.5),
+             dict(temperature=1.0, top_k=40, top_p=0.95, min_p=0.01, repetition_penalty=1.1)]
+    ctx = [torch.randint(0, V, (20,)).tolist() for _ in range(R)]
+    for r in range(R):
+        ctx[r][0] = int(l[r].argmax())                  # the penalty hits the likeliest token
+    state = torch.tensor([1234 + r for r in range(R)], dtype=torch.int64)
+    f = lambda key, d, dt: torch.tensor([c.get(key, d) for c in cases], dtype=dt, device=DEV)
+    offsets = torch.tensor([20 * r for r in range(R + 1)], dtype=torch.int32, device=DEV)
+    context = torch.tensor(sum(ctx, []), dtype=torch.int32, device=DEV)
+    for draw in range(3):
+        dev_state = state.clone().to(DEV)
+        got = ks.sample(l.to(DEV), temperature=f("temperature", 0.0, torch.float32),
+                        top_k=f("top_k", 0, torch.int32), top_p=f("top_p", 1.0, torch.float32),
+                        min_p=f("min_p", 0.0, torch.float32),
+                        repetition_penalty=f("repetition_penalty", 1.0, torch.float32),
+                        context=context, context_offsets=offsets, rng_state=dev_state).cpu().tolist()
+        new_state = []
+        for r, c in enumerate(cases):
+            tok, st = sample_plain(l[r], ctx[r], repeat_last_n=0, state=int(state[r]), **c)
+            new_state.append(st)
+            if got[r] == tok:
+                continue
+            # float32 running sums in another order may cross the target one token earlier or
+            # later; the drawn token must still be the one whose mass interval holds the target
+            assert c["temperature"] > 0, f"case {c}: device {got[r]}, plain {tok}"
+            proc = process_logits_plain(l[r], ctx[r], repeat_last_n=0, **c).double()
+            mass = torch.exp(proc - proc.max())
+            cum = torch.cumsum(mass, 0)
+            target = lcg_next(int(state[r]) & ((1 << 64) - 1))[1] * float(mass.sum())
+            slack = 2e-5 * float(mass.sum())
+            lo = float(cum[got[r] - 1]) if got[r] > 0 else 0.0
+            assert mass[got[r]] > 0 and lo - slack <= target <= float(cum[got[r]]) + slack, \
+                f"draw {draw}, case {c}: device {got[r]}, plain {tok}"
+        back = [int(s) & ((1 << 64) - 1) for s in dev_state.cpu().tolist()]
+        assert back == new_state
+        state = torch.tensor([s - (1 << 64) if s >= (1 << 63) else s for s in new_state], dtype=torch.int64)
