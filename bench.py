@@ -1,0 +1,299 @@
+"""Measurement: decode tokens per second of a Llama-4-Scout-shaped model with
+random bfloat16 weights on one B200, plus prefill of 2,048 tokens, the decode
+step's HBM roofline fraction, and decoding at batch 1 and 64.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+A "step" is one decode step of the whole batch.  Prints one JSON line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# Llama-4-Scout layer shapes, 16 layers (the benchmark configuration)
+SCOUT = dict(
+    architectures=["Llama4ForCausalLM"], num_hidden_layers=16, hidden_size=5120, num_attention_heads=40,
+    num_key_value_heads=8, head_dim=128, interleave_moe_layer_step=1, num_local_experts=16,
+    num_experts_per_tok=1, intermediate_size=8192, intermediate_size_mlp=16384, vocab_size=202048,
+    tie_word_embeddings=False, rope_theta=500000.0,
+    rope_scaling=dict(rope_type="llama3", factor=16.0, low_freq_factor=1.0, high_freq_factor=1.0,
+                      original_max_position_embeddings=8192),
+    attention_chunk_size=8192, no_rope_layer_interval=4, use_qk_norm=True, attn_temperature_tuning=True,
+    floor_scale=8192, attn_scale=0.1, rms_norm_eps=1e-5, max_position_embeddings=131072)
+FULL_LAYERS = 16
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    out, src = dict(FALLBACK_PEAKS), "fallback"
+    if os.path.isfile(path):
+        try:
+            raw = json.load(open(path))
+            for k in out:
+                if isinstance(raw.get(k), (int, float)) and raw[k] > 0:
+                    out[k] = float(raw[k])
+            src = "measured"
+        except (OSError, ValueError):
+            pass
+    return out, src
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.rows, self.proc = [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc:
+            time.sleep(0.25)
+            self.proc.terminate()
+
+    def summary(self):
+        mhz = sorted(int(r[0]) for r in self.rows if r and r[0].isdigit())
+        mx = [int(r[1]) for r in self.rows if len(r) > 1 and r[1].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) > 2 + i and r[2 + i] == "Active" for r in self.rows)]
+        return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(mhz)}
+
+
+def decode_bytes(model, engine, contexts, distinct_experts):
+    """Bytes a decode step has to read: every weight it uses once and the cache of the
+    live requests (each layer reads the keys and values its window lets it see)."""
+    from spite_b200.parts.feedforward import MoESigmoidPrescaled
+    es = 2
+    p = model.plan
+    total = p.vocab_size * p.hidden_size * es                       # output head (embedding rows are negligible)
+    for i, blk in enumerate(model.blocks):
+        total += blk.mixer.weight_bytes() + blk.mixer_norm.weight_bytes() + blk.ffn_norm.weight_bytes()
+        if isinstance(blk.ffn, MoESigmoidPrescaled):
+            total += blk.ffn.active_weight_bytes(distinct_experts[i])
+        else:
+            total += blk.ffn.weight_bytes()
+        win = blk.mixer.window
+        for ctx in contexts:
+            seen = ctx - win.lowest_visible(ctx - 1)
+            total += seen * 2 * blk.mixer.nkv * blk.mixer.hd * es
+    return total
+
+
+def prefill_flops(cfg, T):
+    d, hd, nq, nkv = cfg["hidden_size"], cfg["head_dim"], cfg["num_attention_heads"], cfg["num_key_value_heads"]
+    f = cfg["intermediate_size"]
+    per_layer = 2 * T * d * (nq + 2 * nkv) * hd + 2 * T * nq * hd * d        # projections
+    per_layer += 2 * T * d * cfg["num_local_experts"]                          # router
+    per_layer += 2 * (2 * T * d * 3 * f)                                       # routed + shared expert
+    per_layer += 2 * 2 * nq * hd * T * (T + 1) // 2                            # causal attention
+    return cfg["num_hidden_layers"] * per_layer + 2 * d * cfg["vocab_size"]    # one logits row
+
+
+def run_ours(args):
+    import torch
+    from spite_b200.config import Llama4Config
+    from spite_b200.engine import Engine, Model, StepEntry
+    from spite_b200.engine.scheduler import Request, Scheduler
+    from spite_b200.kernels import build as kb
+    from spite_b200.sampling import Sampler, SamplingParams
+
+    torch.cuda.set_device(0)
+    dev = "cuda:0"
+    cfgd = dict(SCOUT, num_hidden_layers=args.layers)
+    cfg = Llama4Config.from_dict(cfgd)
+    model = Model.from_config(cfg, dtype="bfloat16", device=dev)
+    kb.ensure_built(model.kernel_libraries() + ["sampling"])
+    model.init_random(seed=0, std=0.02)
+    ks = model.kernels
+    B, ctx = args.batch, args.context
+    page = 64
+    max_b = max(B, 64 if not args.skip_points else B)
+    engine = Engine(model, cache_tokens=max_b * (ctx + page), page_size=page, max_requests=max_b,
+                    max_positions=ctx + page)
+    for kv in engine.storage.kv:                       # a cache as earlier steps would have left it
+        kv.normal_(0.0, 1.0)
+    g = torch.Generator().manual_seed(1)
+    vocab = cfg.vocab_size
+
+    def occupy(n_req, n_cached):
+        for r in list(engine.cache.requests):
+            engine.finish(r)
+        for r in range(n_req):
+            engine.cache.admit(r)
+            engine.cache.reserve(r, n_cached)
+            engine.cache.commit(r)
+
+    def timed_decode(n_req, steps, warmup, clocks=None):
+        start_ctx = ctx - (steps + warmup) - 1
+        occupy(n_req, start_ctx)
+        toks = torch.randint(0, vocab, (steps + warmup, n_req), generator=g).tolist()
+        ids = None
+        for i in range(warmup):
+            ids = ks.argmax(engine.step([StepEntry(r, [toks[i][r]], [0]) for r in range(n_req)]))
+        torch.cuda.synchronize()
+        l0 = ks.launches
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ctxm = clocks if clocks is not None else _Null()
+        with ctxm:
+            e0.record()
+            for i in range(warmup, warmup + steps):
+                ids = ks.argmax(engine.step([StepEntry(r, [toks[i][r]], [0]) for r in range(n_req)]))
+            e1.record()
+            torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        return ms / steps, ks.launches - l0, ids
+
+    pk, pk_src = peaks()
+    clocks = ClockSampler()
+    ms_step, launches, _ = timed_decode(B, args.steps, args.warmup, clocks)
+    value = B * 1000.0 / ms_step
+    # experts the batch's tokens use, layer by layer, in the last step
+    distinct = []
+    for blk in model.blocks:
+        r = getattr(blk.ffn, "last_routing", None)
+        distinct.append(int(torch.unique(r.expert_ids).numel()) if r is not None else 0)
+    end_ctx = ctx - 1
+    nbytes = decode_bytes(model, engine, [end_ctx] * B, distinct)
+    achieved = nbytes / (ms_step * 1e-3) / 1e9
+
+    # end to end through the scheduler: host tokens in (pinned copy), sampled tokens out
+    sched = Scheduler(engine, Sampler(ks), max_batch_tokens=4096, ctx=ctx + page)
+    occupy(B, ctx - (args.steps + args.warmup) - 2)
+    prompt_tail = torch.randint(0, vocab, (B,), generator=g).tolist()
+    for r in range(B):
+        req = Request(r, [0] * engine.cached_tokens(r) + [prompt_tail[r]],
+                      SamplingParams(temperature=0.0, max_tokens=args.steps + args.warmup + 1))
+        req.n_fed = engine.cached_tokens(r)
+        req.state = req.state.__class__.PREFILLING
+        req.rng_state = 0
+        sched.running.append(req)
+    for _ in range(args.warmup + 1):
+        sched.step()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    n_tok = 0
+    for _ in range(args.steps - 1):
+        n_tok += sum(1 for o in sched.step() if o.token is not None)
+    e1.record()
+    torch.cuda.synchronize()
+    e2e_ms = max(e0.elapsed_time(e1), (time.perf_counter() - t0) * 1e3)
+    e2e = n_tok * 1000.0 / e2e_ms if e2e_ms > 0 else 0.0
+    table_w = -(-(ctx + page) // page)
+    h2d = 4 * (3 * B + (B + 1) + B + B + 2 * B * table_w)
+    for r in list(engine.cache.requests):
+        engine.finish(r)
+
+    # prefill of 2,048 tokens, logits of the last row
+    T = 2048
+    ptoks = torch.randint(0, vocab, (T,), generator=g).tolist()
+    pre_ms = []
+    for i in range(3):
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        engine.step([StepEntry("p", ptoks, [T - 1])])
+        e1.record()
+        torch.cuda.synchronize()
+        engine.finish("p")
+        pre_ms.append(e0.elapsed_time(e1))
+    pms = min(pre_ms[1:])
+    pflops = prefill_flops(cfgd, T)
+    prefill = {"value": round(T * 1000.0 / pms, 1), "tokens": T, "ms": round(pms, 3),
+               "frac": round(pflops / (pms * 1e-3) / (pk["bf16_tflops_sustained"] * 1e12), 4)}
+
+    points = {}
+    if not args.skip_points:
+        for nb in (1, 64):
+            ms_b, _, _ = timed_decode(nb, max(4, args.steps // 2), 3)
+            points[f"decode_b{nb}"] = round(nb * 1000.0 / ms_b, 1)
+
+    line = {
+        "metric": "decode tok/s (Llama-4-Scout-shaped, batch 8, context 8192)",
+        "value": round(value, 2), "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic (random token ids, random weights N(0,0.02))",
+        "config": {"model": "llama4-scout-shaped", "layers": args.layers, "layers_full": FULL_LAYERS,
+                   "hidden": 5120, "q_heads": 40, "kv_heads": 8, "head_dim": 128, "experts": 16, "top_k": 1,
+                   "expert_ffn": 8192, "shared_ffn": 8192, "vocab": 202048, "chunk": 8192, "nope_every": 4,
+                   "global_batch": B, "seq_len": ctx, "page_size": page, "parallelism": "single-gpu",
+                   "l2": "inputs larger than L2 (weights read per step exceed 126 MB)",
+                   "cache": "random-filled to context"},
+        "e2e": {"value": round(e2e, 2), "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * B},
+        "gpu_launches": launches,
+        "clocks": clocks.summary(),
+        "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4), "bytes_per_step": nbytes, "peaks": pk_src},
+        "points": points,
+    }
+    print(json.dumps(line))
+
+
+class _Null:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        return False
+
+
+def run_reference(args):
+    # giveen/spite is a Rust workspace (Cargo.toml, no pyproject/setup.py): pip cannot install it, the
+    # image has no cargo/rustc, and its Llama 4 path has no GPU kernel to run.
+    print(json.dumps({"impl": "reference",
+                      "unavailable": "giveen/spite is a Rust workspace without a Python package; "
+                                     "no cargo/rustc offline, and its Llama 4 path is CPU-only"}))
+    return 0
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=16)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--layers", type=int, default=FULL_LAYERS)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=8192)
+    ap.add_argument("--skip-points", action="store_true")
+    args = ap.parse_args(argv)
+    if args.impl == "reference":
+        return run_reference(args)
+    if args.gpus != 1:
+        print(f"bench.py measures one GPU; --gpus {args.gpus} is not supported by this engine")
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+    run_ours(args)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -108,6 +108,9 @@ class Scheduler:
             raise ContextOverflow(f"request {request.id!r}: its prompt needs {need} pages, the pool has "
                                   f"{min(p.n_pages for p in cache.pools)}")
         request.rng_state = request.params.seed & ((1 << 64) - 1)
+        if request.params.max_tokens == 0:
+            self._finish(request, FinishReason.MAX_TOKENS)
+            return
         request.state = RequestState.WAITING
         self.waiting.append(request)
 

@@ -76,6 +76,7 @@ class CudaKernels(KernelSet):
         self.device = torch.device(device)
         self._dt = _DT[dtype]
         self._libs = {}
+        self.launches = 0          # kernels launched so far (for measurement reports)
 
     # ------------------------------------------------------------------ helpers
     def _lib(self, name):
@@ -103,6 +104,7 @@ class CudaKernels(KernelSet):
         st = self._lib("elementwise").spite_embed(
             self._dt, C.c_void_p(table.data_ptr()), C.c_void_p(token_ids.data_ptr()),
             C.c_void_p(out_h.data_ptr()), token_ids.numel(), d, V, self._stream())
+        self.launches += 1
         _check(st, "embed")
 
     def rms_norm(self, h, gain, eps, out, rows=None):
@@ -113,11 +115,13 @@ class CudaKernels(KernelSet):
         st = self._lib("elementwise").spite_rms_norm(
             _DT[out.dtype], C.c_void_p(h.data_ptr()), C.c_void_p(gain.data_ptr()),
             C.c_void_p(_ptr(rows)), C.c_void_p(out.data_ptr()), n, d, C.c_float(eps), self._stream())
+        self.launches += 1
         _check(st, "rms_norm")
 
     # ------------------------------------------------------------------ matrix products
     def _gemm(self, p: GemmParams, what):
         st = self._lib("gemm_simt").spite_gemm_simt(self._dt, C.byref(p), self._stream())
+        self.launches += 1
         _check(st, what)
 
     def linear(self, x, w, out, *, accumulate=False, row_scale=None):
@@ -200,6 +204,7 @@ class CudaKernels(KernelSet):
                             temperature_scale=scale, num_heads=num_heads, write_cache=int(cache.write))
         b, c = self._step_tokens(batch, cache.group), self._paged(cache)
         st = self._lib("attention").spite_qk_prepare(self._dt, C.byref(p), C.byref(b), C.byref(c), self._stream())
+        self.launches += 1
         _check(st, "qk_prepare")
 
     def paged_attention(self, q, out, batch, cache, *, num_heads, window, softmax_scale):
@@ -210,6 +215,7 @@ class CudaKernels(KernelSet):
         b, c = self._step_tokens(batch, cache.group), self._paged(cache)
         st = self._lib("attention").spite_paged_attention(self._dt, C.byref(p), C.byref(b), C.byref(c),
                                                           self._stream())
+        self.launches += 1
         _check(st, "paged_attention")
 
     # ------------------------------------------------------------------ mixture of experts
@@ -227,6 +233,8 @@ class CudaKernels(KernelSet):
             self._dt, C.c_void_p(x.data_ptr()), C.c_void_p(w_router.data_ptr()), M, d, E, top_k,
             C.c_void_p(ids.data_ptr()), C.c_void_p(wts.data_ptr()), C.c_void_p(_ptr(logits)),
             C.c_void_p(offsets.data_ptr()), C.c_void_p(rows.data_ptr()), self._stream())
+        self.launches += 1
+        self.launches += 1
         _check(st, "moe_route")
         return Routing(ids, wts, offsets, rows, logits)
 
@@ -237,6 +245,7 @@ class CudaKernels(KernelSet):
         out = torch.empty(R, dtype=torch.int32, device=logits.device)
         st = self._lib("sampling").spite_argmax(C.c_void_p(logits.data_ptr()), R, V,
                                                 C.c_void_p(out.data_ptr()), self._stream())
+        self.launches += 1
         _check(st, "argmax")
         return out
 
@@ -253,5 +262,6 @@ class CudaKernels(KernelSet):
                          context_offsets=_ptr(context_offsets), rng_state=rng_state.data_ptr(),
                          out_tokens=out.data_ptr(), vocab=V)
         st = self._lib("sampling").spite_sample(C.byref(p), R, self._stream())
+        self.launches += 1
         _check(st, "sample")
         return out

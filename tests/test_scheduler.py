@@ -1,0 +1,177 @@
+"""The scheduler's decisions: admission, portions under the token budget, decoding,
+finishing and freeing, and what happens when pages run out.  The step function
+below it is the product's, with the kernels replaced by their plain torch
+restatements so that the test runs without a GPU."""
+import pytest
+import torch
+
+import helpers as H
+import plain_llama4 as plain
+from reference_kernels import TorchReferenceKernels
+from spite_b200.engine import ContextOverflow, Engine, Model
+from spite_b200.engine.scheduler import FinishReason, Request, RequestState, Scheduler
+from spite_b200.sampling import Sampler, SamplingParams
+
+
+@pytest.fixture(scope="module")
+def model(tmp_path_factory):
+    folder = H.write_model(tmp_path_factory.mktemp("modelA"), "A")
+    m = Model.from_folder(folder, dtype="float32", device="cpu", kernels=TorchReferenceKernels())
+    m.folder = folder
+    return m
+
+
+def make(model, *, cache_tokens=512, page_size=16, max_requests=4, **kw):
+    eng = Engine(model, cache_tokens=cache_tokens, page_size=page_size, max_requests=max_requests)
+    return Scheduler(eng, Sampler(model.kernels), **kw)
+
+
+def greedy(n=8, **kw):
+    return SamplingParams(temperature=0.0, max_tokens=n, **kw)
+
+
+def plain_greedy(model, prompt, n):
+    cfg, tensors = H._folder_contents(str(model.folder))
+    return plain.generate_greedy(cfg, tensors, prompt, n)
+
+
+PROMPTS = [H.random_tokens(512, n, s) for s, n in enumerate((48, 5, 20, 33))]
+
+
+def test_portions_follow_the_token_budget_and_decodes_come_first(model):
+    s = make(model, max_batch_tokens=16)
+    s.submit(Request("a", PROMPTS[0], greedy(4)))
+    s.submit(Request("b", PROMPTS[1], greedy(4)))
+    plan = s.plan_step()
+    assert [(r.id, len(t), w) for r, t, w in plan.entries] == [("a", 16, False)]
+    s = make(model, max_batch_tokens=16)
+    s.submit(Request("a", PROMPTS[0], greedy(4)))
+    s.submit(Request("b", PROMPTS[1], greedy(4)))
+    sizes = []
+    for _ in range(6):
+        plan_sizes = None
+        outs = s.step()
+        sizes.append(s.counters["tokens"])
+    # 48-token prompt in portions of 16; the 5-token prompt joins the step in which budget is left
+    assert sizes[:3] == [16, 32, 48]
+    assert s.finished == {} or all(r.state is RequestState.DONE for r in s.finished.values())
+    s.run_until_done()
+    assert s.finished["a"].output == plain_greedy(model, PROMPTS[0], 4)
+    assert s.finished["b"].output == plain_greedy(model, PROMPTS[1], 4)
+    assert s.engine.cache.free_pages() == [s.engine.n_pages] * 2 and s.engine.cache.slots.n_free == 4
+
+
+def test_mixed_step_has_decodes_beside_a_portion(model):
+    s = make(model, max_batch_tokens=12)
+    s.submit(Request("b", PROMPTS[1], greedy(6)))
+    s.step()                                              # b's whole prompt, first token sampled
+    s.submit(Request("a", PROMPTS[0], greedy(2)))
+    plan = s.plan_step()
+    assert [(r.id, len(t), w) for r, t, w in plan.entries] == [("b", 1, True), ("a", 11, False)]
+
+
+@pytest.mark.parametrize("budget,pages,order", [(2048, 512, (0, 1, 2, 3)), (7, 512, (3, 2, 1, 0)),
+                                                (24, 160, (1, 3, 0, 2)), (2, 128, (0, 1, 2, 3))])
+def test_outputs_do_not_depend_on_budget_pool_or_arrival(model, budget, pages, order):
+    s = make(model, max_batch_tokens=budget, cache_tokens=pages, max_requests=3)
+    for i in order:
+        s.submit(Request(i, PROMPTS[i], greedy(6)))
+    done = s.run_until_done()
+    for i in order:
+        assert done[i].output == plain_greedy(model, PROMPTS[i], 6), i
+        assert done[i].finish_reason is FinishReason.MAX_TOKENS
+    s.engine.cache.check_invariants()
+    assert s.engine.cache.free_pages() == [s.engine.n_pages] * 2
+
+
+def test_running_out_of_pages_preempts_the_latest_admitted(model):
+    # 6 pages of 16: a (48 tokens) takes 3... both decode until a page is missing
+    s = make(model, max_batch_tokens=64, cache_tokens=96, page_size=16)
+    s.submit(Request("a", PROMPTS[0][:44], greedy(12)))
+    s.submit(Request("c", PROMPTS[2] + PROMPTS[1], greedy(12)))     # 25 tokens
+    preempted = []
+    while s.active_count():
+        before = s.counters["preemptions"]
+        s.step()
+        if s.counters["preemptions"] > before:
+            preempted.append([r.id for r in s.waiting])
+        s.engine.cache.check_invariants()
+    assert s.counters["preemptions"] >= 1
+    assert preempted[0] == ["c"]                                    # the most recently admitted one
+    assert s.finished["c"].preemptions >= 1 and s.finished["a"].preemptions == 0
+    assert s.finished["a"].output == plain_greedy(model, PROMPTS[0][:44], 12)
+    assert s.finished["c"].output == plain_greedy(model, PROMPTS[2] + PROMPTS[1], 12)
+    assert s.engine.cache.free_pages() == [6, 6]
+
+
+def test_a_lone_request_that_fills_the_cache_ends(model):
+    s = make(model, cache_tokens=32, page_size=16)
+    s.submit(Request("a", PROMPTS[2], greedy(40)))                   # 20 tokens, room for 32
+    done = s.run_until_done()
+    r = done["a"]
+    assert r.finish_reason is FinishReason.CACHE_FULL
+    assert len(PROMPTS[2]) + len(r.output) == 33                     # 32 cached + the token not yet fed
+    assert r.output == plain_greedy(model, PROMPTS[2], len(r.output))
+    assert s.engine.cache.free_pages() == [2, 2]
+    with pytest.raises(ContextOverflow):
+        s.submit(Request("big", PROMPTS[0], greedy(1)))              # 48 tokens can never fit 2 pages
+
+
+def test_finish_reasons(model):
+    ref = plain_greedy(model, PROMPTS[1], 6)
+    s = make(model, eos_token_ids=[ref[3]])
+    s.submit(Request("e", PROMPTS[1], greedy(6)))
+    s.submit(Request("s", PROMPTS[1], greedy(6, stop_token_ids=(ref[2],))))
+    s.submit(Request("z", PROMPTS[1], greedy(0)))
+    outs = []
+    while s.active_count():
+        outs += s.step()
+    first = ref.index(ref[3])
+    assert s.finished["e"].output == ref[:first] and s.finished["e"].finish_reason is FinishReason.EOS_TOKEN
+    assert s.finished["s"].finish_reason in (FinishReason.STOP_TOKEN, FinishReason.EOS_TOKEN)
+    assert s.finished["s"].output == ref[:min(ref.index(ref[2]), first)]
+    assert s.finished["z"].output == [] and s.finished["z"].finish_reason is FinishReason.MAX_TOKENS
+    ended = [o for o in outs if o.done and o.request_id == "e"]
+    assert len(ended) == 1 and ended[0].token is None                # the end token is not emitted
+    s = make(model, ctx=8)
+    s.submit(Request("c", PROMPTS[1], greedy(50)))
+    s.run_until_done()
+    assert s.finished["c"].finish_reason is FinishReason.CONTEXT_FULL and len(s.finished["c"].output) == 3
+    with pytest.raises(ContextOverflow):
+        s.submit(Request("x", PROMPTS[0], greedy(1)))
+    with pytest.raises(ValueError):
+        s.submit(Request("y", [], greedy(1)))
+
+
+def test_sampling_is_reproducible_and_independent_of_batching(model):
+    def run(ids, budget):
+        s = make(model, max_batch_tokens=budget)
+        for i in ids:
+            s.submit(Request(i, PROMPTS[i], SamplingParams(temperature=0.7, top_p=0.9, repetition_penalty=1.1,
+                                                          seed=100 + i, max_tokens=8)))
+        return {i: r.output for i, r in s.run_until_done().items()}
+    together = run([0, 1, 2], 2048)
+    assert together == run([0, 1, 2], 2048)
+    assert together == run([2, 1, 0], 9)
+    assert run([1], 2048)[1] == together[1]
+    assert len({tuple(v) for v in together.values()}) == 3
+    # the plain sampler with the same per-request state gives the same tokens
+    cfg, tensors = H._folder_contents(str(model.folder))
+    ids, state, out = list(PROMPTS[1]), 101, []
+    for _ in range(8):
+        logits = plain.forward(cfg, tensors, ids)[-1]
+        tok, state = plain.sample_plain(logits, ids, temperature=0.7, top_p=0.9, repetition_penalty=1.1,
+                                        repeat_last_n=64, state=state)
+        ids.append(tok)
+        out.append(tok)
+    assert out == together[1]
+
+
+def test_no_slot_means_waiting_not_failing(model):
+    s = make(model, max_requests=1)
+    for i in (1, 2):
+        s.submit(Request(i, PROMPTS[i], greedy(3)))
+    s.step()
+    assert [r.id for r in s.running] == [1] and [r.id for r in s.waiting] == [2]
+    done = s.run_until_done()
+    assert done[2].output == plain_greedy(model, PROMPTS[2], 3)
