@@ -272,3 +272,63 @@ SPITE_API int spite_sample(const SampleParams* p, int rows, void* stream) {
     sample_kernel<<<rows, THREADS, 0, (cudaStream_t)stream>>>(*p);
     return spite_launch_status();
 }
+
+// ---------------------------------------------------------------------------------
+// spite_sample_noalloc: the same kernel with its scratch rows in a fixed array of
+// this library instead of memory the caller allocates.  See sampling_noalloc.h for
+// who needs this, the size limit, and the rules on sharing and on the first call.
+// ---------------------------------------------------------------------------------
+#include "sampling_noalloc.h"
+
+// Scratch of the no-allocation entry point.  In host code this name is only a handle
+// for cudaGetSymbolAddress; it is never passed to a kernel as if it were a pointer.
+static __device__ __align__(256) float g_sample_noalloc_scratch[SPITE_SAMPLE_NOALLOC_MAX_FLOATS];
+
+namespace {
+
+constexpr int NOALLOC_MAX_DEVICES = 64;
+float* g_noalloc_scratch_addr[NOALLOC_MAX_DEVICES] = {};     // device address of the array, per device
+
+// The device address of the scratch array on the current device; looked up once per
+// device with that device current.  Returns null if the runtime refuses.
+float* noalloc_scratch_for_current_device() {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= NOALLOC_MAX_DEVICES) return nullptr;
+    if (!g_noalloc_scratch_addr[dev]) {
+        float* ptr = nullptr;
+        if (cudaGetSymbolAddress((void**)&ptr, g_sample_noalloc_scratch) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return nullptr;
+        }
+        g_noalloc_scratch_addr[dev] = ptr;
+    }
+    return g_noalloc_scratch_addr[dev];
+}
+
+}  // namespace
+
+SPITE_API int spite_sample_noalloc(const SpiteSampleNoAllocArgs* a, void* stream) {
+    if (!a || !a->logits || !a->temperature || !a->rng_state || !a->out_tokens) return SPITE_BAD_ARG;
+    if (a->rows < 0 || a->vocab < 1) return SPITE_BAD_ARG;
+    if (a->context && !a->context_offsets) return SPITE_BAD_ARG;
+    if ((long long)a->rows * (long long)a->vocab > (long long)SPITE_SAMPLE_NOALLOC_MAX_FLOATS)
+        return SPITE_UNSUPPORTED;                            // beyond the fixed scratch: nothing runs
+    if (a->rows == 0) return SPITE_OK;
+    float* scratch = noalloc_scratch_for_current_device();
+    if (!scratch) return SPITE_LAUNCH_FAILED;
+    SampleParams p;
+    p.logits = a->logits;
+    p.work = scratch;                                        // every element is written before it is read
+    p.temperature = a->temperature;
+    p.top_k = a->top_k;
+    p.top_p = a->top_p;
+    p.min_p = a->min_p;
+    p.repetition_penalty = a->repetition_penalty;
+    p.context = a->context;
+    p.context_offsets = a->context_offsets;
+    p.rng_state = a->rng_state;
+    p.out_tokens = a->out_tokens;
+    p.vocab = a->vocab;
+    sample_kernel<<<a->rows, THREADS, 0, (cudaStream_t)stream>>>(p);
+    return spite_launch_status();
+}

@@ -51,7 +51,7 @@ def _nvcc() -> str | None:
 def _signature(name: str) -> str:
     sources, extra = LIBRARIES[name]
     h = hashlib.sha256()
-    for f in sorted(CSRC.glob("*.cuh")):
+    for f in sorted(list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h"))):
         h.update(f.name.encode())
         h.update(f.read_bytes())
     for s in sources:
