@@ -70,7 +70,7 @@ class Model:
         return out
 
     def kernel_libraries(self) -> list[str]:
-        libs = {"elementwise", "gemm_simt"}
+        libs = {"elementwise", "gemm_simt", "gemm_skinny"}
         for _, part in self.parts():
             libs.update(part.kernel_libraries)
         return sorted(libs)

@@ -28,6 +28,7 @@ NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", 
 LIBRARIES = {
     "elementwise": (["elementwise.cu"], []),
     "gemm_simt": (["gemm_simt.cu"], []),
+    "gemm_skinny": (["gemm_skinny.cu"], []),
     "attention": (["attention.cu"], []),
     "moe": (["moe.cu"], []),
     "sampling": (["sampling.cu"], []),

@@ -119,7 +119,15 @@ class CudaKernels(KernelSet):
         _check(st, "rms_norm")
 
     # ------------------------------------------------------------------ matrix products
-    def _gemm(self, p: GemmParams, what):
+    def _gemm(self, p: GemmParams, what, max_rows_per_group):
+        """Pick the kernel: the tensor-core weight-streaming kernel for few bfloat16 rows,
+        else the CUDA-core kernel (always for float32)."""
+        if self.dtype == torch.bfloat16 and max_rows_per_group <= 64:
+            st = self._lib("gemm_skinny").spite_gemm_skinny(C.byref(p), int(max_rows_per_group), self._stream())
+            if st != -2:                       # -2: shape outside the kernel's domain, fall through
+                self.launches += 1
+                _check(st, what)
+                return
         st = self._lib("gemm_simt").spite_gemm_simt(self._dt, C.byref(p), self._stream())
         self.launches += 1
         _check(st, what)
@@ -143,7 +151,7 @@ class CudaKernels(KernelSet):
         p = GemmParams(A=x.data_ptr(), W=w.data_ptr(), C=out.data_ptr(), a_rows=None, c_rows=None,
                        group_offsets=None, row_scale=_ptr(row_scale), lda=K, ldc=N, w_group_stride=0,
                        n_groups=1, M=M, N=N, K=K, epilogue=epi, scale_by_a_row=0)
-        self._gemm(p, "linear")
+        self._gemm(p, "linear", M)
 
     def linear_swiglu(self, x, w_gate_up, out, *, row_scale=None):
         self._t(x, self.dtype, "x"); self._t(w_gate_up, self.dtype, "w"); self._t(out, self.dtype, "out")
@@ -154,7 +162,7 @@ class CudaKernels(KernelSet):
         p = GemmParams(A=x.data_ptr(), W=w_gate_up.data_ptr(), C=out.data_ptr(), a_rows=None, c_rows=None,
                        group_offsets=None, row_scale=_ptr(row_scale), lda=K, ldc=F, w_group_stride=0,
                        n_groups=1, M=M, N=F, K=K, epilogue=EPI_SWIGLU, scale_by_a_row=0)
-        self._gemm(p, "linear_swiglu")
+        self._gemm(p, "linear_swiglu", M)
 
     def grouped_linear_swiglu(self, x, w_gate_up, sorted_rows, offsets, row_scale, out):
         self._t(x, self.dtype, "x"); self._t(w_gate_up, self.dtype, "w"); self._t(out, self.dtype, "out")
@@ -168,7 +176,7 @@ class CudaKernels(KernelSet):
                        a_rows=sorted_rows.data_ptr(), c_rows=None, group_offsets=offsets.data_ptr(),
                        row_scale=_ptr(row_scale), lda=K, ldc=F, w_group_stride=F2 * K,
                        n_groups=E, M=M, N=F, K=K, epilogue=EPI_SWIGLU, scale_by_a_row=1)
-        self._gemm(p, "grouped_linear_swiglu")
+        self._gemm(p, "grouped_linear_swiglu", M)
 
     def grouped_linear_accumulate(self, a, w_down, sorted_rows, offsets, h):
         self._t(a, self.dtype, "a"); self._t(w_down, self.dtype, "w"); self._t(h, torch.float32, "h")
@@ -180,7 +188,7 @@ class CudaKernels(KernelSet):
                        c_rows=sorted_rows.data_ptr(), group_offsets=offsets.data_ptr(), row_scale=None,
                        lda=F, ldc=d, w_group_stride=d * F, n_groups=E, M=M, N=d, K=F,
                        epilogue=EPI_ADD_F32, scale_by_a_row=0)
-        self._gemm(p, "grouped_linear_accumulate")
+        self._gemm(p, "grouped_linear_accumulate", M)
 
     # ------------------------------------------------------------------ attention
     def _step_tokens(self, batch, group):
