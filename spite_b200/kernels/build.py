@@ -30,6 +30,7 @@ LIBRARIES = {
     "gemm_simt": (["gemm_simt.cu"], []),
     "gemm_skinny": (["gemm_skinny.cu"], []),
     "attention": (["attention.cu"], []),
+    "attention_mma": (["attention_mma.cu"], []),
     "moe": (["moe.cu"], []),
     "sampling": (["sampling.cu"], []),
 }

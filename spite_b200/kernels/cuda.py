@@ -49,6 +49,11 @@ class AttentionParams(C.Structure):
                 ("window_kind", C.c_int), ("window_size", C.c_int), ("softmax_scale", C.c_float)]
 
 
+class AttnMmaExtra(C.Structure):
+    _fields_ = [("cu_seqlens", C.c_void_p), ("o_part", C.c_void_p), ("ml_part", C.c_void_p),
+                ("n_segments", C.c_int), ("tokens_per_block", C.c_int), ("n_splits", C.c_int)]
+
+
 class SampleParams(C.Structure):
     _fields_ = [("logits", C.c_void_p), ("work", C.c_void_p), ("temperature", C.c_void_p),
                 ("top_k", C.c_void_p), ("top_p", C.c_void_p), ("min_p", C.c_void_p),
@@ -77,6 +82,7 @@ class CudaKernels(KernelSet):
         self._dt = _DT[dtype]
         self._libs = {}
         self.launches = 0          # kernels launched so far (for measurement reports)
+        self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
 
     # ------------------------------------------------------------------ helpers
     def _lib(self, name):
@@ -221,6 +227,31 @@ class CudaKernels(KernelSet):
                             window_kind=_WINDOW[window.kind], window_size=int(window.size),
                             softmax_scale=float(softmax_scale))
         b, c = self._step_tokens(batch, cache.group), self._paged(cache)
+        group = num_heads // c.num_kv_heads
+        if (self.dtype == torch.bfloat16 and c.head_dim % 16 == 0 and c.head_dim <= 128 and group <= 16
+                and c.page_size % 16 == 0 and batch.segments):
+            # tensor-core kernel: rows are (token, head of a kv group) pairs, up to 16 a block
+            tpb = max(1, 16 // group)
+            n_blocks, longest = 0, 1
+            for s in batch.segments:
+                n_blocks += -(-s.n_tokens // tpb)
+                last = s.start_pos + s.n_tokens - 1
+                longest = max(longest, last - window.lowest_visible(max(s.start_pos, last - tpb + 1)) + 1)
+            tiles = -(-longest // 16) + 1
+            base = n_blocks * c.num_kv_heads
+            splits = max(1, min(-(-2 * self.sm_count // base), tiles // 8, 128))
+            o_part = ml_part = None
+            if splits > 1:
+                o_part = torch.empty((batch.n_tokens, num_heads, splits, c.head_dim), dtype=torch.float32,
+                                     device=q.device)
+                ml_part = torch.empty((batch.n_tokens, num_heads, splits, 2), dtype=torch.float32, device=q.device)
+            x = AttnMmaExtra(cu_seqlens=batch.cu_seqlens.data_ptr(), o_part=_ptr(o_part), ml_part=_ptr(ml_part),
+                             n_segments=len(batch.segments), tokens_per_block=tpb, n_splits=splits)
+            st = self._lib("attention_mma").spite_paged_attention_mma(
+                C.byref(p), C.byref(b), C.byref(c), C.byref(x), n_blocks, self._stream())
+            self.launches += 1 + (splits > 1)
+            _check(st, "paged_attention (tensor cores)")
+            return
         st = self._lib("attention").spite_paged_attention(self._dt, C.byref(p), C.byref(b), C.byref(c),
                                                           self._stream())
         self.launches += 1
