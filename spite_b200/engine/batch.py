@@ -34,6 +34,8 @@ class StepBatch:
     logit_rows: torch.Tensor       # [R] int32 rows whose logits are wanted
     block_tables: list = field(default_factory=list)   # per group: [S, W] int32
     max_seg_len: int = 0
+    context_bucket: int | None = None   # steps replayed from a CUDA graph: launch shapes are chosen for
+                                        # this context length instead of the step's own
 
 
 def build_step_batch(segments, tokens_per_segment, wants, tables_per_group, device, pin=True) -> StepBatch:
@@ -87,3 +89,58 @@ def build_step_batch(segments, tokens_per_segment, wants, tables_per_group, devi
         seg_of_token=view("sot"), cu_seqlens=view("cu"), slots=view("slots"), logit_rows=view("rows"),
         block_tables=[view(f"bt{g}").view(S, widths[g]) for g in range(len(tables_per_group))],
         max_seg_len=max((len(t) for t in tokens_per_segment), default=0))
+
+
+class StaticDecodeBatch:
+    """The inputs of a decode step (one token per request) at fixed device addresses,
+    so that the step's kernels can be captured once in a CUDA graph and replayed:
+    only the contents of these buffers change from step to step."""
+
+    def __init__(self, n_requests: int, table_widths: list, device, context_bucket: int):
+        S = self.S = n_requests
+        self.widths = list(table_widths)
+        total = 3 * S + (S + 1) + S + S + sum(S * w for w in self.widths)
+        self.host = torch.empty(total, dtype=torch.int32)
+        if torch.device(device).type == "cuda":
+            self.host = self.host.pin_memory()
+        self.dev = torch.empty(total, dtype=torch.int32, device=device)
+        buf = self.host.numpy()
+        o = 0
+
+        def take(n):
+            nonlocal o
+            o += n
+            return slice(o - n, o)
+        self._tok, self._pos, sot = take(S), take(S), take(S)
+        cu, self._slots, rows = take(S + 1), take(S), take(S)
+        self._bt = [take(S * w) for w in self.widths]
+        buf[sot] = range(S)
+        buf[cu] = range(S + 1)
+        buf[rows] = range(S)
+        self.batch = StepBatch(
+            n_tokens=S, segments=[], token_ids=self.dev[self._tok], positions=self.dev[self._pos],
+            seg_of_token=self.dev[sot], cu_seqlens=self.dev[cu], slots=self.dev[self._slots],
+            logit_rows=self.dev[rows],
+            block_tables=[self.dev[sl].view(S, w) for sl, w in zip(self._bt, self.widths)],
+            max_seg_len=1, context_bucket=context_bucket)
+        self._copied = None
+
+    def fill(self, segments, tokens, tables_per_group):
+        """Write this step's tokens, positions, slots and block tables and start the copy."""
+        if self._copied is not None:
+            self._copied.synchronize()          # the last step's copy has read the host buffer
+        buf = self.host.numpy()
+        buf[self._tok] = tokens
+        buf[self._pos] = [s.start_pos for s in segments]
+        buf[self._slots] = [s.slot for s in segments]
+        for sl, w, tabs in zip(self._bt, self.widths, tables_per_group):
+            bt = buf[sl].reshape(self.S, w)
+            bt[:] = -1
+            for i, t in enumerate(tabs):
+                bt[i, :len(t)] = t
+        self.batch.segments = list(segments)
+        self.dev.copy_(self.host, non_blocking=True)
+        if self.dev.is_cuda:
+            self._copied = torch.cuda.Event()
+            self._copied.record()
+        return self.batch

@@ -17,7 +17,7 @@ from dataclasses import dataclass
 import torch
 
 from ..cache import CacheError, CacheStorage, OutOfPages, OutOfSlots
-from .batch import Segment, build_step_batch
+from .batch import Segment, StaticDecodeBatch, build_step_batch
 
 
 class StepError(ValueError):
@@ -37,7 +37,7 @@ class StepEntry:
 
 class Engine:
     def __init__(self, model, *, cache_tokens: int, page_size: int = 64, max_requests: int = 64,
-                 max_positions: int | None = None):
+                 max_positions: int | None = None, cuda_graphs: bool | None = None, max_graphs: int = 12):
         if page_size < 1:
             raise ValueError("page_size must be positive")
         self.model = model
@@ -49,6 +49,14 @@ class Engine:
         self.cache = self.storage.manager
         self.steps_run = 0
         self.tokens_run = 0
+        # Decode steps (one token per request) are launch-bound: their kernels are captured in
+        # a CUDA graph per (number of requests, context bucket) and replayed.
+        if cuda_graphs is None:
+            cuda_graphs = model.device.type == "cuda" and model.graph_safe()
+        self.cuda_graphs = bool(cuda_graphs)
+        self.max_graphs = max_graphs
+        self._graphs: dict = {}
+        self.graph_replays = 0
 
     # ------------------------------------------------------------------ requests
     def is_live(self, req_id) -> bool:
@@ -116,10 +124,16 @@ class Engine:
                 self.storage.clear_state(rc.slot)
         tables = [[self.cache.requests[e.req_id].tables[g] for e in entries]
                   for g in range(self.storage.n_groups)]
-        batch = build_step_batch(segments, [e.tokens for e in entries], [e.want for e in entries],
-                                 tables, self.model.device)
         try:
-            logits = self.model.forward(batch, self.storage)
+            if self.cuda_graphs and all(len(e.tokens) == 1 for e in entries):
+                logits = self._decode_step_from_graph(segments, [e.tokens[0] for e in entries], tables)
+                rows = [i for i, e in enumerate(entries) if e.want]
+                if len(rows) < len(entries):
+                    logits = logits[torch.tensor(rows, dtype=torch.long, device=logits.device)]
+            else:
+                batch = build_step_batch(segments, [e.tokens for e in entries], [e.want for e in entries],
+                                         tables, self.model.device)
+                logits = self.model.forward(batch, self.storage)
         except Exception:
             for r in reserved:
                 self.cache.rollback(r)
@@ -131,3 +145,47 @@ class Engine:
         self.steps_run += 1
         self.tokens_run += offset
         return logits
+
+    # ------------------------------------------------------------------ decode steps from CUDA graphs
+    def _decode_step_from_graph(self, segments, tokens, tables) -> torch.Tensor:
+        """A step of single tokens.  The first step of a shape runs eagerly (it loads and warms
+        every kernel), the second is captured, later ones replay the capture.  The returned
+        logits live in the graph's memory and are valid until the next step of that shape."""
+        S = len(segments)
+        longest = max(s.start_pos for s in segments) + 1
+        bucket = max(128, 1 << (longest - 1).bit_length())
+        key = (S, bucket)
+        st = self._graphs.get(key)
+        if st is None:
+            while len(self._graphs) >= self.max_graphs:
+                self._graphs.pop(next(iter(self._graphs)))
+            width = -(-self.max_positions // self.page_size)
+            st = _GraphState(StaticDecodeBatch(S, [width] * self.storage.n_groups, self.model.device, bucket))
+            self._graphs[key] = st
+        batch = st.static.fill(segments, tokens, tables)
+        if st.graph is None:
+            if st.eager_runs == 0:
+                st.eager_runs = 1
+                return self.model.forward(batch, self.storage)
+            graph = torch.cuda.CUDAGraph()
+            counted = getattr(self.model.kernels, "launches", 0)
+            with torch.cuda.graph(graph):
+                st.logits = self.model.forward(batch, self.storage)
+            st.graph = graph
+            if hasattr(self.model.kernels, "launches"):          # captured, not run: count them per replay
+                st.n_kernels = self.model.kernels.launches - counted
+                self.model.kernels.launches = counted
+        st.graph.replay()
+        if st.n_kernels:
+            self.model.kernels.launches += st.n_kernels
+        self.graph_replays += 1
+        return st.logits
+
+
+class _GraphState:
+    def __init__(self, static):
+        self.static = static
+        self.graph = None
+        self.logits = None
+        self.eager_runs = 0
+        self.n_kernels = 0

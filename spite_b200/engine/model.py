@@ -75,6 +75,13 @@ class Model:
             libs.update(part.kernel_libraries)
         return sorted(libs)
 
+    def graph_safe(self) -> bool:
+        """True if a step's kernels can be captured in a CUDA graph: the product kernel set
+        and parts that launch nothing but its kernels and never read device data on the host."""
+        from ..kernels.cuda import CudaKernels
+        return isinstance(self.kernels, CudaKernels) and all(part.graph_safe for _, part in self.parts()) \
+            and all(getattr(b, "graph_safe", False) for b in self.blocks)
+
     def _check_caches(self):
         self._cache_specs = {}
         for call in self.plan.order:

@@ -237,6 +237,8 @@ class CudaKernels(KernelSet):
                 n_blocks += -(-s.n_tokens // tpb)
                 last = s.start_pos + s.n_tokens - 1
                 longest = max(longest, last - window.lowest_visible(max(s.start_pos, last - tpb + 1)) + 1)
+            if batch.context_bucket:            # fixed launch shape for a captured step
+                longest = batch.context_bucket if window.kind == "full" else min(batch.context_bucket, window.size)
             tiles = -(-longest // 16) + 1
             base = n_blocks * c.num_kv_heads
             splits = max(1, min(-(-2 * self.sm_count // base), tiles // 8, 128))

@@ -91,6 +91,9 @@ class Part:
     kind = "?"
     #: names of kernel libraries (csrc) the part launches; compiled when a model is built
     kernel_libraries: tuple = ()
+    #: the part launches kernels of the kernel set only and never reads device data on the
+    #: host, so a step that contains it can be captured in a CUDA graph
+    graph_safe = False
 
     def __init__(self, ctx: BuildContext):
         self.ctx = ctx

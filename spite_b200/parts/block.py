@@ -14,6 +14,7 @@ from .base import Block, build_part, register_block
 
 @register_block("prenorm_residual")
 class PreNormResidual(Block):
+    graph_safe = True
     def __init__(self, ctx, spec):
         super().__init__(ctx)
         self.mixer_norm = build_part("norm", spec.mixer_norm, ctx)

@@ -16,6 +16,7 @@ from .base import FeedForward, ParamSpec, register_feed_forward
 @register_feed_forward("dense_swiglu")
 class DenseSwiGLU(FeedForward):
     """h += down( silu(gate x) * (up x) )          (llama4.rs:257-271)"""
+    graph_safe = True
     kernel_libraries = ("gemm_simt",)
 
     def __init__(self, ctx, hidden_size: int, intermediate_size: int):
@@ -53,6 +54,7 @@ class MoESigmoidPrescaled(FeedForward):
     g, u the products of the unscaled token.  That equals the pre-scaled form
     and spares rounding the scaled token to the activation type.
     """
+    graph_safe = True
     kernel_libraries = ("gemm_simt", "moe")
 
     def __init__(self, ctx, hidden_size: int, num_experts: int, top_k: int, expert_size: int,

@@ -8,6 +8,7 @@ from .base import Norm, ParamSpec, register_norm
 
 @register_norm("rms_norm")
 class RmsNorm(Norm):
+    graph_safe = True
     kernel_libraries = ("elementwise",)
 
     def __init__(self, ctx, size: int, eps: float):

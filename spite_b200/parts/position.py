@@ -42,6 +42,7 @@ def rotary_frequencies(head_dim: int, theta: float, scaling: dict | None) -> lis
 @register_position("rotary_interleaved")
 class RotaryInterleaved(PositionEncoding):
     """Rotation of neighbouring pairs (2i, 2i+1) of every head of q and k."""
+    graph_safe = True
 
     def __init__(self, ctx, head_dim: int, theta: float, scaling: dict | None = None):
         super().__init__(ctx)
@@ -56,6 +57,7 @@ class RotaryInterleaved(PositionEncoding):
 
 @register_position("no_position")
 class NoPosition(PositionEncoding):
+    graph_safe = True
     def __init__(self, ctx):
         super().__init__(ctx)
 
