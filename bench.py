@@ -134,7 +134,7 @@ def run_ours(args):
     page = 64
     max_b = max(B, 64 if not args.skip_points else B)
     engine = Engine(model, cache_tokens=max_b * (ctx + page), page_size=page, max_requests=max_b,
-                    max_positions=ctx + page)
+                    max_positions=ctx + page, cuda_graphs=False if args.no_graphs else None)
     for kv in engine.storage.kv:                       # a cache as earlier steps would have left it
         kv.normal_(0.0, 1.0)
     g = torch.Generator().manual_seed(1)
@@ -180,6 +180,10 @@ def run_ours(args):
     end_ctx = ctx - 1
     nbytes = decode_bytes(model, engine, [end_ctx] * B, distinct)
     achieved = nbytes / (ms_step * 1e-3) / 1e9
+    if args.only_decode:
+        print(json.dumps({"decode_ms_per_step": round(ms_step, 4), "tok_per_s": round(value, 1), "batch": B,
+                          "layers": args.layers, "launches": launches, "GBps": round(achieved, 1)}))
+        return
 
     # end to end through the scheduler: host tokens in (pinned copy), sampled tokens out
     sched = Scheduler(engine, Sampler(ks), max_batch_tokens=4096, ctx=ctx + page)
@@ -283,6 +287,8 @@ def main(argv=None):
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=8192)
     ap.add_argument("--skip-points", action="store_true")
+    ap.add_argument("--no-graphs", action="store_true", help="launch every kernel of a decode step by itself")
+    ap.add_argument("--only-decode", action="store_true", help="measure the decode step only (for profiling)")
     args = ap.parse_args(argv)
     if args.impl == "reference":
         return run_reference(args)

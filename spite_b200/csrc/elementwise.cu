@@ -35,6 +35,25 @@ __global__ void rms_norm_kernel(const float* __restrict__ x, const float* __rest
     for (int c = threadIdx.x; c < d; c += blockDim.x) out[c] = from_f32<T>(in[c] * scale * gain[c]);
 }
 
+// dst[i, :] = src[idx[i], :]   (rows of activations brought into expert order), 16 bytes per thread and step
+__global__ void gather_rows_kernel(const uint4* __restrict__ src, const int* __restrict__ idx,
+                                   uint4* __restrict__ dst, int row_vecs) {
+    const size_t i = blockIdx.x;
+    const uint4* in = src + (size_t)idx[i] * row_vecs;
+    uint4* out = dst + i * row_vecs;
+    for (int c = threadIdx.x; c < row_vecs; c += blockDim.x) out[c] = in[c];
+}
+
+SPITE_API int spite_gather_rows(const void* src, const int* idx, void* dst, int n_rows, long long row_bytes,
+                                void* stream) {
+    if (!src || !idx || !dst || n_rows < 0 || row_bytes <= 0) return SPITE_BAD_ARG;
+    if (row_bytes % 16 || (((uintptr_t)src | (uintptr_t)dst) & 15)) return SPITE_UNSUPPORTED;
+    if (n_rows == 0) return SPITE_OK;
+    gather_rows_kernel<<<n_rows, 128, 0, (cudaStream_t)stream>>>((const uint4*)src, idx, (uint4*)dst,
+                                                                 (int)(row_bytes / 16));
+    return spite_launch_status();
+}
+
 SPITE_API int spite_embed(int dtype, const void* table, const int* tokens, float* h,
                           int n_tokens, int d, int vocab, void* stream) {
     if (!table || !tokens || !h || n_tokens < 0 || d <= 0 || vocab <= 0) return SPITE_BAD_ARG;

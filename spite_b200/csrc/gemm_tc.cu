@@ -1,0 +1,355 @@
+// Matrix product for many tokens (prefill) on the fifth-generation tensor cores:
+//   C[M, N] (=|+=) epilogue( A[M, K] W[N, K]^T ),  bfloat16 inputs, float32 sums in TMEM.
+//
+// One block computes a 128 x 128 tile (two accumulators for the SwiGLU epilogue: gate and
+// up rows of W).  Roles by warp:
+//   warp 0    one lane issues TMA loads (cp.async.bulk.tensor) of the A and W tiles of a
+//             64-wide k block into a ring of shared-memory stages (128-byte swizzle);
+//   warp 1    allocates TMEM; one lane issues tcgen05.mma (128x128x16, operands straight
+//             from shared memory through matrix descriptors) and commits each stage back
+//             to the loader, the finished accumulator to the epilogue;
+//   warps 2-5 read the accumulator with tcgen05.ld (one row per thread) and apply the
+//             epilogue: store, add to the float32 residual stream (optionally scattered
+//             through c_rows), or SwiGLU with a per-row scale.
+// Stages and roles hand over through mbarriers.  Every wait is bounded: after about two
+// seconds a waiter raises an abort flag that all roles poll, records an error code that
+// the host can read with spite_gemm_tc_error(), and the block leaves through the common
+// exit, where TMEM is freed.
+//
+// Rows of A are contiguous (a grouped product gets its rows gathered into expert order
+// beforehand); `a_rows`, if set, only indexes `row_scale`.  Edges in M, N and K are
+// covered by TMA's zero fill on loads and by bounds checks on stores.
+#include "gemm.cuh"
+#include <cuda.h>
+
+namespace {
+
+constexpr int BM = 128, BN = 128, BK = 64, UMMA_K = 16;
+constexpr int TILE_BYTES = BM * BK * 2;                  // 16 KiB, one operand tile of one stage
+constexpr int THREADS = 192;
+constexpr long long WAIT_CYCLES = 4000000000ll;          // about two seconds
+
+__device__ int g_tc_error = 0;
+
+// ---------------------------------------------------------------- PTX wrappers
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(unsigned bar, unsigned parity) {
+    unsigned ok;
+    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.b32 %0, 1, 0, p;\n}\n"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Waits for the phase of `parity`; gives up when the abort flag is up or time has run out.
+__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatile int* abort_flag, int code) {
+    if (mbar_try(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (true) {
+        if (mbar_try(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (clock64() - t0 > WAIT_CYCLES) {
+            *abort_flag = 1;
+            atomicCAS(&g_tc_error, 0, code);
+            return false;
+        }
+    }
+}
+__device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap* map, int x, int y, unsigned bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
+                 ::"r"(dst), "l"((unsigned long long)map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(unsigned bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma(unsigned d_tmem, unsigned long long a_desc, unsigned long long b_desc,
+                                       unsigned idesc, unsigned accumulate) {
+    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+                 ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_ld32(float (&v)[32], unsigned taddr) {
+    unsigned r[32];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+                 "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: rows of 128
+// bytes, 8-row groups 1024 bytes apart (stride byte offset), descriptor version 1.
+__device__ __forceinline__ unsigned long long smem_desc(unsigned addr) {
+    unsigned long long d = 0;
+    d |= (unsigned long long)((addr & 0x3FFFF) >> 4);            // start address
+    d |= (unsigned long long)1 << 16;                            // leading byte offset (unused with swizzle)
+    d |= (unsigned long long)(1024 >> 4) << 32;                  // stride byte offset
+    d |= (unsigned long long)1 << 46;                            // version
+    d |= (unsigned long long)2 << 61;                            // SWIZZLE_128B
+    return d;
+}
+
+// kind::f16 instruction descriptor: float32 accumulator, bfloat16 A and B, both K-major.
+__host__ __device__ constexpr unsigned make_idesc(int m, int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(n >> 3) << 17) | ((unsigned)(m >> 4) << 24);
+}
+
+struct SharedTail {
+    unsigned long long full[8];
+    unsigned long long empty[8];
+    unsigned long long acc_full;
+    unsigned tmem_base;
+    int abort_flag;
+};
+
+template <int EPI, int STAGES>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+               const GemmParams p) {
+    constexpr bool DUAL = (EPI == EPI_SWIGLU);
+    constexpr int OPERANDS = DUAL ? 3 : 2;
+    constexpr int STAGE_BYTES = OPERANDS * TILE_BYTES;
+    constexpr int TMEM_COLS = DUAL ? 2 * BN : BN;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    SharedTail* tail = (SharedTail*)(smem + STAGES * STAGE_BYTES);
+
+    int group, row0, rows;
+    const bool have_tile = locate_row_tile(p, blockIdx.y, BM, group, row0, rows);
+    if (!have_tile) return;                                   // whole block, before any barrier
+    const int n0 = blockIdx.x * BN;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int num_kb = (p.K + BK - 1) / BK;
+    const int w_rows = DUAL ? 2 * p.N : p.N;
+    volatile int* abort_flag = &tail->abort_flag;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(smem_u32(&tail->full[s]), 1); mbar_init(smem_u32(&tail->empty[s]), 1); }
+        mbar_init(smem_u32(&tail->acc_full), 1);
+        tail->abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n"
+                     ::"r"(smem_u32(&tail->tmem_base)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const unsigned tmem = tail->tmem_base;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // ---- loader
+            int issued = 0;
+            for (int kb = 0; kb < num_kb; ++kb) {
+                const int s = kb % STAGES;
+                const unsigned ph = (kb / STAGES) & 1;
+                if (!mbar_wait(smem_u32(&tail->empty[s]), ph ^ 1, abort_flag, 1)) break;
+                const unsigned bar = smem_u32(&tail->full[s]);
+                const unsigned dst = smem_u32(smem + s * STAGE_BYTES);
+                mbar_expect_tx(bar, STAGE_BYTES);
+                tma_load_2d(dst, &map_a, kb * BK, row0, bar);
+                tma_load_2d(dst + TILE_BYTES, &map_w, kb * BK, group * w_rows + n0, bar);
+                if (DUAL) tma_load_2d(dst + 2 * TILE_BYTES, &map_w, kb * BK, group * w_rows + p.N + n0, bar);
+                issued = kb + 1;
+            }
+            if (*abort_flag) {
+                // copies in flight must land before the block gives its shared memory back
+                for (int kb = max(0, issued - STAGES); kb < issued; ++kb) {
+                    const long long t0 = clock64();
+                    while (!mbar_try(smem_u32(&tail->full[kb % STAGES]), (kb / STAGES) & 1) &&
+                           clock64() - t0 < WAIT_CYCLES) {}
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // ---- tensor-core issue
+            constexpr unsigned IDESC = make_idesc(BM, BN);
+            bool ok = true;
+            for (int kb = 0; kb < num_kb && ok; ++kb) {
+                const int s = kb % STAGES;
+                const unsigned ph = (kb / STAGES) & 1;
+                ok = mbar_wait(smem_u32(&tail->full[s]), ph, abort_flag, 2);
+                if (!ok) break;
+                tc_fence_after();
+                const unsigned a_addr = smem_u32(smem + s * STAGE_BYTES);
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; ++k) {
+                    const unsigned long long a_desc = smem_desc(a_addr + k * UMMA_K * 2);
+                    const unsigned long long b_desc = smem_desc(a_addr + TILE_BYTES + k * UMMA_K * 2);
+                    const unsigned acc = (kb > 0 || k > 0) ? 1u : 0u;
+                    tc_mma(tmem, a_desc, b_desc, IDESC, acc);
+                    if (DUAL) tc_mma(tmem + BN, a_desc, smem_desc(a_addr + 2 * TILE_BYTES + k * UMMA_K * 2), IDESC, acc);
+                }
+                tc_commit(smem_u32(&tail->empty[s]));          // the stage is free once these MMAs have read it
+            }
+            if (ok) tc_commit(smem_u32(&tail->acc_full));       // the accumulator is complete
+        }
+    } else {
+        // ---- epilogue: warp w may read TMEM lanes [32 (w % 4), 32 (w % 4) + 32)
+        const int quarter = warp & 3;
+        const int r = quarter * 32 + lane;
+        const bool got = mbar_wait(smem_u32(&tail->acc_full), 0, abort_flag, 3);
+        tc_fence_after();
+        if (got) {
+            const int li = row0 + r;
+            const bool row_ok = r < rows;
+            int crow = li, srow = li;
+            float sc = 1.f;
+            if (row_ok) {
+                if (p.c_rows) crow = p.c_rows[li];
+                if (p.row_scale) {
+                    if (p.scale_by_a_row && p.a_rows) srow = p.a_rows[li];
+                    sc = p.row_scale[srow];
+                }
+            }
+            const unsigned lane_addr = tmem + ((unsigned)(quarter * 32) << 16);
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                float v[32];
+                tc_ld32(v, lane_addr + c0);                    // warp-collective: every lane takes part
+                float u[32];
+                if (DUAL) tc_ld32(u, lane_addr + BN + c0);
+                if (!row_ok) continue;
+                const int n = n0 + c0;
+                if (n >= p.N) continue;
+                const size_t o = (size_t)crow * p.ldc + n;
+                const bool full = (n + 32 <= p.N);
+                if (EPI == EPI_STORE || EPI == EPI_SWIGLU) {
+                    __nv_bfloat16* dst = (__nv_bfloat16*)p.C + o;
+                    float y[32];
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) y[i] = DUAL ? silu_f32(v[i] * sc) * (u[i] * sc) : v[i] * sc;
+                    if (full && ((uintptr_t)dst & 15) == 0) {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 8) {
+                            uint4 q;
+                            __nv_bfloat162 h0 = __floats2bfloat162_rn(y[i], y[i + 1]), h1 = __floats2bfloat162_rn(y[i + 2], y[i + 3]);
+                            __nv_bfloat162 h2 = __floats2bfloat162_rn(y[i + 4], y[i + 5]), h3 = __floats2bfloat162_rn(y[i + 6], y[i + 7]);
+                            q.x = *(unsigned*)&h0; q.y = *(unsigned*)&h1; q.z = *(unsigned*)&h2; q.w = *(unsigned*)&h3;
+                            *(uint4*)(dst + i) = q;
+                        }
+                    } else {
+                        for (int i = 0; i < 32 && n + i < p.N; ++i) dst[i] = __float2bfloat16_rn(y[i]);
+                    }
+                } else {
+                    float* dst = (float*)p.C + o;
+                    if (full && ((uintptr_t)dst & 15) == 0) {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 4) {
+                            float4 q = make_float4(v[i] * sc, v[i + 1] * sc, v[i + 2] * sc, v[i + 3] * sc);
+                            if (EPI == EPI_ADD_F32) {
+                                const float4 old = *(const float4*)(dst + i);
+                                q.x += old.x; q.y += old.y; q.z += old.z; q.w += old.w;
+                            }
+                            *(float4*)(dst + i) = q;
+                        }
+                    } else {
+                        for (int i = 0; i < 32 && n + i < p.N; ++i)
+                            dst[i] = (EPI == EPI_ADD_F32 ? dst[i] : 0.f) + v[i] * sc;
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// ---------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult res;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &res) == cudaSuccess &&
+            res == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)ptr;
+    }
+    return fn;
+}
+
+// A row-major [rows, cols] bfloat16 matrix with leading dimension ld; boxes of 64 columns x 128 rows.
+bool make_map(CUtensorMap* map, const void* base, long long rows, long long cols, long long ld) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)BM};
+    cuuint32_t estr[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int EPI, int STAGES>
+int launch(const GemmParams& p, const CUtensorMap& ma, const CUtensorMap& mw, cudaStream_t st) {
+    constexpr int OPERANDS = (EPI == EPI_SWIGLU) ? 3 : 2;
+    const size_t smem = (size_t)STAGES * OPERANDS * TILE_BYTES + sizeof(SharedTail) + 1024;
+    auto k = gemm_tc_kernel<EPI, STAGES>;
+    if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+        return SPITE_LAUNCH_FAILED;
+    const int row_tiles = (p.M + BM - 1) / BM + (p.group_offsets ? p.n_groups : 0);
+    dim3 grid((p.N + BN - 1) / BN, row_tiles);
+    if (grid.y > 65535) return SPITE_UNSUPPORTED;
+    k<<<grid, THREADS, smem, st>>>(ma, mw, p);
+    return spite_launch_status();
+}
+
+}  // namespace
+
+SPITE_API int spite_gemm_tc(const GemmParams* p, void* stream) {
+    if (!p || !p->A || !p->W || !p->C) return SPITE_BAD_ARG;
+    if (p->M < 0 || p->N <= 0 || p->K <= 0 || p->lda < p->K || p->ldc < p->N) return SPITE_BAD_ARG;
+    if (p->group_offsets ? p->n_groups < 1 : p->n_groups != 1) return SPITE_BAD_ARG;
+    if (p->epilogue < 0 || p->epilogue > EPI_SWIGLU) return SPITE_BAD_ARG;
+    // TMA: 16-byte aligned bases and row pitches
+    if (p->K % 8 || p->lda % 8 || (((uintptr_t)p->A | (uintptr_t)p->W) & 15)) return SPITE_UNSUPPORTED;
+    if (p->n_groups > 1 && p->w_group_stride != (long long)(p->epilogue == EPI_SWIGLU ? 2 : 1) * p->N * p->K)
+        return SPITE_UNSUPPORTED;                              // groups must be stacked without gaps
+    if (p->M == 0) return SPITE_OK;
+    const long long w_rows = (long long)(p->epilogue == EPI_SWIGLU ? 2 : 1) * p->N * p->n_groups;
+    CUtensorMap ma, mw;
+    if (!make_map(&ma, p->A, p->M, p->K, p->lda) || !make_map(&mw, p->W, w_rows, p->K, p->K))
+        return SPITE_LAUNCH_FAILED;
+    cudaStream_t st = (cudaStream_t)stream;
+    switch (p->epilogue) {
+        case EPI_STORE: return launch<EPI_STORE, 6>(*p, ma, mw, st);
+        case EPI_STORE_F32: return launch<EPI_STORE_F32, 6>(*p, ma, mw, st);
+        case EPI_ADD_F32: return launch<EPI_ADD_F32, 6>(*p, ma, mw, st);
+        default: return launch<EPI_SWIGLU, 4>(*p, ma, mw, st);
+    }
+}
+
+// Error code recorded by a block that gave up waiting (0: none); reading it clears it.
+// 1: loader waited for a free stage, 2: tensor-core issue waited for a tile, 3: epilogue waited for the accumulator.
+SPITE_API int spite_gemm_tc_error() {
+    int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, g_tc_error, sizeof(int)) != cudaSuccess) return -3;
+    if (v) cudaMemcpyToSymbol(g_tc_error, &zero, sizeof(int));
+    return v;
+}

@@ -15,29 +15,53 @@ namespace {
 
 constexpr int MAX_EXPERTS = 1024;
 
-// grid ceil(tokens/4), block 128: one warp per token.
+// grid tokens, block 256: the token's row is staged in shared memory as float32, every
+// warp takes experts e = warp, warp + 8, ...; warp 0 then picks the k largest logits.
+// A logit is summed in an order fixed by the width d alone.
 template <typename T>
-__global__ void __launch_bounds__(128) route_kernel(const T* __restrict__ x, const float* __restrict__ wr,
+__global__ void __launch_bounds__(256) route_kernel(const T* __restrict__ x, const float* __restrict__ wr,
                                                     int n_tokens, int d, int n_experts, int top_k,
                                                     int* __restrict__ expert_ids, float* __restrict__ weights,
                                                     float* __restrict__ logits_out) {
-    extern __shared__ float logits_s[];                      // [4][n_experts]
+    extern __shared__ __align__(16) float route_s[];         // [d] token, [n_experts] logits
+    float* xs = route_s;
+    float* lg = route_s + ((d + 3) & ~3);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int t = blockIdx.x * 4 + warp;
-    if (t >= n_tokens) return;
-    float* lg = logits_s + (size_t)warp * n_experts;
+    const int t = blockIdx.x;
     const T* xr = x + (size_t)t * d;
-    for (int e = 0; e < n_experts; ++e) {
+    for (int k = threadIdx.x; k < d; k += blockDim.x) xs[k] = to_f32(xr[k]);
+    __syncthreads();
+    const bool vec = (d % 4 == 0) && (((uintptr_t)wr & 15) == 0);
+    for (int e = warp; e < n_experts; e += 8) {
         const float* w = wr + (size_t)e * d;
-        float s = 0.f;
-        for (int k = lane; k < d; k += 32) s = fmaf(to_f32(xr[k]), w[k], s);
-        s = warp_sum(s);
+        float s0 = 0.f, s1 = 0.f;
+        if (vec) {
+            const float4* w4 = (const float4*)w;
+            const float4* x4 = (const float4*)xs;
+            const int n4 = d >> 2;
+            int k = lane;
+            for (; k + 32 < n4; k += 64) {
+                const float4 a = w4[k], b = w4[k + 32];
+                const float4 xa = x4[k], xb = x4[k + 32];
+                s0 = fmaf(xa.x, a.x, s0); s0 = fmaf(xa.y, a.y, s0); s0 = fmaf(xa.z, a.z, s0); s0 = fmaf(xa.w, a.w, s0);
+                s1 = fmaf(xb.x, b.x, s1); s1 = fmaf(xb.y, b.y, s1); s1 = fmaf(xb.z, b.z, s1); s1 = fmaf(xb.w, b.w, s1);
+            }
+            for (; k < n4; k += 32) {
+                const float4 a = w4[k];
+                const float4 xa = x4[k];
+                s0 = fmaf(xa.x, a.x, s0); s0 = fmaf(xa.y, a.y, s0); s0 = fmaf(xa.z, a.z, s0); s0 = fmaf(xa.w, a.w, s0);
+            }
+        } else {
+            for (int k = lane; k < d; k += 32) s0 = fmaf(xs[k], w[k], s0);
+        }
+        const float sum = warp_sum(s0 + s1);
         if (lane == 0) {
-            lg[e] = s;
-            if (logits_out) logits_out[(size_t)t * n_experts + e] = s;
+            lg[e] = sum;
+            if (logits_out) logits_out[(size_t)t * n_experts + e] = sum;
         }
     }
-    __syncwarp();
+    __syncthreads();
+    if (warp != 0) return;
     for (int slot = 0; slot < top_k; ++slot) {
         float best = -INFINITY;
         int best_e = 0x7fffffff;
@@ -103,16 +127,24 @@ SPITE_API int spite_moe_route(int dtype, const void* x, const float* w_router, i
     if (n_experts > MAX_EXPERTS) return SPITE_UNSUPPORTED;
     cudaStream_t st = (cudaStream_t)stream;
     if (n_tokens > 0) {
-        const int grid = (n_tokens + 3) / 4;
-        const size_t smem = (size_t)4 * n_experts * sizeof(float);
-        if (dtype == SPITE_DT_F32)
-            route_kernel<float><<<grid, 128, smem, st>>>((const float*)x, w_router, n_tokens, d, n_experts,
-                                                         top_k, expert_ids, weights, logits_out);
-        else if (dtype == SPITE_DT_BF16)
-            route_kernel<__nv_bfloat16><<<grid, 128, smem, st>>>((const __nv_bfloat16*)x, w_router, n_tokens, d,
-                                                                 n_experts, top_k, expert_ids, weights, logits_out);
-        else
+        const size_t smem = ((size_t)((d + 3) & ~3) + n_experts) * sizeof(float);
+        if (smem > 200 * 1024) return SPITE_UNSUPPORTED;
+        cudaError_t attr = cudaSuccess;
+        if (dtype == SPITE_DT_F32) {
+            if (smem > 48 * 1024)
+                attr = cudaFuncSetAttribute(route_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (attr != cudaSuccess) return SPITE_LAUNCH_FAILED;
+            route_kernel<float><<<n_tokens, 256, smem, st>>>((const float*)x, w_router, n_tokens, d, n_experts,
+                                                             top_k, expert_ids, weights, logits_out);
+        } else if (dtype == SPITE_DT_BF16) {
+            if (smem > 48 * 1024)
+                attr = cudaFuncSetAttribute(route_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (attr != cudaSuccess) return SPITE_LAUNCH_FAILED;
+            route_kernel<__nv_bfloat16><<<n_tokens, 256, smem, st>>>((const __nv_bfloat16*)x, w_router, n_tokens, d,
+                                                                     n_experts, top_k, expert_ids, weights, logits_out);
+        } else {
             return SPITE_BAD_ARG;
+        }
         if (cudaGetLastError() != cudaSuccess) return SPITE_LAUNCH_FAILED;
     }
     sort_by_expert_kernel<<<top_k, 1024, 0, st>>>(expert_ids, n_tokens, n_experts, top_k, offsets, sorted_rows);

@@ -29,6 +29,7 @@ LIBRARIES = {
     "elementwise": (["elementwise.cu"], []),
     "gemm_simt": (["gemm_simt.cu"], []),
     "gemm_skinny": (["gemm_skinny.cu"], []),
+    "gemm_tc": (["gemm_tc.cu"], []),
     "attention": (["attention.cu"], []),
     "attention_mma": (["attention_mma.cu"], []),
     "moe": (["moe.cu"], []),

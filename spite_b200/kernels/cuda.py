@@ -6,6 +6,7 @@ device or without the compiled libraries every call raises.
 from __future__ import annotations
 
 import ctypes as C
+import os
 
 import torch
 
@@ -83,6 +84,7 @@ class CudaKernels(KernelSet):
         self._libs = {}
         self.launches = 0          # kernels launched so far (for measurement reports)
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
+        self.use_tcgen05 = os.environ.get("SPITE_NO_TCGEN05", "") == ""
 
     # ------------------------------------------------------------------ helpers
     def _lib(self, name):
@@ -125,18 +127,45 @@ class CudaKernels(KernelSet):
         _check(st, "rms_norm")
 
     # ------------------------------------------------------------------ matrix products
-    def _gemm(self, p: GemmParams, what, max_rows_per_group):
-        """Pick the kernel: the tensor-core weight-streaming kernel for few bfloat16 rows,
-        else the CUDA-core kernel (always for float32)."""
-        if self.dtype == torch.bfloat16 and max_rows_per_group <= 64:
-            st = self._lib("gemm_skinny").spite_gemm_skinny(C.byref(p), int(max_rows_per_group), self._stream())
-            if st != -2:                       # -2: shape outside the kernel's domain, fall through
-                self.launches += 1
-                _check(st, what)
-                return
+    def _gemm(self, p: GemmParams, what, max_rows_per_group, gather_src=None):
+        """Pick the kernel.  bfloat16: up to 64 rows per group the weight-streaming mma.sync
+        kernel, above that the tcgen05 kernel (TMA-fed, accumulators in TMEM); float32 and
+        shapes those two refuse: the CUDA-core kernel.  `gather_src` is the tensor whose rows
+        `p.a_rows` gathers: the tcgen05 kernel wants contiguous rows, so they are gathered first."""
+        if self.dtype == torch.bfloat16:
+            if max_rows_per_group <= 64:
+                st = self._lib("gemm_skinny").spite_gemm_skinny(C.byref(p), int(max_rows_per_group), self._stream())
+                if st != -2:                       # -2: shape outside the kernel's domain, fall through
+                    self.launches += 1
+                    _check(st, what)
+                    return
+            elif self.use_tcgen05 and p.K % 8 == 0 and p.lda % 8 == 0:
+                keep = None
+                if gather_src is not None:
+                    keep = torch.empty_like(gather_src)
+                    st = self._lib("elementwise").spite_gather_rows(
+                        C.c_void_p(gather_src.data_ptr()), C.c_void_p(p.a_rows), C.c_void_p(keep.data_ptr()),
+                        gather_src.shape[0], C.c_longlong(gather_src.shape[1] * gather_src.element_size()),
+                        self._stream())
+                    self.launches += 1
+                    _check(st, "gather_rows")
+                    q = GemmParams.from_buffer_copy(p)
+                    q.A = keep.data_ptr()          # rows are in place now; a_rows only indexes the row scale
+                    p = q
+                st = self._lib("gemm_tc").spite_gemm_tc(C.byref(p), self._stream())
+                if st != -2:
+                    self.launches += 1
+                    _check(st, what + " (tcgen05)")
+                    return
+                if gather_src is not None:         # refused after all: undo the pointer swap
+                    p.A = gather_src.data_ptr()
         st = self._lib("gemm_simt").spite_gemm_simt(self._dt, C.byref(p), self._stream())
         self.launches += 1
         _check(st, what)
+
+    def gemm_tc_error(self) -> int:
+        """Error code left by a tcgen05 block that gave up waiting (0: none); clears it. Synchronises."""
+        return int(self._lib("gemm_tc").spite_gemm_tc_error())
 
     def linear(self, x, w, out, *, accumulate=False, row_scale=None):
         self._t(x, self.dtype, "x"); self._t(w, self.dtype, "w"); self._t(out, None, "out")
@@ -182,7 +211,7 @@ class CudaKernels(KernelSet):
                        a_rows=sorted_rows.data_ptr(), c_rows=None, group_offsets=offsets.data_ptr(),
                        row_scale=_ptr(row_scale), lda=K, ldc=F, w_group_stride=F2 * K,
                        n_groups=E, M=M, N=F, K=K, epilogue=EPI_SWIGLU, scale_by_a_row=1)
-        self._gemm(p, "grouped_linear_swiglu", M)
+        self._gemm(p, "grouped_linear_swiglu", M, gather_src=x)
 
     def grouped_linear_accumulate(self, a, w_down, sorted_rows, offsets, h):
         self._t(a, self.dtype, "a"); self._t(w_down, self.dtype, "w"); self._t(h, torch.float32, "h")
