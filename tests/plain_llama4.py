@@ -259,64 +259,93 @@ def lm_head(h, norm_w, head_w, eps):
 # ----------------------------------------------------------------------------
 # the model
 # ----------------------------------------------------------------------------
-def forward(cfg, tensors, token_ids, *, collect=None):
-    """Logits [T, vocab] (float32) of one whole sequence starting at position 0.
-    llama4.rs:116-279 restated for all positions at once.
-    `collect`, if a dict, receives the per-layer router margins."""
-    W = {k: v for k, v in _strip_prefix(tensors).items()}
-    g = lambda name: W[name].float()
+def _sizes(cfg):
     d = cfg["hidden_size"]
     nq = cfg["num_attention_heads"]
     nkv = cfg.get("num_key_value_heads", nq)
     hd = cfg.get("head_dim") or d // nq
-    eps = float(cfg.get("rms_norm_eps", 1e-5))
-    chunk = cfg.get("attention_chunk_size", 8192)
-    top_k = int(cfg.get("num_experts_per_tok", 1))
+    return d, nq, nkv, hd, float(cfg.get("rms_norm_eps", 1e-5))
+
+
+def attention_layer(cfg, W, L, x, pos, shared_kv=None):
+    """The mixer of layer L on normalised input x [T, d]: llama4.rs:129-207 without the
+    residual add.  Returns (output [T, d], (k, v)).  With `shared_kv` the layer reads
+    another layer's keys and values instead of making its own."""
+    d, nq, nkv, hd, eps = _sizes(cfg)
+    T = x.shape[0]
+    p = f"model.layers.{L}."
+    g = lambda name: W[name].float()
+    q = (x @ g(p + "self_attn.q_proj.weight").T).view(T, nq, hd)
+    k = (x @ g(p + "self_attn.k_proj.weight").T).view(T, nkv, hd)
+    v = (x @ g(p + "self_attn.v_proj.weight").T).view(T, nkv, hd)
+    if layer_uses_rope(cfg, L):
+        inv_freq = rotary_inv_freq(cfg, hd)
+        q = apply_rotary(q, pos, inv_freq)
+        k = apply_rotary(k, pos, inv_freq)
+        if cfg.get("use_qk_norm", True):
+            q, k = qk_norm(q, eps), qk_norm(k, eps)
+        mask = visible(pos, cfg.get("attention_chunk_size", 8192))
+    else:
+        if cfg.get("attn_temperature_tuning", True):
+            s = temperature_scale(pos, cfg.get("floor_scale", 8192), cfg.get("attn_scale", 0.1))
+            q = q * s[:, None, None]
+        mask = visible(pos, None)
+    if shared_kv is not None:
+        k, v = shared_kv
+    o = attention(q, k, v, mask).reshape(T, nq * hd)
+    return o @ g(p + "self_attn.o_proj.weight").T, (k, v)
+
+
+def feed_forward_layer(cfg, W, L, x, margins=None):
+    """The feed-forward of layer L on normalised input x: llama4.rs:212-271."""
+    p = f"model.layers.{L}."
+    g = lambda name: W[name].float()
+    if layer_is_moe(cfg, L):
+        ids, w, margin, _ = route(x, g(p + "feed_forward.router.weight"), int(cfg.get("num_experts_per_tok", 1)))
+        if margins is not None:
+            margins.append(margin)
+        y = routed_experts(x, ids, w, W[p + "feed_forward.experts.gate_up_proj"],
+                           W[p + "feed_forward.experts.down_proj"])
+        return y + shared_expert(x, g(p + "feed_forward.shared_expert.gate_proj.weight"),
+                                 g(p + "feed_forward.shared_expert.up_proj.weight"),
+                                 g(p + "feed_forward.shared_expert.down_proj.weight"))
+    return dense_swiglu(x, g(p + "feed_forward.gate_proj.weight"), g(p + "feed_forward.up_proj.weight"),
+                        g(p + "feed_forward.down_proj.weight"))
+
+
+def block(cfg, W, L, h, pos, shared_kv=None, margins=None):
+    """One layer on the residual stream: llama4.rs:126-127, 202-211, 272-274."""
+    eps = _sizes(cfg)[4]
+    p = f"model.layers.{L}."
+    o, kv = attention_layer(cfg, W, L, rms_norm(h, W[p + "input_layernorm.weight"].float(), eps), pos, shared_kv)
+    h = h + o
+    h = h + feed_forward_layer(cfg, W, L, rms_norm(h, W[p + "post_attention_layernorm.weight"].float(), eps), margins)
+    return h, kv
+
+
+def forward(cfg, tensors, token_ids, *, collect=None, order=None):
+    """Logits [T, vocab] (float32) of one whole sequence starting at position 0.
+    llama4.rs:116-279 restated for all positions at once.
+    `collect`, if a dict, receives the per-layer router margins.  `order`, a list of
+    (layer, cache id, writes), runs the layers in another order than 0..n-1; a run
+    that does not write reads the keys and values of the run that wrote its cache id."""
+    W = _strip_prefix(tensors)
+    eps = _sizes(cfg)[4]
     tokens = torch.as_tensor(token_ids, dtype=torch.long)
     T = tokens.numel()
     pos = torch.arange(T)
-    inv_freq = rotary_inv_freq(cfg, hd)
-
     h = embed(W["model.embed_tokens.weight"], tokens)
-    margins = []
-    for L in range(cfg["num_hidden_layers"]):
-        p = f"model.layers.{L}."
-        x = rms_norm(h, g(p + "input_layernorm.weight"), eps)
-        q = (x @ g(p + "self_attn.q_proj.weight").T).view(T, nq, hd)
-        k = (x @ g(p + "self_attn.k_proj.weight").T).view(T, nkv, hd)
-        v = (x @ g(p + "self_attn.v_proj.weight").T).view(T, nkv, hd)
-        if layer_uses_rope(cfg, L):
-            q = apply_rotary(q, pos, inv_freq)
-            k = apply_rotary(k, pos, inv_freq)
-            if cfg.get("use_qk_norm", True):
-                q, k = qk_norm(q, eps), qk_norm(k, eps)
-            mask = visible(pos, chunk)
-        else:
-            if cfg.get("attn_temperature_tuning", True):
-                s = temperature_scale(pos, cfg.get("floor_scale", 8192), cfg.get("attn_scale", 0.1))
-                q = q * s[:, None, None]
-            mask = visible(pos, None)
-        o = attention(q, k, v, mask).reshape(T, nq * hd)
-        h = h + o @ g(p + "self_attn.o_proj.weight").T
-
-        x = rms_norm(h, g(p + "post_attention_layernorm.weight"), eps)
-        if layer_is_moe(cfg, L):
-            ids, w, margin, _ = route(x, g(p + "feed_forward.router.weight"), top_k)
-            margins.append(margin)
-            y = routed_experts(x, ids, w, W[p + "feed_forward.experts.gate_up_proj"],
-                               W[p + "feed_forward.experts.down_proj"])
-            y = y + shared_expert(x, g(p + "feed_forward.shared_expert.gate_proj.weight"),
-                                  g(p + "feed_forward.shared_expert.up_proj.weight"),
-                                  g(p + "feed_forward.shared_expert.down_proj.weight"))
-        else:
-            y = dense_swiglu(x, g(p + "feed_forward.gate_proj.weight"),
-                             g(p + "feed_forward.up_proj.weight"),
-                             g(p + "feed_forward.down_proj.weight"))
-        h = h + y
+    margins, caches = [], {}
+    if order is None:
+        order = [(L, L, True) for L in range(cfg["num_hidden_layers"])]
+    for L, cache_id, writes in order:
+        h, kv = block(cfg, W, L, h, pos, None if writes else caches[cache_id], margins)
+        if writes:
+            caches[cache_id] = kv
     head = W["model.embed_tokens.weight"] if cfg.get("tie_word_embeddings", False) else W["lm_head.weight"]
     if collect is not None:
         collect["router_margins"] = torch.stack(margins) if margins else torch.zeros(0, T)
-    return lm_head(h, g("model.norm.weight"), head, eps)
+    return lm_head(h, W["model.norm.weight"].float(), head, eps)
 
 
 def generate_greedy(cfg, tensors, prompt, n_new):
