@@ -120,3 +120,29 @@ def test_whole_model_is_causal_and_chunks_forget(name, tmp_path):
     n_moe = sum(plain.layer_is_moe(cfg, L) for L in range(cfg["num_hidden_layers"]))
     assert info["router_margins"].shape == (n_moe, 40)
     assert len(plain.generate_greedy(cfg, tensors, toks[:6], 3)) == 3
+
+
+def test_parts_match_the_reference_projects_generic_c_kernel():
+    """Outputs of giveen/spite's generic C ops (kernels/generic/generic/ops.c: rms_norm, matmul,
+    ffn, attention), stored by tests/golden/make_golden.py, against the plain functions."""
+    import json
+    import sys
+    from pathlib import Path
+    golden = Path(__file__).parent / "golden"
+    sys.path.insert(0, str(golden))
+    from make_golden import SIZES as s, golden_inputs
+    stored = json.loads((golden / "generic_ops.json").read_text())
+    assert stored["sizes"] == s
+    g, i = stored["outputs"], golden_inputs(stored["seed"])
+    diff = lambda a, b: float((torch.tensor(a) - b).abs().max())
+    assert diff(g["rms_norm"], plain.rms_norm(i["x"], i["gain"], s["eps"])) < 2e-6
+    assert diff(g["matmul"], i["x"] @ i["w"].T) < 2e-6
+    assert diff(g["ffn"], plain.dense_swiglu(i["x"], i["w_gate"], i["w_up"], i["w_down"])) < 5e-6
+    cfg = dict(hidden_size=s["d"], num_attention_heads=s["nq"], num_key_value_heads=s["nkv"], head_dim=s["hd"],
+               rms_norm_eps=s["eps"], rope_theta=s["theta"], use_qk_norm=True, attention_chunk_size=64,
+               no_rope_layers=[1])
+    W = {"model.layers.0.self_attn.q_proj.weight": i["wq"], "model.layers.0.self_attn.k_proj.weight": i["wk"],
+         "model.layers.0.self_attn.v_proj.weight": i["wv"], "model.layers.0.self_attn.o_proj.weight": i["wo"]}
+    out, (k, v) = plain.attention_layer(cfg, W, 0, i["x"], torch.arange(s["T"]))
+    assert diff(g["attention"], out) < 5e-6
+    assert diff(g["values_row_3"], v[3].reshape(-1)) < 2e-6
