@@ -1,24 +1,29 @@
-// Matrix product for few tokens (decode): y[M, N] = x[M, K] W[N, K]^T with M <= 64
+// Matrix product for few tokens (decode): y[M, N] = x[M, K] W[N, K]^T with at most 64
 // rows per group, bfloat16 inputs, float32 sums.
 //
-// With few tokens the product is bound by reading W once from HBM.  The weight
-// rows are the 16-row operand of mma.sync.m16n8k16 and the tokens its 8 columns,
-// so 8 tokens cost one instruction per 16x16 weight tile.  Each lane fetches 16
-// contiguous bytes of a weight row straight into its fragment registers: the k
-// index inside a 32-wide step is permuted, identically for W and x, which leaves
-// every dot product unchanged.  A block of 8 warps owns 32 weight rows (or 16 gate
-// and 16 up rows for the SwiGLU epilogue) and splits K among its warps; the partial
-// sums meet in shared memory, where the epilogue runs.  An output element is summed
-// in an order fixed by K alone, whatever else is in the batch.
+// With few tokens the product is bound by reading W once from HBM.  The weight rows are
+// the 16-row operand of mma.sync.m16n8k16 and the tokens its 8 columns, so 8 tokens cost
+// one instruction per 16x16 weight tile.  Each lane fetches 16 contiguous bytes of a
+// weight row straight into its fragment registers: the k index inside a 32-wide step is
+// permuted, identically for W and x, which leaves every dot product unchanged.
 //
-// Grouped form (experts): blockIdx.y is the group; its tokens are
-// rows [off[g], off[g+1]) of the sorted order, gathered through a_rows.
+// The kernel is persistent: a fixed number of blocks walk the work items (group, tile of
+// 32 weight rows; 16 gate + 16 up rows for the SwiGLU epilogue) with a stride of the grid
+// size.  A block's 8 warps split K; each warp keeps a ring of U steps of weight and token
+// fragments in flight, and the first steps of the next item are requested before the
+// current item's partial sums meet in shared memory, so the stream from HBM keeps
+// flowing through the epilogue.
+// An output element is summed in an order fixed by K alone, whatever else is in the batch.
+//
+// Grouped form (experts): the tokens of group g are rows [off[g], off[g+1]) of the sorted
+// order, gathered through a_rows; groups without tokens are skipped on the device.
 #include "gemm.cuh"
 
 namespace {
 
 constexpr int WARPS = 8;
 constexpr int NFRAG = 2;          // 16-row weight fragments per warp
+constexpr int MAX_GROUPS = 1024;
 
 __device__ __forceinline__ void mma16816(float (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
                                          unsigned b0, unsigned b1) {
@@ -34,52 +39,105 @@ __device__ __forceinline__ uint4 ld_stream(const void* p) {     // read once: do
     return v;
 }
 
+struct Item {                     // one work item of a block
+    int group, row_lo, m, tile;
+};
+
 template <int NT, int U, int EPI>
-__global__ void __launch_bounds__(WARPS * 32) gemm_skinny_kernel(const GemmParams p) {
+__global__ void __launch_bounds__(WARPS * 32, (NT <= 1 ? 2 : 1)) gemm_skinny_kernel(const GemmParams p) {
     constexpr bool DUAL = (EPI == EPI_SWIGLU);
-    constexpr int ROWS = DUAL ? 16 : 32;                         // output columns (weight rows) per block
+    constexpr int ROWS = DUAL ? 16 : 32;                         // output columns (weight rows) per item
     constexpr int TOK = NT * 8;
     extern __shared__ float red[];                               // [WARPS][NFRAG*16][TOK]
+    __shared__ int active_s[MAX_GROUPS];
+    __shared__ int n_active_s;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, c = lane & 3;
-    const int group = blockIdx.y;
-    int row_lo = 0, m = p.M;
-    if (p.group_offsets) {
-        row_lo = p.group_offsets[group];
-        m = p.group_offsets[group + 1] - row_lo;
-    }
-    if (m <= 0) return;
-    const int n0 = blockIdx.x * ROWS;
-    const __nv_bfloat16* W = (const __nv_bfloat16*)p.W + (size_t)group * p.w_group_stride;
-    const __nv_bfloat16* X = (const __nv_bfloat16*)p.A;
+    const int n_tiles = (p.N + ROWS - 1) / ROWS;
 
-    // weight row pointers of this lane: fragment f, rows g and g+8
-    const __nv_bfloat16* wrow[NFRAG][2];
-#pragma unroll
-    for (int f = 0; f < NFRAG; ++f)
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            int r = DUAL ? (n0 + g + 8 * h + (f ? p.N : 0)) : (n0 + 16 * f + g + 8 * h);
-            const int last = DUAL ? (f ? 2 * p.N - 1 : p.N - 1) : p.N - 1;
-            wrow[f][h] = W + (size_t)min(r, last) * p.K + 8 * c;
+    // groups that have tokens
+    if (threadIdx.x == 0) {
+        int n = 0;
+        if (p.group_offsets) {
+            for (int e = 0; e < p.n_groups; ++e)
+                if (p.group_offsets[e + 1] > p.group_offsets[e]) active_s[n++] = e;
+        } else {
+            active_s[n++] = 0;
         }
+        n_active_s = n;
+    }
+    __syncthreads();
+    const int total = n_active_s * n_tiles;
 
-    const int steps = p.K >> 5;
-    const int s_begin = (int)((long long)steps * warp / WARPS), s_end = (int)((long long)steps * (warp + 1) / WARPS);
-
-    for (int t0 = 0; t0 < m; t0 += TOK) {                        // one pass unless a group has more than TOK tokens
-        const __nv_bfloat16* xrow[NT];
+    auto item_at = [&](int i) {
+        Item it;
+        it.group = active_s[i / n_tiles];
+        it.tile = i % n_tiles;
+        it.row_lo = p.group_offsets ? p.group_offsets[it.group] : 0;
+        it.m = p.group_offsets ? p.group_offsets[it.group + 1] - it.row_lo : p.M;
+        return it;
+    };
+    const __nv_bfloat16* X = (const __nv_bfloat16*)p.A;
+    auto weight_rows = [&](const Item& it, const __nv_bfloat16* (&wrow)[NFRAG][2]) {
+        const __nv_bfloat16* W = (const __nv_bfloat16*)p.W + (size_t)it.group * p.w_group_stride;
+        const int n0 = it.tile * ROWS;
+#pragma unroll
+        for (int f = 0; f < NFRAG; ++f)
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int r = DUAL ? (n0 + g + 8 * h + (f ? p.N : 0)) : (n0 + 16 * f + g + 8 * h);
+                const int last = DUAL ? (f ? 2 * p.N - 1 : p.N - 1) : p.N - 1;
+                wrow[f][h] = W + (size_t)min(r, last) * p.K + 8 * c;
+            }
+    };
+    auto token_rows = [&](const Item& it, const __nv_bfloat16* (&xrow)[NT]) {
 #pragma unroll
         for (int j = 0; j < NT; ++j) {
-            const int t = t0 + 8 * j + g;
-            if (t < m) {
-                const int li = row_lo + t;
+            const int t = 8 * j + g;
+            if (t < it.m) {
+                const int li = it.row_lo + t;
                 xrow[j] = X + (size_t)(p.a_rows ? p.a_rows[li] : li) * p.lda + 8 * c;
             } else {
                 xrow[j] = nullptr;
             }
         }
+    };
+
+    // this warp's share of the 32-wide k steps
+    const int steps = p.K >> 5;
+    const int s_begin = (int)((long long)steps * warp / WARPS), s_end = (int)((long long)steps * (warp + 1) / WARPS);
+    const int n_my = s_end - s_begin;
+
+    int i_cur = blockIdx.x;
+    if (i_cur >= total) return;
+    Item cur = item_at(i_cur);
+    const __nv_bfloat16* wrow[NFRAG][2];
+    const __nv_bfloat16* xrow[NT];
+    uint4 wbuf[U][NFRAG][2];
+    uint4 xbuf[U][NT];
+
+    // first U steps of an item into the ring
+    auto fill_ring = [&]() {
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            if (u < n_my) {
+                const size_t off = (size_t)(s_begin + u) * 32;
+#pragma unroll
+                for (int f = 0; f < NFRAG; ++f)
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) wbuf[u][f][h] = ld_stream(wrow[f][h] + off);
+#pragma unroll
+                for (int j = 0; j < NT; ++j)
+                    xbuf[u][j] = xrow[j] ? *(const uint4*)(xrow[j] + off) : make_uint4(0, 0, 0, 0);
+            }
+        }
+    };
+    weight_rows(cur, wrow);
+    token_rows(cur, xrow);
+    fill_ring();
+
+    for (; i_cur < total; i_cur += gridDim.x) {
         float acc[NFRAG][NT][4];
 #pragma unroll
         for (int f = 0; f < NFRAG; ++f)
@@ -88,32 +146,26 @@ __global__ void __launch_bounds__(WARPS * 32) gemm_skinny_kernel(const GemmParam
 #pragma unroll
                 for (int e = 0; e < 4; ++e) acc[f][j][e] = 0.f;
 
-        uint4 wbuf[U][NFRAG][2];
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const int s = min(s_begin + u, steps - 1);
-#pragma unroll
-            for (int f = 0; f < NFRAG; ++f)
-#pragma unroll
-                for (int h = 0; h < 2; ++h) wbuf[u][f][h] = ld_stream(wrow[f][h] + (size_t)s * 32);
-        }
-        for (int s0 = s_begin; s0 < s_end; s0 += U) {
+        for (int i0 = 0; i0 < n_my; i0 += U) {
 #pragma unroll
             for (int u = 0; u < U; ++u) {
-                const int s = s0 + u;
-                if (s < s_end) {
-                    uint4 xv[NT];
-#pragma unroll
-                    for (int j = 0; j < NT; ++j)
-                        xv[j] = xrow[j] ? *(const uint4*)(xrow[j] + (size_t)s * 32) : make_uint4(0, 0, 0, 0);
-                    uint4 w[NFRAG][2];
+                const int i = i0 + u;
+                if (i < n_my) {
+                    uint4 w[NFRAG][2], xv[NT];
 #pragma unroll
                     for (int f = 0; f < NFRAG; ++f) { w[f][0] = wbuf[u][f][0]; w[f][1] = wbuf[u][f][1]; }
-                    const int sn = min(s + U, steps - 1);
 #pragma unroll
-                    for (int f = 0; f < NFRAG; ++f)
+                    for (int j = 0; j < NT; ++j) xv[j] = xbuf[u][j];
+                    if (i + U < n_my) {                          // refill this ring slot, U steps ahead
+                        const size_t off = (size_t)(s_begin + i + U) * 32;
 #pragma unroll
-                        for (int h = 0; h < 2; ++h) wbuf[u][f][h] = ld_stream(wrow[f][h] + (size_t)sn * 32);
+                        for (int f = 0; f < NFRAG; ++f)
+#pragma unroll
+                            for (int h = 0; h < 2; ++h) wbuf[u][f][h] = ld_stream(wrow[f][h] + off);
+#pragma unroll
+                        for (int j = 0; j < NT; ++j)
+                            xbuf[u][j] = xrow[j] ? *(const uint4*)(xrow[j] + off) : make_uint4(0, 0, 0, 0);
+                    }
 #pragma unroll
                     for (int f = 0; f < NFRAG; ++f)
 #pragma unroll
@@ -123,6 +175,14 @@ __global__ void __launch_bounds__(WARPS * 32) gemm_skinny_kernel(const GemmParam
                         }
                 }
             }
+        }
+        // the next item's first steps go out now and travel while this item's sums are reduced
+        const Item done = cur;
+        if (i_cur + gridDim.x < total) {
+            cur = item_at(i_cur + gridDim.x);
+            weight_rows(cur, wrow);
+            token_rows(cur, xrow);
+            fill_ring();
         }
         // partial sums of this warp: red[warp][fragment row][token]
         __syncthreads();
@@ -138,7 +198,8 @@ __global__ void __launch_bounds__(WARPS * 32) gemm_skinny_kernel(const GemmParam
             }
         __syncthreads();
         // epilogue: one output element per thread and round, weight rows fastest
-        const int n_tok = min(TOK, m - t0);
+        const int n0 = done.tile * ROWS;
+        const int n_tok = min(TOK, done.m);
         for (int idx = threadIdx.x; idx < ROWS * n_tok; idx += WARPS * 32) {
             const int r = idx % ROWS, t = idx / ROWS;
             const int n = n0 + r;
@@ -149,7 +210,7 @@ __global__ void __launch_bounds__(WARPS * 32) gemm_skinny_kernel(const GemmParam
                 v += red[((size_t)w8 * NFRAG * 16 + r) * TOK + t];
                 if (DUAL) v2 += red[((size_t)w8 * NFRAG * 16 + 16 + r) * TOK + t];
             }
-            const int li = row_lo + t0 + t;
+            const int li = done.row_lo + t;
             const int arow = p.a_rows ? p.a_rows[li] : li;
             const int crow = p.c_rows ? p.c_rows[li] : li;
             const float sc = p.row_scale ? p.row_scale[p.scale_by_a_row ? arow : li] : 1.f;
@@ -163,15 +224,15 @@ __global__ void __launch_bounds__(WARPS * 32) gemm_skinny_kernel(const GemmParam
 }
 
 template <int NT, int U>
-int launch_nt(const GemmParams& p, cudaStream_t st) {
+int launch_nt(const GemmParams& p, int n_blocks, cudaStream_t st) {
     const int rows = p.epilogue == EPI_SWIGLU ? 16 : 32;
-    dim3 grid((p.N + rows - 1) / rows, p.group_offsets ? p.n_groups : 1);
-    if (grid.y > 65535) return SPITE_UNSUPPORTED;
+    const long long tiles = (long long)((p.N + rows - 1) / rows) * (p.group_offsets ? p.n_groups : 1);
+    const int grid = (int)(tiles < n_blocks ? tiles : n_blocks);
     const size_t smem = (size_t)WARPS * NFRAG * 16 * NT * 8 * sizeof(float);
 #define SPITE_SKINNY_CASE(E)                                                                              \
     case E: {                                                                                             \
         auto k = gemm_skinny_kernel<NT, U, E>;                                                            \
-        if (smem > 48 * 1024 &&                                                                           \
+        if (smem > 44 * 1024 &&                                                                           \
             cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) \
             return SPITE_LAUNCH_FAILED;                                                                   \
         k<<<grid, WARPS * 32, smem, st>>>(p);                                                             \
@@ -190,20 +251,21 @@ int launch_nt(const GemmParams& p, cudaStream_t st) {
 
 }  // namespace
 
-int gemm_check(const GemmParams* p);
-
 // `max_rows_per_group`: an upper bound on the tokens of any group (M for one group).
-SPITE_API int spite_gemm_skinny(const GemmParams* p, int max_rows_per_group, void* stream) {
+// `n_blocks`: twice the number of multiprocessors; the launch uses as many blocks as stay resident
+// (two per multiprocessor up to 8 tokens, one above), fewer if there is less work.
+SPITE_API int spite_gemm_skinny(const GemmParams* p, int max_rows_per_group, int n_blocks, void* stream) {
     if (!p || !p->A || !p->W || !p->C) return SPITE_BAD_ARG;
-    if (p->M < 0 || p->N <= 0 || p->K <= 0 || p->lda < p->K || p->ldc < p->N) return SPITE_BAD_ARG;
+    if (p->M < 0 || p->N <= 0 || p->K <= 0 || p->lda < p->K || p->ldc < p->N || n_blocks < 1) return SPITE_BAD_ARG;
     if (p->group_offsets ? p->n_groups < 1 : p->n_groups != 1) return SPITE_BAD_ARG;
     if (p->K % 32 || p->lda % 8) return SPITE_UNSUPPORTED;                 // 16-byte loads, 32-wide steps
     if (((uintptr_t)p->A | (uintptr_t)p->W) & 15) return SPITE_UNSUPPORTED;
-    if (max_rows_per_group < 1 || max_rows_per_group > 64) return SPITE_UNSUPPORTED;
+    if (max_rows_per_group < 1 || max_rows_per_group > 64 || p->n_groups > MAX_GROUPS) return SPITE_UNSUPPORTED;
     if (p->M == 0) return SPITE_OK;
     cudaStream_t st = (cudaStream_t)stream;
-    if (max_rows_per_group <= 8) return launch_nt<1, 4>(*p, st);
-    if (max_rows_per_group <= 16) return launch_nt<2, 4>(*p, st);
-    if (max_rows_per_group <= 32) return launch_nt<4, 2>(*p, st);
-    return launch_nt<8, 2>(*p, st);
+    const int half = (n_blocks + 1) / 2;                                   // kernels that fit once per multiprocessor
+    if (max_rows_per_group <= 8) return launch_nt<1, 4>(*p, n_blocks, st);
+    if (max_rows_per_group <= 16) return launch_nt<2, 4>(*p, half, st);
+    if (max_rows_per_group <= 32) return launch_nt<4, 2>(*p, half, st);
+    return launch_nt<8, 2>(*p, half, st);
 }

@@ -134,7 +134,8 @@ class CudaKernels(KernelSet):
         `p.a_rows` gathers: the tcgen05 kernel wants contiguous rows, so they are gathered first."""
         if self.dtype == torch.bfloat16:
             if max_rows_per_group <= 64:
-                st = self._lib("gemm_skinny").spite_gemm_skinny(C.byref(p), int(max_rows_per_group), self._stream())
+                st = self._lib("gemm_skinny").spite_gemm_skinny(C.byref(p), int(max_rows_per_group), 2 * self.sm_count,
+                                                                self._stream())
                 if st != -2:                       # -2: shape outside the kernel's domain, fall through
                     self.launches += 1
                     _check(st, what)
@@ -270,7 +271,14 @@ class CudaKernels(KernelSet):
                 longest = batch.context_bucket if window.kind == "full" else min(batch.context_bucket, window.size)
             tiles = -(-longest // 16) + 1
             base = n_blocks * c.num_kv_heads
-            splits = max(1, min(-(-2 * self.sm_count // base), tiles // 8, 128))
+            # key splits: fill the resident blocks (three per multiprocessor) once if the step is
+            # small, else pick the split count whose last wave is fullest
+            slots = 3 * self.sm_count
+            if base <= slots:
+                splits = slots // base
+            else:
+                splits = max(range(1, 5), key=lambda s: (base * s / slots) / -(-base * s // slots))
+            splits = max(1, min(splits, tiles // 8, 128))
             o_part = ml_part = None
             if splits > 1:
                 o_part = torch.empty((batch.n_tokens, num_heads, splits, c.head_dim), dtype=torch.float32,
