@@ -1,20 +1,26 @@
 // Matrix product for many tokens (prefill) on the fifth-generation tensor cores:
 //   C[M, N] (=|+=) epilogue( A[M, K] W[N, K]^T ),  bfloat16 inputs, float32 sums in TMEM.
 //
-// One block computes a 128 x 128 tile (two accumulators for the SwiGLU epilogue: gate and
-// up rows of W).  Roles by warp:
-//   warp 0    one lane issues TMA loads (cp.async.bulk.tensor) of the A and W tiles of a
-//             64-wide k block into a ring of shared-memory stages (128-byte swizzle);
-//   warp 1    allocates TMEM; one lane issues tcgen05.mma (128x128x16, operands straight
-//             from shared memory through matrix descriptors) and commits each stage back
-//             to the loader, the finished accumulator to the epilogue;
-//   warps 2-5 read the accumulator with tcgen05.ld (one row per thread) and apply the
-//             epilogue: store, add to the float32 residual stream (optionally scattered
-//             through c_rows), or SwiGLU with a per-row scale.
-// Stages and roles hand over through mbarriers.  Every wait is bounded: after about two
-// seconds a waiter raises an abort flag that all roles poll, records an error code that
-// the host can read with spite_gemm_tc_error(), and the block leaves through the common
-// exit, where TMEM is freed.
+// Persistent blocks (one per multiprocessor) walk the output tiles of 128 rows x BN
+// columns, BN = 64..256 chosen on the host so that the last wave of tiles is full.  Roles:
+//   warp 0    one lane issues TMA loads (cp.async.bulk.tensor, 128-byte swizzle) of the A
+//             tile and the two halves of the W tile of a 64-wide k block into a ring of four
+//             shared-memory stages;
+//   warp 1    allocates TMEM (512 columns: two accumulators of up to 256); one lane issues
+//             tcgen05.mma 128 x BN x 16, operands straight from shared memory through matrix
+//             descriptors, commits each stage back to the loader and each finished
+//             accumulator to the epilogue;
+//   warps 2-5 read an accumulator with tcgen05.ld (one row per thread) and apply the
+//             epilogue while the tensor cores fill the other accumulator.
+// The two halves of the W tile are the next BN/2 output columns, or, for the SwiGLU
+// epilogue, BN/2 gate rows and the matching BN/2 up rows; the main loop is the same.
+// Epilogues: store, store float32, add to the float32 residual stream (optionally
+// scattered through c_rows), SwiGLU with a per-row scale.
+//
+// Stages, accumulators and roles hand over through mbarriers.  Every wait is bounded:
+// after about two seconds a waiter raises an abort flag that all roles poll, records an
+// error code that the host reads with spite_gemm_tc_error(), waits for its own copies in
+// flight, and the block leaves through the common exit, where TMEM is freed.
 //
 // Rows of A are contiguous (a grouped product gets its rows gathered into expert order
 // beforehand); `a_rows`, if set, only indexes `row_scale`.  Edges in M, N and K are
@@ -24,8 +30,11 @@
 
 namespace {
 
-constexpr int BM = 128, BN = 128, BK = 64, UMMA_K = 16;
-constexpr int TILE_BYTES = BM * BK * 2;                  // 16 KiB, one operand tile of one stage
+constexpr int BM = 128, BK = 64, UMMA_K = 16, STAGES = 4;
+constexpr int A_BYTES = BM * BK * 2;                     // 16 KiB
+constexpr int B_BYTES = 256 * BK * 2;                    // room for 256 weight rows, 32 KiB
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int ACC_COLS = 256, TMEM_COLS = 512;
 constexpr int THREADS = 192;
 constexpr long long WAIT_CYCLES = 4000000000ll;          // about two seconds
 
@@ -39,6 +48,9 @@ __device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
 }
 __device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(unsigned bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ bool mbar_try(unsigned bar, unsigned parity) {
     unsigned ok;
@@ -108,37 +120,46 @@ __host__ __device__ constexpr unsigned make_idesc(int m, int n) {
 }
 
 struct SharedTail {
-    unsigned long long full[8];
-    unsigned long long empty[8];
-    unsigned long long acc_full;
+    unsigned long long full[STAGES];
+    unsigned long long empty[STAGES];
+    unsigned long long acc_full[2];
+    unsigned long long acc_empty[2];
     unsigned tmem_base;
     int abort_flag;
 };
 
-template <int EPI, int STAGES>
+// The tile with running index `idx`: column tile idx / row_tiles, row tile idx % row_tiles.
+struct Tile {
+    int group, row0, rows, n0;
+    bool ok;
+};
+__device__ __forceinline__ Tile tile_at(const GemmParams& p, int idx, int row_tiles, int cols_per_tile) {
+    Tile t;
+    t.n0 = (idx / row_tiles) * cols_per_tile;
+    t.ok = locate_row_tile(p, idx % row_tiles, BM, t.group, t.row0, t.rows);
+    return t;
+}
+
+// `bnh`: weight rows per half of the W tile (32, 64, 96 or 128); the MMA is 128 x 2 bnh x 16.
+template <int EPI>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-               const GemmParams p) {
+               const GemmParams p, const int bnh, const int row_tiles, const int total_tiles) {
     constexpr bool DUAL = (EPI == EPI_SWIGLU);
-    constexpr int OPERANDS = DUAL ? 3 : 2;
-    constexpr int STAGE_BYTES = OPERANDS * TILE_BYTES;
-    constexpr int TMEM_COLS = DUAL ? 2 * BN : BN;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     SharedTail* tail = (SharedTail*)(smem + STAGES * STAGE_BYTES);
 
-    int group, row0, rows;
-    const bool have_tile = locate_row_tile(p, blockIdx.y, BM, group, row0, rows);
-    if (!have_tile) return;                                   // whole block, before any barrier
-    const int n0 = blockIdx.x * BN;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int num_kb = (p.K + BK - 1) / BK;
     const int w_rows = DUAL ? 2 * p.N : p.N;
+    const int cols_per_tile = DUAL ? bnh : 2 * bnh;          // output columns of one tile
+    const unsigned stage_tx = A_BYTES + 2 * bnh * BK * 2;
     volatile int* abort_flag = &tail->abort_flag;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(smem_u32(&tail->full[s]), 1); mbar_init(smem_u32(&tail->empty[s]), 1); }
-        mbar_init(smem_u32(&tail->acc_full), 1);
+        for (int b = 0; b < 2; ++b) { mbar_init(smem_u32(&tail->acc_full[b]), 1); mbar_init(smem_u32(&tail->acc_empty[b]), 4); }
         tail->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
@@ -155,24 +176,31 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (warp == 0) {
         if (lane == 0) {
             // ---- loader
-            int issued = 0;
-            for (int kb = 0; kb < num_kb; ++kb) {
-                const int s = kb % STAGES;
-                const unsigned ph = (kb / STAGES) & 1;
-                if (!mbar_wait(smem_u32(&tail->empty[s]), ph ^ 1, abort_flag, 1)) break;
-                const unsigned bar = smem_u32(&tail->full[s]);
-                const unsigned dst = smem_u32(smem + s * STAGE_BYTES);
-                mbar_expect_tx(bar, STAGE_BYTES);
-                tma_load_2d(dst, &map_a, kb * BK, row0, bar);
-                tma_load_2d(dst + TILE_BYTES, &map_w, kb * BK, group * w_rows + n0, bar);
-                if (DUAL) tma_load_2d(dst + 2 * TILE_BYTES, &map_w, kb * BK, group * w_rows + p.N + n0, bar);
-                issued = kb + 1;
+            int it = 0;                                       // k blocks issued so far, over all tiles
+            bool ok = true;
+            for (int idx = blockIdx.x; idx < total_tiles && ok; idx += gridDim.x) {
+                const Tile t = tile_at(p, idx, row_tiles, cols_per_tile);
+                if (!t.ok) continue;
+                const int wy0 = t.group * w_rows + t.n0;
+                const int wy1 = DUAL ? t.group * w_rows + p.N + t.n0 : wy0 + bnh;
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const unsigned ph = (it / STAGES) & 1;
+                    ok = mbar_wait(smem_u32(&tail->empty[s]), ph ^ 1, abort_flag, 1);
+                    if (!ok) break;
+                    const unsigned bar = smem_u32(&tail->full[s]);
+                    const unsigned dst = smem_u32(smem + s * STAGE_BYTES);
+                    mbar_expect_tx(bar, stage_tx);
+                    tma_load_2d(dst, &map_a, kb * BK, t.row0, bar);
+                    tma_load_2d(dst + A_BYTES, &map_w, kb * BK, wy0, bar);
+                    tma_load_2d(dst + A_BYTES + bnh * BK * 2, &map_w, kb * BK, wy1, bar);
+                }
             }
             if (*abort_flag) {
                 // copies in flight must land before the block gives its shared memory back
-                for (int kb = max(0, issued - STAGES); kb < issued; ++kb) {
+                for (int j = max(0, it - STAGES); j < it; ++j) {
                     const long long t0 = clock64();
-                    while (!mbar_try(smem_u32(&tail->full[kb % STAGES]), (kb / STAGES) & 1) &&
+                    while (!mbar_try(smem_u32(&tail->full[j % STAGES]), (j / STAGES) & 1) &&
                            clock64() - t0 < WAIT_CYCLES) {}
                 }
             }
@@ -180,36 +208,48 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     } else if (warp == 1) {
         if (lane == 0) {
             // ---- tensor-core issue
-            constexpr unsigned IDESC = make_idesc(BM, BN);
+            const unsigned idesc = make_idesc(BM, 2 * bnh);
+            int it = 0, lt = 0;
             bool ok = true;
-            for (int kb = 0; kb < num_kb && ok; ++kb) {
-                const int s = kb % STAGES;
-                const unsigned ph = (kb / STAGES) & 1;
-                ok = mbar_wait(smem_u32(&tail->full[s]), ph, abort_flag, 2);
+            for (int idx = blockIdx.x; idx < total_tiles && ok; idx += gridDim.x) {
+                const Tile t = tile_at(p, idx, row_tiles, cols_per_tile);
+                if (!t.ok) continue;
+                const int buf = lt & 1;
+                ok = mbar_wait(smem_u32(&tail->acc_empty[buf]), ((lt >> 1) & 1) ^ 1, abort_flag, 4);
                 if (!ok) break;
                 tc_fence_after();
-                const unsigned a_addr = smem_u32(smem + s * STAGE_BYTES);
+                const unsigned d_tmem = tmem + buf * ACC_COLS;
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    ok = mbar_wait(smem_u32(&tail->full[s]), (it / STAGES) & 1, abort_flag, 2);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const unsigned a_addr = smem_u32(smem + s * STAGE_BYTES);
 #pragma unroll
-                for (int k = 0; k < BK / UMMA_K; ++k) {
-                    const unsigned long long a_desc = smem_desc(a_addr + k * UMMA_K * 2);
-                    const unsigned long long b_desc = smem_desc(a_addr + TILE_BYTES + k * UMMA_K * 2);
-                    const unsigned acc = (kb > 0 || k > 0) ? 1u : 0u;
-                    tc_mma(tmem, a_desc, b_desc, IDESC, acc);
-                    if (DUAL) tc_mma(tmem + BN, a_desc, smem_desc(a_addr + 2 * TILE_BYTES + k * UMMA_K * 2), IDESC, acc);
+                    for (int k = 0; k < BK / UMMA_K; ++k)
+                        tc_mma(d_tmem, smem_desc(a_addr + k * UMMA_K * 2), smem_desc(a_addr + A_BYTES + k * UMMA_K * 2),
+                               idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    tc_commit(smem_u32(&tail->empty[s]));      // the stage is free once these MMAs have read it
                 }
-                tc_commit(smem_u32(&tail->empty[s]));          // the stage is free once these MMAs have read it
+                if (ok) tc_commit(smem_u32(&tail->acc_full[buf]));   // this accumulator is complete
+                ++lt;
             }
-            if (ok) tc_commit(smem_u32(&tail->acc_full));       // the accumulator is complete
         }
     } else {
         // ---- epilogue: warp w may read TMEM lanes [32 (w % 4), 32 (w % 4) + 32)
         const int quarter = warp & 3;
         const int r = quarter * 32 + lane;
-        const bool got = mbar_wait(smem_u32(&tail->acc_full), 0, abort_flag, 3);
-        tc_fence_after();
-        if (got) {
-            const int li = row0 + r;
-            const bool row_ok = r < rows;
+        int lt = 0;
+        bool ok = true;
+        for (int idx = blockIdx.x; idx < total_tiles && ok; idx += gridDim.x) {
+            const Tile t = tile_at(p, idx, row_tiles, cols_per_tile);
+            if (!t.ok) continue;
+            const int buf = lt & 1;
+            ok = mbar_wait(smem_u32(&tail->acc_full[buf]), (lt >> 1) & 1, abort_flag, 3);
+            if (!ok) break;
+            tc_fence_after();
+            const int li = t.row0 + r;
+            const bool row_ok = r < t.rows;
             int crow = li, srow = li;
             float sc = 1.f;
             if (row_ok) {
@@ -219,16 +259,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     sc = p.row_scale[srow];
                 }
             }
-            const unsigned lane_addr = tmem + ((unsigned)(quarter * 32) << 16);
+            const unsigned lane_addr = tmem + buf * ACC_COLS + ((unsigned)(quarter * 32) << 16);
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
+            for (int c0 = 0; c0 < cols_per_tile; c0 += 32) {
                 float v[32];
                 tc_ld32(v, lane_addr + c0);                    // warp-collective: every lane takes part
                 float u[32];
-                if (DUAL) tc_ld32(u, lane_addr + BN + c0);
-                if (!row_ok) continue;
-                const int n = n0 + c0;
-                if (n >= p.N) continue;
+                if (DUAL) tc_ld32(u, lane_addr + bnh + c0);
+                const int n = t.n0 + c0;
+                if (!row_ok || n >= p.N) continue;
                 const size_t o = (size_t)crow * p.ldc + n;
                 const bool full = (n + 32 <= p.N);
                 if (EPI == EPI_STORE || EPI == EPI_SWIGLU) {
@@ -246,7 +285,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                             *(uint4*)(dst + i) = q;
                         }
                     } else {
-                        for (int i = 0; i < 32 && n + i < p.N; ++i) dst[i] = __float2bfloat16_rn(y[i]);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (n + i < p.N) dst[i] = __float2bfloat16_rn(y[i]);
                     }
                 } else {
                     float* dst = (float*)p.C + o;
@@ -261,11 +302,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                             *(float4*)(dst + i) = q;
                         }
                     } else {
-                        for (int i = 0; i < 32 && n + i < p.N; ++i)
-                            dst[i] = (EPI == EPI_ADD_F32 ? dst[i] : 0.f) + v[i] * sc;
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (n + i < p.N) dst[i] = (EPI == EPI_ADD_F32 ? dst[i] : 0.f) + v[i] * sc;
                     }
                 }
             }
+            // this warp has read its lanes of the accumulator: hand it back to the tensor cores
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&tail->acc_empty[buf]));
+            ++lt;
         }
     }
     tc_fence_before();
@@ -293,38 +340,61 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
-// A row-major [rows, cols] bfloat16 matrix with leading dimension ld; boxes of 64 columns x 128 rows.
-bool make_map(CUtensorMap* map, const void* base, long long rows, long long cols, long long ld) {
+// A row-major [rows, cols] bfloat16 matrix with leading dimension ld; boxes of 64 columns x box_rows rows.
+bool make_map(CUtensorMap* map, const void* base, long long rows, long long cols, long long ld, int box_rows) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return false;
     cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
     cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)BM};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
     cuuint32_t estr[2] = {1, 1};
     return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int EPI, int STAGES>
-int launch(const GemmParams& p, const CUtensorMap& ma, const CUtensorMap& mw, cudaStream_t st) {
-    constexpr int OPERANDS = (EPI == EPI_SWIGLU) ? 3 : 2;
-    const size_t smem = (size_t)STAGES * OPERANDS * TILE_BYTES + sizeof(SharedTail) + 1024;
-    auto k = gemm_tc_kernel<EPI, STAGES>;
+// Half-tile height that makes the tile waves fullest: fewest rounds of n_blocks tiles, weighted by
+// the tile's width plus a fixed cost for filling and draining the pipeline.
+int choose_bnh(const GemmParams& p, int row_tiles, int n_blocks) {
+    const bool dual = p.epilogue == EPI_SWIGLU;
+    int best = 128;
+    long long best_cost = -1;
+    for (int bnh = 128; bnh >= 32; bnh -= 32) {
+        const int cols = dual ? bnh : 2 * bnh;
+        const long long tiles = (long long)((p.N + cols - 1) / cols) * row_tiles;
+        const long long rounds = (tiles + n_blocks - 1) / n_blocks;
+        const long long cost = rounds * (2 * bnh + 40);
+        if (best_cost < 0 || cost < best_cost) { best = bnh; best_cost = cost; }
+    }
+    return best;
+}
+
+template <int EPI>
+int launch(const GemmParams& p, int n_blocks, cudaStream_t st) {
+    const int row_tiles = (p.M + BM - 1) / BM + (p.group_offsets ? p.n_groups : 0);
+    const int bnh = choose_bnh(p, row_tiles, n_blocks);
+    const int cols = (EPI == EPI_SWIGLU) ? bnh : 2 * bnh;
+    const long long total = (long long)((p.N + cols - 1) / cols) * row_tiles;
+    if (total > 0x7fffffff) return SPITE_UNSUPPORTED;
+    const long long w_rows = (long long)(EPI == EPI_SWIGLU ? 2 : 1) * p.N * p.n_groups;
+    CUtensorMap ma, mw;
+    if (!make_map(&ma, p.A, p.M, p.K, p.lda, BM) || !make_map(&mw, p.W, w_rows, p.K, p.K, bnh))
+        return SPITE_LAUNCH_FAILED;
+    const size_t smem = (size_t)STAGES * STAGE_BYTES + sizeof(SharedTail) + 1024;
+    auto k = gemm_tc_kernel<EPI>;
     if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
         return SPITE_LAUNCH_FAILED;
-    const int row_tiles = (p.M + BM - 1) / BM + (p.group_offsets ? p.n_groups : 0);
-    dim3 grid((p.N + BN - 1) / BN, row_tiles);
-    if (grid.y > 65535) return SPITE_UNSUPPORTED;
-    k<<<grid, THREADS, smem, st>>>(ma, mw, p);
+    const int grid = (int)(total < n_blocks ? total : n_blocks);
+    k<<<grid, THREADS, smem, st>>>(ma, mw, p, bnh, row_tiles, (int)total);
     return spite_launch_status();
 }
 
 }  // namespace
 
-SPITE_API int spite_gemm_tc(const GemmParams* p, void* stream) {
+// `n_blocks`: number of multiprocessors (one persistent block each).
+SPITE_API int spite_gemm_tc(const GemmParams* p, int n_blocks, void* stream) {
     if (!p || !p->A || !p->W || !p->C) return SPITE_BAD_ARG;
-    if (p->M < 0 || p->N <= 0 || p->K <= 0 || p->lda < p->K || p->ldc < p->N) return SPITE_BAD_ARG;
+    if (p->M < 0 || p->N <= 0 || p->K <= 0 || p->lda < p->K || p->ldc < p->N || n_blocks < 1) return SPITE_BAD_ARG;
     if (p->group_offsets ? p->n_groups < 1 : p->n_groups != 1) return SPITE_BAD_ARG;
     if (p->epilogue < 0 || p->epilogue > EPI_SWIGLU) return SPITE_BAD_ARG;
     // TMA: 16-byte aligned bases and row pitches
@@ -332,21 +402,18 @@ SPITE_API int spite_gemm_tc(const GemmParams* p, void* stream) {
     if (p->n_groups > 1 && p->w_group_stride != (long long)(p->epilogue == EPI_SWIGLU ? 2 : 1) * p->N * p->K)
         return SPITE_UNSUPPORTED;                              // groups must be stacked without gaps
     if (p->M == 0) return SPITE_OK;
-    const long long w_rows = (long long)(p->epilogue == EPI_SWIGLU ? 2 : 1) * p->N * p->n_groups;
-    CUtensorMap ma, mw;
-    if (!make_map(&ma, p->A, p->M, p->K, p->lda) || !make_map(&mw, p->W, w_rows, p->K, p->K))
-        return SPITE_LAUNCH_FAILED;
     cudaStream_t st = (cudaStream_t)stream;
     switch (p->epilogue) {
-        case EPI_STORE: return launch<EPI_STORE, 6>(*p, ma, mw, st);
-        case EPI_STORE_F32: return launch<EPI_STORE_F32, 6>(*p, ma, mw, st);
-        case EPI_ADD_F32: return launch<EPI_ADD_F32, 6>(*p, ma, mw, st);
-        default: return launch<EPI_SWIGLU, 4>(*p, ma, mw, st);
+        case EPI_STORE: return launch<EPI_STORE>(*p, n_blocks, st);
+        case EPI_STORE_F32: return launch<EPI_STORE_F32>(*p, n_blocks, st);
+        case EPI_ADD_F32: return launch<EPI_ADD_F32>(*p, n_blocks, st);
+        default: return launch<EPI_SWIGLU>(*p, n_blocks, st);
     }
 }
 
 // Error code recorded by a block that gave up waiting (0: none); reading it clears it.
-// 1: loader waited for a free stage, 2: tensor-core issue waited for a tile, 3: epilogue waited for the accumulator.
+// 1: loader waited for a free stage, 2: tensor-core issue waited for a tile, 3: epilogue waited
+// for an accumulator, 4: tensor-core issue waited for a free accumulator.
 SPITE_API int spite_gemm_tc_error() {
     int v = 0, zero = 0;
     if (cudaMemcpyFromSymbol(&v, g_tc_error, sizeof(int)) != cudaSuccess) return -3;

@@ -153,7 +153,7 @@ class CudaKernels(KernelSet):
                     q = GemmParams.from_buffer_copy(p)
                     q.A = keep.data_ptr()          # rows are in place now; a_rows only indexes the row scale
                     p = q
-                st = self._lib("gemm_tc").spite_gemm_tc(C.byref(p), self._stream())
+                st = self._lib("gemm_tc").spite_gemm_tc(C.byref(p), self.sm_count, self._stream())
                 if st != -2:
                     self.launches += 1
                     _check(st, what + " (tcgen05)")
