@@ -169,6 +169,28 @@ def run_ours(args):
         return ms / steps, ks.launches - l0, ids
 
     pk, pk_src = peaks()
+    def measure_prefill():
+        """Prefill of 2,048 tokens, logits of the last row."""
+        T = 2048
+        ptoks = torch.randint(0, vocab, (T,), generator=g).tolist()
+        pre_ms = []
+        for i in range(3):
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            engine.step([StepEntry("p", ptoks, [T - 1])])
+            e1.record()
+            torch.cuda.synchronize()
+            engine.finish("p")
+            pre_ms.append(e0.elapsed_time(e1))
+        pms = min(pre_ms[1:])
+        pflops = prefill_flops(cfgd, T)
+        return {"value": round(T * 1000.0 / pms, 1), "tokens": T, "ms": round(pms, 3),
+                "frac": round(pflops / (pms * 1e-3) / (pk["bf16_tflops_sustained"] * 1e12), 4)}
+
+    if args.only_prefill:
+        print(json.dumps({"prefill": measure_prefill(), "layers": args.layers}))
+        return
     clocks = ClockSampler()
     ms_step, launches, _ = timed_decode(B, args.steps, args.warmup, clocks)
     value = B * 1000.0 / ms_step
@@ -214,23 +236,7 @@ def run_ours(args):
     for r in list(engine.cache.requests):
         engine.finish(r)
 
-    # prefill of 2,048 tokens, logits of the last row
-    T = 2048
-    ptoks = torch.randint(0, vocab, (T,), generator=g).tolist()
-    pre_ms = []
-    for i in range(3):
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        engine.step([StepEntry("p", ptoks, [T - 1])])
-        e1.record()
-        torch.cuda.synchronize()
-        engine.finish("p")
-        pre_ms.append(e0.elapsed_time(e1))
-    pms = min(pre_ms[1:])
-    pflops = prefill_flops(cfgd, T)
-    prefill = {"value": round(T * 1000.0 / pms, 1), "tokens": T, "ms": round(pms, 3),
-               "frac": round(pflops / (pms * 1e-3) / (pk["bf16_tflops_sustained"] * 1e12), 4)}
+    prefill = measure_prefill()
 
     points = {}
     if not args.skip_points:
@@ -289,6 +295,7 @@ def main(argv=None):
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--no-graphs", action="store_true", help="launch every kernel of a decode step by itself")
     ap.add_argument("--only-decode", action="store_true", help="measure the decode step only (for profiling)")
+    ap.add_argument("--only-prefill", action="store_true", help="measure the prefill step only (for profiling)")
     args = ap.parse_args(argv)
     if args.impl == "reference":
         return run_reference(args)

@@ -48,6 +48,21 @@ struct AttentionParams {
     float softmax_scale;
 };
 
+// What the tensor-core attention kernels need beyond the above.  Two kernels share a step:
+// segments of few tokens (decode) go to the one that splits the keys among blocks, segments
+// of many tokens (prompt portions) to the one that gives every warp its own rows; each kernel
+// serves the segments whose token count lies in [seg_min_tokens, seg_max_tokens].
+struct AttnMmaExtra {
+    const int* cu_seqlens;       // [segments + 1]
+    float* o_part;               // [tokens, heads, splits, head_dim]   (splits > 1)
+    float* ml_part;              // [tokens, heads, splits, 2]          running maximum, sum
+    int n_segments;
+    int tokens_per_block;        // tokens whose (token, head) rows fill one block
+    int n_splits;
+    int seg_min_tokens;
+    int seg_max_tokens;
+};
+
 __device__ __forceinline__ int window_lowest(int kind, int size, int pos) {
     if (kind == SPITE_WINDOW_CHUNK) return (pos / size) * size;
     if (kind == SPITE_WINDOW_SLIDING) return max(0, pos - size + 1);

@@ -14,15 +14,6 @@
 // window rule is the architecture's (same chunk), see attention.cuh.
 #include "attention.cuh"
 
-struct AttnMmaExtra {
-    const int* cu_seqlens;       // [segments + 1]
-    float* o_part;               // [tokens, heads, splits, head_dim]   (splits > 1)
-    float* ml_part;              // [tokens, heads, splits, 2]          running maximum, sum
-    int n_segments;
-    int tokens_per_block;        // floor(16 / group size), at least 1
-    int n_splits;
-};
-
 namespace {
 
 constexpr int WARPS = 4;
@@ -73,6 +64,7 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_kernel(const AttentionPar
     int idx = blockIdx.x, seg = -1, t0 = 0, nt = 0;
     for (int s = 0; s < x.n_segments; ++s) {
         const int lo = x.cu_seqlens[s], n = x.cu_seqlens[s + 1] - lo;
+        if (n < x.seg_min_tokens || n > x.seg_max_tokens) continue;   // another kernel serves this segment
         const int blocks = (n + x.tokens_per_block - 1) / x.tokens_per_block;
         if (idx < blocks) { seg = s; t0 = lo + idx * x.tokens_per_block; nt = min(x.tokens_per_block, lo + n - t0); break; }
         idx -= blocks;
@@ -276,8 +268,13 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_kernel(const AttentionPar
 // grid tokens * heads, block 128: merge the splits of one (token, head)
 __global__ void __launch_bounds__(128) attn_merge_kernel(const float* __restrict__ o_part,
                                                          const float* __restrict__ ml_part,
-                                                         __nv_bfloat16* __restrict__ out, int n_splits, int hd) {
+                                                         __nv_bfloat16* __restrict__ out, int n_splits, int hd,
+                                                         int num_heads, const int* __restrict__ seg_of_token,
+                                                         const int* __restrict__ cu_seqlens, int seg_min, int seg_max) {
     const size_t row = blockIdx.x;
+    const int seg = seg_of_token[row / num_heads];
+    const int seg_n = cu_seqlens[seg + 1] - cu_seqlens[seg];
+    if (seg_n < seg_min || seg_n > seg_max) return;
     float m = -INFINITY;
     for (int s = 0; s < n_splits; ++s) m = fmaxf(m, ml_part[(row * n_splits + s) * 2]);
     float l = 0.f;
@@ -316,7 +313,8 @@ int launch(const AttentionParams& p, const StepTokens& b, const PagedCache& c, c
 SPITE_API int spite_paged_attention_mma(const AttentionParams* p, const StepTokens* b, const PagedCache* c,
                                         const AttnMmaExtra* x, int n_blocks, void* stream) {
     if (!p || !b || !c || !x || !p->q || !p->out || !x->cu_seqlens || !c->kv) return SPITE_BAD_ARG;
-    if (!b->positions || !b->block_table || b->n_tokens < 0 || b->table_width < 1) return SPITE_BAD_ARG;
+    if (!b->positions || !b->block_table || !b->seg_of_token || b->n_tokens < 0 || b->table_width < 1)
+        return SPITE_BAD_ARG;
     if (p->num_heads < 1 || c->num_kv_heads < 1 || p->num_heads % c->num_kv_heads) return SPITE_BAD_ARG;
     if (p->window_kind < 0 || p->window_kind > 2) return SPITE_BAD_ARG;
     if (p->window_kind != SPITE_WINDOW_FULL && p->window_size < 1) return SPITE_BAD_ARG;
@@ -341,6 +339,8 @@ SPITE_API int spite_paged_attention_mma(const AttentionParams* p, const StepToke
     }
     if (rc != SPITE_OK || x->n_splits == 1) return rc;
     attn_merge_kernel<<<b->n_tokens * p->num_heads, 128, 0, st>>>(x->o_part, x->ml_part, (__nv_bfloat16*)p->out,
-                                                                  x->n_splits, c->head_dim);
+                                                                  x->n_splits, c->head_dim, p->num_heads,
+                                                                  b->seg_of_token, x->cu_seqlens, x->seg_min_tokens,
+                                                                  x->seg_max_tokens);
     return spite_launch_status();
 }

@@ -32,6 +32,7 @@ LIBRARIES = {
     "gemm_tc": (["gemm_tc.cu"], []),
     "attention": (["attention.cu"], []),
     "attention_mma": (["attention_mma.cu"], []),
+    "attention_rows": (["attention_rows.cu"], []),
     "moe": (["moe.cu"], []),
     "sampling": (["sampling.cu"], []),
 }

@@ -52,7 +52,8 @@ class AttentionParams(C.Structure):
 
 class AttnMmaExtra(C.Structure):
     _fields_ = [("cu_seqlens", C.c_void_p), ("o_part", C.c_void_p), ("ml_part", C.c_void_p),
-                ("n_segments", C.c_int), ("tokens_per_block", C.c_int), ("n_splits", C.c_int)]
+                ("n_segments", C.c_int), ("tokens_per_block", C.c_int), ("n_splits", C.c_int),
+                ("seg_min_tokens", C.c_int), ("seg_max_tokens", C.c_int)]
 
 
 class SampleParams(C.Structure):
@@ -260,22 +261,42 @@ class CudaKernels(KernelSet):
         group = num_heads // c.num_kv_heads
         if (self.dtype == torch.bfloat16 and c.head_dim % 16 == 0 and c.head_dim <= 128 and group <= 16
                 and c.page_size % 16 == 0 and batch.segments):
-            # tensor-core kernel: rows are (token, head of a kv group) pairs, up to 16 a block
-            tpb = max(1, 16 // group)
-            n_blocks, longest = 0, 1
+            # Tensor-core kernels; rows are (token, head of a kv group) pairs.  Segments of many
+            # tokens (prompt portions) go to the kernel with 64 rows a block and warps that own
+            # rows; segments of few tokens (decode) to the kernel with 16 rows a block whose
+            # warps and blocks split the keys.
+            big_from = -(-32 // group) if c.page_size % 32 == 0 else 1 << 30
+            tpb, tpb_rows = max(1, 16 // group), max(1, 64 // group)
+            n_small = n_big = 0
+            longest = 1
             for s in batch.segments:
-                n_blocks += -(-s.n_tokens // tpb)
+                if s.n_tokens >= big_from:
+                    n_big += -(-s.n_tokens // tpb_rows)
+                    continue
+                n_small += -(-s.n_tokens // tpb)
                 last = s.start_pos + s.n_tokens - 1
                 longest = max(longest, last - window.lowest_visible(max(s.start_pos, last - tpb + 1)) + 1)
+            if n_big:
+                x = AttnMmaExtra(cu_seqlens=batch.cu_seqlens.data_ptr(), o_part=None, ml_part=None,
+                                 n_segments=len(batch.segments), tokens_per_block=tpb_rows, n_splits=1,
+                                 seg_min_tokens=big_from, seg_max_tokens=0x7fffffff)
+                st = self._lib("attention_rows").spite_paged_attention_rows(
+                    C.byref(p), C.byref(b), C.byref(c), C.byref(x), n_big, self._stream())
+                self.launches += 1
+                _check(st, "paged_attention (tensor cores, prompt portions)")
+            if not n_small:
+                return
             if batch.context_bucket:            # fixed launch shape for a captured step
                 longest = batch.context_bucket if window.kind == "full" else min(batch.context_bucket, window.size)
             tiles = -(-longest // 16) + 1
-            base = n_blocks * c.num_kv_heads
+            base = n_small * c.num_kv_heads
             # key splits: fill the resident blocks (three per multiprocessor) once if the step is
             # small, else pick the split count whose last wave is fullest
             slots = 3 * self.sm_count
             if base <= slots:
                 splits = slots // base
+            elif base >= 4 * slots:
+                splits = 1
             else:
                 splits = max(range(1, 5), key=lambda s: (base * s / slots) / -(-base * s // slots))
             splits = max(1, min(splits, tiles // 8, 128))
@@ -285,9 +306,10 @@ class CudaKernels(KernelSet):
                                      device=q.device)
                 ml_part = torch.empty((batch.n_tokens, num_heads, splits, 2), dtype=torch.float32, device=q.device)
             x = AttnMmaExtra(cu_seqlens=batch.cu_seqlens.data_ptr(), o_part=_ptr(o_part), ml_part=_ptr(ml_part),
-                             n_segments=len(batch.segments), tokens_per_block=tpb, n_splits=splits)
+                             n_segments=len(batch.segments), tokens_per_block=tpb, n_splits=splits,
+                             seg_min_tokens=0, seg_max_tokens=big_from - 1)
             st = self._lib("attention_mma").spite_paged_attention_mma(
-                C.byref(p), C.byref(b), C.byref(c), C.byref(x), n_blocks, self._stream())
+                C.byref(p), C.byref(b), C.byref(c), C.byref(x), n_small, self._stream())
             self.launches += 1 + (splits > 1)
             _check(st, "paged_attention (tensor cores)")
             return

@@ -190,7 +190,9 @@ def test_qk_prepare(ks, nq, nkv, hd, rope, norm, temp):
 @pytest.mark.parametrize("nq,nkv,hd,window,P", [
     (4, 2, 16, ("full", 0), 16), (6, 1, 32, ("chunk", 16), 16), (5, 5, 48, ("chunk", 40), 16),
     (40, 8, 128, ("full", 0), 64), (10, 2, 128, ("chunk", 96), 64), (3, 1, 256, ("sliding", 37), 16),
-    (8, 2, 64, ("full", 0), 16)])
+    (8, 2, 64, ("full", 0), 16), (4, 2, 16, ("full", 0), 32), (6, 1, 32, ("chunk", 16), 32),
+    (5, 5, 48, ("chunk", 40), 32), (8, 2, 64, ("sliding", 50), 32), (16, 1, 80, ("sliding", 37), 32),
+    (12, 4, 112, ("full", 0), 64)])
 def test_paged_attention(ks, nq, nkv, hd, window, P):
     """Segments of different kinds in one call: a long prompt portion that crosses
     window and page edges, single tokens deep in a context, a first token."""
