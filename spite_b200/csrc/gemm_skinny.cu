@@ -24,6 +24,7 @@ namespace {
 constexpr int WARPS = 8;
 constexpr int NFRAG = 2;          // 16-row weight fragments per warp
 constexpr int MAX_GROUPS = 1024;
+constexpr int MAX_ACTIVE = MAX_GROUPS + 64;   // (group, token chunk) pairs of one call
 
 __device__ __forceinline__ void mma16816(float (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
                                          unsigned b0, unsigned b1) {
@@ -49,21 +50,24 @@ __global__ void __launch_bounds__(WARPS * 32, (NT <= 1 ? 2 : 1)) gemm_skinny_ker
     constexpr int ROWS = DUAL ? 16 : 32;                         // output columns (weight rows) per item
     constexpr int TOK = NT * 8;
     extern __shared__ float red[];                               // [WARPS][NFRAG*16][TOK]
-    __shared__ int active_s[MAX_GROUPS];
+    __shared__ int active_s[MAX_ACTIVE];
     __shared__ int n_active_s;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, c = lane & 3;
     const int n_tiles = (p.N + ROWS - 1) / ROWS;
 
-    // groups that have tokens
+    // (group, chunk of TOK tokens) pairs that have tokens: a group with more than TOK tokens
+    // streams its weights once per chunk
     if (threadIdx.x == 0) {
         int n = 0;
         if (p.group_offsets) {
-            for (int e = 0; e < p.n_groups; ++e)
-                if (p.group_offsets[e + 1] > p.group_offsets[e]) active_s[n++] = e;
+            for (int e = 0; e < p.n_groups && n < MAX_ACTIVE; ++e) {
+                const int m = p.group_offsets[e + 1] - p.group_offsets[e];
+                for (int ch = 0; ch * TOK < m && n < MAX_ACTIVE; ++ch) active_s[n++] = e | (ch << 16);
+            }
         } else {
-            active_s[n++] = 0;
+            for (int ch = 0; ch * TOK < p.M && n < MAX_ACTIVE; ++ch) active_s[n++] = ch << 16;
         }
         n_active_s = n;
     }
@@ -72,10 +76,13 @@ __global__ void __launch_bounds__(WARPS * 32, (NT <= 1 ? 2 : 1)) gemm_skinny_ker
 
     auto item_at = [&](int i) {
         Item it;
-        it.group = active_s[i / n_tiles];
+        const int a = active_s[i / n_tiles];
+        it.group = a & 0xffff;
         it.tile = i % n_tiles;
-        it.row_lo = p.group_offsets ? p.group_offsets[it.group] : 0;
-        it.m = p.group_offsets ? p.group_offsets[it.group + 1] - it.row_lo : p.M;
+        const int lo = p.group_offsets ? p.group_offsets[it.group] : 0;
+        const int m = p.group_offsets ? p.group_offsets[it.group + 1] - lo : p.M;
+        it.row_lo = lo + (a >> 16) * TOK;
+        it.m = min(TOK, m - (a >> 16) * TOK);
         return it;
     };
     const __nv_bfloat16* X = (const __nv_bfloat16*)p.A;
@@ -260,12 +267,16 @@ SPITE_API int spite_gemm_skinny(const GemmParams* p, int max_rows_per_group, int
     if (p->group_offsets ? p->n_groups < 1 : p->n_groups != 1) return SPITE_BAD_ARG;
     if (p->K % 32 || p->lda % 8) return SPITE_UNSUPPORTED;                 // 16-byte loads, 32-wide steps
     if (((uintptr_t)p->A | (uintptr_t)p->W) & 15) return SPITE_UNSUPPORTED;
-    if (max_rows_per_group < 1 || max_rows_per_group > 64 || p->n_groups > MAX_GROUPS) return SPITE_UNSUPPORTED;
+    if (max_rows_per_group < 1 || p->n_groups > MAX_GROUPS || p->M > 64 * 8) return SPITE_UNSUPPORTED;
     if (p->M == 0) return SPITE_OK;
     cudaStream_t st = (cudaStream_t)stream;
     const int half = (n_blocks + 1) / 2;                                   // kernels that fit once per multiprocessor
+    // Tokens per pass: a group with more tokens than one pass holds streams its weights again
+    // for the next chunk.  Groups of a routed batch are small, so 16 tokens a pass serve them;
+    // one dense group of up to 64 tokens is held whole.
     if (max_rows_per_group <= 8) return launch_nt<1, 4>(*p, n_blocks, st);
-    if (max_rows_per_group <= 16) return launch_nt<2, 4>(*p, half, st);
+    if (max_rows_per_group <= 16 || p->group_offsets) return launch_nt<2, 4>(*p, half, st);
     if (max_rows_per_group <= 32) return launch_nt<4, 2>(*p, half, st);
-    return launch_nt<8, 2>(*p, half, st);
+    if (max_rows_per_group <= 64) return launch_nt<8, 2>(*p, half, st);
+    return SPITE_UNSUPPORTED;
 }

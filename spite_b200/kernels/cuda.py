@@ -86,6 +86,9 @@ class CudaKernels(KernelSet):
         self.launches = 0          # kernels launched so far (for measurement reports)
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.use_tcgen05 = os.environ.get("SPITE_NO_TCGEN05", "") == ""
+        # row counts up to which the weight-streaming kernel is preferred over the tcgen05 one
+        self.skinny_dense_max = int(os.environ.get("SPITE_SKINNY_DENSE_MAX", "16"))
+        self.skinny_group_avg = int(os.environ.get("SPITE_SKINNY_GROUP_AVG", "8"))
 
     # ------------------------------------------------------------------ helpers
     def _lib(self, name):
@@ -129,20 +132,24 @@ class CudaKernels(KernelSet):
 
     # ------------------------------------------------------------------ matrix products
     def _gemm(self, p: GemmParams, what, max_rows_per_group, gather_src=None):
-        """Pick the kernel.  bfloat16: up to 64 rows per group the weight-streaming mma.sync
-        kernel, above that the tcgen05 kernel (TMA-fed, accumulators in TMEM); float32 and
-        shapes those two refuse: the CUDA-core kernel.  `gather_src` is the tensor whose rows
+        """Pick the kernel.  bfloat16: few rows go to the weight-streaming mma.sync kernel (one
+        group: up to 16 rows; routed groups: up to 8 rows per group on average, passes of 16),
+        more rows to the tcgen05 kernel (TMA-fed, accumulators in TMEM); float32, and shapes
+        those two refuse, to the CUDA-core kernel.  `gather_src` is the tensor whose rows
         `p.a_rows` gathers: the tcgen05 kernel wants contiguous rows, so they are gathered first."""
         if self.dtype == torch.bfloat16:
-            if max_rows_per_group <= 64:
+            grouped = bool(p.group_offsets)
+            few = p.M <= (min(self.skinny_group_avg * p.n_groups, 512) if grouped else self.skinny_dense_max)
+            tc_ok = self.use_tcgen05 and p.K % 8 == 0 and p.lda % 8 == 0
+            if few or (not tc_ok and max_rows_per_group <= 64):
                 st = self._lib("gemm_skinny").spite_gemm_skinny(C.byref(p), int(max_rows_per_group), 2 * self.sm_count,
                                                                 self._stream())
                 if st != -2:                       # -2: shape outside the kernel's domain, fall through
                     self.launches += 1
                     _check(st, what)
                     return
-            elif self.use_tcgen05 and p.K % 8 == 0 and p.lda % 8 == 0:
-                keep = None
+            if tc_ok:
+                orig = p
                 if gather_src is not None:
                     keep = torch.empty_like(gather_src)
                     st = self._lib("elementwise").spite_gather_rows(
@@ -151,16 +158,21 @@ class CudaKernels(KernelSet):
                         self._stream())
                     self.launches += 1
                     _check(st, "gather_rows")
-                    q = GemmParams.from_buffer_copy(p)
-                    q.A = keep.data_ptr()          # rows are in place now; a_rows only indexes the row scale
-                    p = q
+                    p = GemmParams.from_buffer_copy(p)
+                    p.A = keep.data_ptr()          # rows are in place now; a_rows only indexes the row scale
                 st = self._lib("gemm_tc").spite_gemm_tc(C.byref(p), self.sm_count, self._stream())
                 if st != -2:
                     self.launches += 1
                     _check(st, what + " (tcgen05)")
                     return
-                if gather_src is not None:         # refused after all: undo the pointer swap
-                    p.A = gather_src.data_ptr()
+                p = orig
+                if max_rows_per_group <= 64:       # refused (alignment): the streaming kernel may still take it
+                    st = self._lib("gemm_skinny").spite_gemm_skinny(C.byref(p), int(max_rows_per_group),
+                                                                    2 * self.sm_count, self._stream())
+                    if st != -2:
+                        self.launches += 1
+                        _check(st, what)
+                        return
         st = self._lib("gemm_simt").spite_gemm_simt(self._dt, C.byref(p), self._stream())
         self.launches += 1
         _check(st, what)
