@@ -4,8 +4,8 @@
 // Persistent blocks (one per multiprocessor) walk the output tiles of 128 rows x BN
 // columns, BN = 64..256 chosen on the host so that the last wave of tiles is full.  Roles:
 //   warp 0    one lane issues TMA loads (cp.async.bulk.tensor, 128-byte swizzle) of the A
-//             tile and the two halves of the W tile of a 64-wide k block into a ring of four
-//             shared-memory stages;
+//             tile and the two halves of the W tile of a 64-wide k block into a ring of four to
+//             eight shared-memory stages (192 KiB; narrower tiles get more stages);
 //   warp 1    allocates TMEM (512 columns: two accumulators of up to 256); one lane issues
 //             tcgen05.mma 128 x BN x 16, operands straight from shared memory through matrix
 //             descriptors, commits each stage back to the loader and each finished
@@ -30,10 +30,10 @@
 
 namespace {
 
-constexpr int BM = 128, BK = 64, UMMA_K = 16, STAGES = 4;
+constexpr int BM = 128, BK = 64, UMMA_K = 16, MAX_STAGES = 8;
 constexpr int A_BYTES = BM * BK * 2;                     // 16 KiB
 constexpr int B_BYTES = 256 * BK * 2;                    // room for 256 weight rows, 32 KiB
-constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int RING_BYTES = 4 * (A_BYTES + B_BYTES);      // 192 KiB of stages: 4 of the widest tile, up to 8 of narrower ones
 constexpr int ACC_COLS = 256, TMEM_COLS = 512;
 constexpr int THREADS = 192;
 constexpr long long WAIT_CYCLES = 4000000000ll;          // about two seconds
@@ -120,8 +120,8 @@ __host__ __device__ constexpr unsigned make_idesc(int m, int n) {
 }
 
 struct SharedTail {
-    unsigned long long full[STAGES];
-    unsigned long long empty[STAGES];
+    unsigned long long full[MAX_STAGES];
+    unsigned long long empty[MAX_STAGES];
     unsigned long long acc_full[2];
     unsigned long long acc_empty[2];
     unsigned tmem_base;
@@ -144,21 +144,21 @@ __device__ __forceinline__ Tile tile_at(const GemmParams& p, int idx, int row_ti
 template <int EPI>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-               const GemmParams p, const int bnh, const int row_tiles, const int total_tiles) {
+               const GemmParams p, const int bnh, const int row_tiles, const int total_tiles, const int n_stages) {
     constexpr bool DUAL = (EPI == EPI_SWIGLU);
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    SharedTail* tail = (SharedTail*)(smem + STAGES * STAGE_BYTES);
+    SharedTail* tail = (SharedTail*)(smem + RING_BYTES);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int num_kb = (p.K + BK - 1) / BK;
     const int w_rows = DUAL ? 2 * p.N : p.N;
     const int cols_per_tile = DUAL ? bnh : 2 * bnh;          // output columns of one tile
-    const unsigned stage_tx = A_BYTES + 2 * bnh * BK * 2;
+    const unsigned stage_tx = A_BYTES + 2 * bnh * BK * 2;   // bytes of one stage, also its stride in the ring
     volatile int* abort_flag = &tail->abort_flag;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; ++s) { mbar_init(smem_u32(&tail->full[s]), 1); mbar_init(smem_u32(&tail->empty[s]), 1); }
+        for (int s = 0; s < n_stages; ++s) { mbar_init(smem_u32(&tail->full[s]), 1); mbar_init(smem_u32(&tail->empty[s]), 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(smem_u32(&tail->acc_full[b]), 1); mbar_init(smem_u32(&tail->acc_empty[b]), 4); }
         tail->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -177,19 +177,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         if (lane == 0) {
             // ---- loader
             int it = 0;                                       // k blocks issued so far, over all tiles
+            int s = 0;                                        // it % n_stages and the ring's phase, kept by counting
+            unsigned ph = 0;
             bool ok = true;
             for (int idx = blockIdx.x; idx < total_tiles && ok; idx += gridDim.x) {
                 const Tile t = tile_at(p, idx, row_tiles, cols_per_tile);
                 if (!t.ok) continue;
                 const int wy0 = t.group * w_rows + t.n0;
                 const int wy1 = DUAL ? t.group * w_rows + p.N + t.n0 : wy0 + bnh;
-                for (int kb = 0; kb < num_kb; ++kb, ++it) {
-                    const int s = it % STAGES;
-                    const unsigned ph = (it / STAGES) & 1;
+                for (int kb = 0; kb < num_kb; ++kb, ++it, s = (s + 1 == n_stages ? 0 : s + 1), ph ^= (s == 0)) {
                     ok = mbar_wait(smem_u32(&tail->empty[s]), ph ^ 1, abort_flag, 1);
                     if (!ok) break;
                     const unsigned bar = smem_u32(&tail->full[s]);
-                    const unsigned dst = smem_u32(smem + s * STAGE_BYTES);
+                    const unsigned dst = smem_u32(smem + s * stage_tx);
                     mbar_expect_tx(bar, stage_tx);
                     tma_load_2d(dst, &map_a, kb * BK, t.row0, bar);
                     tma_load_2d(dst + A_BYTES, &map_w, kb * BK, wy0, bar);
@@ -198,9 +198,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             }
             if (*abort_flag) {
                 // copies in flight must land before the block gives its shared memory back
-                for (int j = max(0, it - STAGES); j < it; ++j) {
+                for (int j = max(0, it - n_stages); j < it; ++j) {
                     const long long t0 = clock64();
-                    while (!mbar_try(smem_u32(&tail->full[j % STAGES]), (j / STAGES) & 1) &&
+                    while (!mbar_try(smem_u32(&tail->full[j % n_stages]), (j / n_stages) & 1) &&
                            clock64() - t0 < WAIT_CYCLES) {}
                 }
             }
@@ -209,7 +209,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         if (lane == 0) {
             // ---- tensor-core issue
             const unsigned idesc = make_idesc(BM, 2 * bnh);
-            int it = 0, lt = 0;
+            int lt = 0, s = 0;
+            unsigned ph = 0;
             bool ok = true;
             for (int idx = blockIdx.x; idx < total_tiles && ok; idx += gridDim.x) {
                 const Tile t = tile_at(p, idx, row_tiles, cols_per_tile);
@@ -219,12 +220,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 if (!ok) break;
                 tc_fence_after();
                 const unsigned d_tmem = tmem + buf * ACC_COLS;
-                for (int kb = 0; kb < num_kb; ++kb, ++it) {
-                    const int s = it % STAGES;
-                    ok = mbar_wait(smem_u32(&tail->full[s]), (it / STAGES) & 1, abort_flag, 2);
+                for (int kb = 0; kb < num_kb; ++kb, s = (s + 1 == n_stages ? 0 : s + 1), ph ^= (s == 0)) {
+                    ok = mbar_wait(smem_u32(&tail->full[s]), ph, abort_flag, 2);
                     if (!ok) break;
                     tc_fence_after();
-                    const unsigned a_addr = smem_u32(smem + s * STAGE_BYTES);
+                    const unsigned a_addr = smem_u32(smem + s * stage_tx);
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; ++k)
                         tc_mma(d_tmem, smem_desc(a_addr + k * UMMA_K * 2), smem_desc(a_addr + A_BYTES + k * UMMA_K * 2),
@@ -380,12 +380,14 @@ int launch(const GemmParams& p, int n_blocks, cudaStream_t st) {
     CUtensorMap ma, mw;
     if (!make_map(&ma, p.A, p.M, p.K, p.lda, BM) || !make_map(&mw, p.W, w_rows, p.K, p.K, bnh))
         return SPITE_LAUNCH_FAILED;
-    const size_t smem = (size_t)STAGES * STAGE_BYTES + sizeof(SharedTail) + 1024;
+    const size_t smem = (size_t)RING_BYTES + sizeof(SharedTail) + 1024;
+    int n_stages = RING_BYTES / (A_BYTES + 2 * bnh * BK * 2);
+    if (n_stages > MAX_STAGES) n_stages = MAX_STAGES;
     auto k = gemm_tc_kernel<EPI>;
     if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
         return SPITE_LAUNCH_FAILED;
     const int grid = (int)(total < n_blocks ? total : n_blocks);
-    k<<<grid, THREADS, smem, st>>>(ma, mw, p, bnh, row_tiles, (int)total);
+    k<<<grid, THREADS, smem, st>>>(ma, mw, p, bnh, row_tiles, (int)total, n_stages);
     return spite_launch_status();
 }
 

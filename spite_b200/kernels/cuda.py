@@ -87,8 +87,8 @@ class CudaKernels(KernelSet):
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.use_tcgen05 = os.environ.get("SPITE_NO_TCGEN05", "") == ""
         # row counts up to which the weight-streaming kernel is preferred over the tcgen05 one
-        self.skinny_dense_max = int(os.environ.get("SPITE_SKINNY_DENSE_MAX", "16"))
-        self.skinny_group_avg = int(os.environ.get("SPITE_SKINNY_GROUP_AVG", "8"))
+        self.skinny_max_rows = int(os.environ.get("SPITE_SKINNY_MAX_ROWS", "16"))
+        self.skinny_tall_rows = int(os.environ.get("SPITE_SKINNY_TALL_ROWS", "0"))
 
     # ------------------------------------------------------------------ helpers
     def _lib(self, name):
@@ -139,7 +139,9 @@ class CudaKernels(KernelSet):
         `p.a_rows` gathers: the tcgen05 kernel wants contiguous rows, so they are gathered first."""
         if self.dtype == torch.bfloat16:
             grouped = bool(p.group_offsets)
-            few = p.M <= (min(self.skinny_group_avg * p.n_groups, 512) if grouped else self.skinny_dense_max)
+            # measured on B200 at Scout shapes: the streaming kernel wins up to 16 rows except on very
+            # tall matrices (output head), where the TMA pipeline of the tcgen05 kernel streams better
+            few = p.M <= self.skinny_max_rows and not (not grouped and p.N >= 65536 and p.M > self.skinny_tall_rows)
             tc_ok = self.use_tcgen05 and p.K % 8 == 0 and p.lda % 8 == 0
             if few or (not tc_ok and max_rows_per_group <= 64):
                 st = self._lib("gemm_skinny").spite_gemm_skinny(C.byref(p), int(max_rows_per_group), 2 * self.sm_count,
