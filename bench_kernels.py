@@ -5,6 +5,7 @@ peak.  Also the small driver that `ncu` captures for the summaries under `profil
     python bench_kernels.py                      # all cases, one JSON line each
     python bench_kernels.py --only gemm_decode   # one family (for ncu: -k regex:...)
     python bench_kernels.py --small              # shapes a profiler can replay in seconds
+    python bench_kernels.py --only gemm_decode --case "lm_head M=8"   # one case
 
 Families: gemm_decode (weight streaming, mma.sync), gemm_prefill (tcgen05/TMA),
 moe_decode, moe_prefill (grouped products), attention_decode, attention_prefill,
@@ -33,6 +34,7 @@ def main(argv=None):
     ap.add_argument("--only", default="")
     ap.add_argument("--small", action="store_true")
     ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--case", default="", help="run only the cases whose name contains this text")
     args = ap.parse_args(argv)
     dev = "cuda:0"
     torch.cuda.set_device(0)
@@ -45,7 +47,7 @@ def main(argv=None):
         V = 32768
     rnd = lambda *s: (torch.randn(s, device=dev, dtype=torch.float32) * 0.05).to(bf)
 
-    def timed(fn, iters=args.iters):
+    def _timed(fn, iters):
         """One launch between two events, L2 flushed before it.  Includes the launch latency:
         right for kernels of hundreds of microseconds, too pessimistic for short ones."""
         for _ in range(3):
@@ -62,7 +64,7 @@ def main(argv=None):
         ms.sort()
         return ms[len(ms) // 2]
 
-    def timed_rotating(make, nbytes, iters=args.iters):
+    def _timed_rotating(make, nbytes, iters):
         """Short kernels: `make()` builds a launch closure on fresh operands; enough copies are
         made that together they exceed L2 several times, and they run back to back between two
         events, so every launch finds its operands in HBM and no launch gap is counted."""
@@ -86,7 +88,14 @@ def main(argv=None):
         best.sort()
         return best[len(best) // 2]
 
-    def report(family, name, ms, nbytes=0, flops=0, **extra):
+    # the timers are lazy, so that a case filtered out by --case launches nothing
+    timed = lambda fn, iters=args.iters: (lambda: _timed(fn, iters))
+    timed_rotating = lambda make, nbytes, iters=args.iters: (lambda: _timed_rotating(make, nbytes, iters))
+
+    def report(family, name, timer, nbytes=0, flops=0, **extra):
+        if args.case and args.case not in name:
+            return
+        ms = timer()
         out = {"family": family, "case": name, "us": round(ms * 1e3, 2)}
         if nbytes:
             gbs = nbytes / (ms * 1e-3) / 1e9

@@ -16,6 +16,8 @@ namespace {
 template <typename T>
 __global__ void __launch_bounds__(128) qk_prepare_kernel(const QkPrepareParams p, const StepTokens b,
                                                          const PagedCache c) {
+    pdl_wait();
+    pdl_launch_dependents();
     const int t = blockIdx.x;
     const int lane = threadIdx.x & 31;
     const int head = blockIdx.y * 4 + (threadIdx.x >> 5);
@@ -88,6 +90,9 @@ template <typename T>
 __global__ void __launch_bounds__(128) paged_attention_kernel(const AttentionParams p, const StepTokens b,
                                                               const PagedCache c) {
     __shared__ float q_s[4][256];
+    pdl_wait();
+    pdl_launch_dependents();
+
     const int t = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int h = blockIdx.y * 4 + warp;
@@ -172,8 +177,8 @@ SPITE_API int spite_qk_prepare(int dtype, const QkPrepareParams* p, const StepTo
     dim3 grid(b->n_tokens, (heads + 3) / 4);
     if (grid.y > 65535) return SPITE_UNSUPPORTED;
     cudaStream_t st = (cudaStream_t)stream;
-    if (dtype == SPITE_DT_F32) qk_prepare_kernel<float><<<grid, 128, 0, st>>>(*p, *b, *c);
-    else if (dtype == SPITE_DT_BF16) qk_prepare_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>(*p, *b, *c);
+    if (dtype == SPITE_DT_F32) SPITE_LAUNCH(qk_prepare_kernel<float>, grid, 128, 0, st, *p, *b, *c);
+    else if (dtype == SPITE_DT_BF16) SPITE_LAUNCH(qk_prepare_kernel<__nv_bfloat16>, grid, 128, 0, st, *p, *b, *c);
     else return SPITE_BAD_ARG;
     return spite_launch_status();
 }
@@ -189,8 +194,8 @@ SPITE_API int spite_paged_attention(int dtype, const AttentionParams* p, const S
     dim3 grid(b->n_tokens, (p->num_heads + 3) / 4);
     if (grid.y > 65535) return SPITE_UNSUPPORTED;
     cudaStream_t st = (cudaStream_t)stream;
-    if (dtype == SPITE_DT_F32) paged_attention_kernel<float><<<grid, 128, 0, st>>>(*p, *b, *c);
-    else if (dtype == SPITE_DT_BF16) paged_attention_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>(*p, *b, *c);
+    if (dtype == SPITE_DT_F32) SPITE_LAUNCH(paged_attention_kernel<float>, grid, 128, 0, st, *p, *b, *c);
+    else if (dtype == SPITE_DT_BF16) SPITE_LAUNCH(paged_attention_kernel<__nv_bfloat16>, grid, 128, 0, st, *p, *b, *c);
     else return SPITE_BAD_ARG;
     return spite_launch_status();
 }

@@ -55,6 +55,8 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_kernel(const AttentionPar
     constexpr int SWZ = (CH % 8 == 0) ? 7 : 0;          // xor of the chunk index with the row, where rows alias
     constexpr int TILE_BYTES = TILE * HD * 2;
     extern __shared__ __align__(128) unsigned char smem[];
+    pdl_wait();
+    pdl_launch_dependents();
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, cc = lane & 3;
@@ -271,6 +273,8 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(const float* __restrict
                                                          __nv_bfloat16* __restrict__ out, int n_splits, int hd,
                                                          int num_heads, const int* __restrict__ seg_of_token,
                                                          const int* __restrict__ cu_seqlens, int seg_min, int seg_max) {
+    pdl_wait();
+    pdl_launch_dependents();
     const size_t row = blockIdx.x;
     const int seg = seg_of_token[row / num_heads];
     const int seg_n = cu_seqlens[seg + 1] - cu_seqlens[seg];
@@ -303,7 +307,7 @@ int launch(const AttentionParams& p, const StepTokens& b, const PagedCache& c, c
         cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
         return SPITE_LAUNCH_FAILED;
     dim3 grid(n_blocks, c.num_kv_heads, x.n_splits);
-    k<<<grid, WARPS * 32, smem, st>>>(p, b, c, x);
+    SPITE_LAUNCH(k, grid, WARPS * 32, smem, st, p, b, c, x);
     return spite_launch_status();
 }
 
@@ -338,9 +342,8 @@ SPITE_API int spite_paged_attention_mma(const AttentionParams* p, const StepToke
         default: rc = launch<8>(*p, *b, *c, *x, n_blocks, st); break;
     }
     if (rc != SPITE_OK || x->n_splits == 1) return rc;
-    attn_merge_kernel<<<b->n_tokens * p->num_heads, 128, 0, st>>>(x->o_part, x->ml_part, (__nv_bfloat16*)p->out,
-                                                                  x->n_splits, c->head_dim, p->num_heads,
-                                                                  b->seg_of_token, x->cu_seqlens, x->seg_min_tokens,
-                                                                  x->seg_max_tokens);
+    SPITE_LAUNCH(attn_merge_kernel, b->n_tokens * p->num_heads, 128, 0, st, (const float*)x->o_part,
+                 (const float*)x->ml_part, (__nv_bfloat16*)p->out, x->n_splits, c->head_dim, p->num_heads,
+                 b->seg_of_token, x->cu_seqlens, x->seg_min_tokens, x->seg_max_tokens);
     return spite_launch_status();
 }

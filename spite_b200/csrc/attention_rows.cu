@@ -56,6 +56,8 @@ __global__ void __launch_bounds__(WARPS * 32) attn_rows_kernel(const AttentionPa
     constexpr int SWZ = (CH % 8 == 0) ? 7 : 0;          // xor of the chunk index with the row, where rows alias
     constexpr int TILE_BYTES = TILE * HD * 2;
     extern __shared__ __align__(128) unsigned char smem[];   // [stage][K, V][32][HD]
+    pdl_wait();
+    pdl_launch_dependents();
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, cc = lane & 3;
@@ -251,7 +253,7 @@ int launch(const AttentionParams& p, const StepTokens& b, const PagedCache& c, c
         cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
         return SPITE_LAUNCH_FAILED;
     dim3 grid(n_blocks, c.num_kv_heads);
-    k<<<grid, WARPS * 32, smem, st>>>(p, b, c, x);
+    SPITE_LAUNCH(k, grid, WARPS * 32, smem, st, p, b, c, x);
     return spite_launch_status();
 }
 

@@ -63,3 +63,43 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
     __syncthreads();
     return scratch[32];
 }
+
+// ---------------------------------------------------------------------------------
+// Programmatic dependent launch.  Kernels of a step run back to back on one stream; with
+// this launch attribute the next kernel's blocks may be set up while the last blocks of
+// the current one still run.  Every kernel launched this way starts with pdl_wait(): it
+// returns when the preceding kernel has finished and its writes are visible, so nothing
+// a kernel reads or writes can race with its predecessor.  What a kernel does before
+// pdl_wait() must not touch anything an earlier kernel of the step writes (weights only).
+// SPITE_NO_PDL=1 in the environment switches the attribute off.
+// ---------------------------------------------------------------------------------
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+
+#include <cstdlib>
+static inline bool spite_pdl_enabled() {
+    static int on = -1;
+    if (on < 0) {
+        const char* e = getenv("SPITE_NO_PDL");
+        on = (e && e[0] && e[0] != '0') ? 0 : 1;
+    }
+    return on == 1;
+}
+
+template <typename... P, typename... A>
+static inline void spite_launch_kernel(void (*kernel)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                       A&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = spite_pdl_enabled() ? 1 : 0;
+    (void)cudaLaunchKernelEx(&cfg, kernel, static_cast<A&&>(args)...);
+}
+#define SPITE_LAUNCH(kernel, grid, block, smem, stream, ...) \
+    spite_launch_kernel(kernel, dim3(grid), dim3(block), smem, stream, __VA_ARGS__)

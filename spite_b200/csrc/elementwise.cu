@@ -7,6 +7,8 @@
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ tokens,
                              float* __restrict__ h, int d, int vocab) {
+    pdl_wait();
+    pdl_launch_dependents();
     const int m = blockIdx.x;
     const int tok = tokens[m];
     float* out = h + (size_t)m * d;
@@ -23,6 +25,8 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
 template <typename T>
 __global__ void rms_norm_kernel(const float* __restrict__ x, const float* __restrict__ gain,
                                 const int* __restrict__ rows, T* __restrict__ y, int d, float eps) {
+    pdl_wait();
+    pdl_launch_dependents();
     __shared__ float scratch[33];
     const int i = blockIdx.x;
     const int r = rows ? rows[i] : i;
@@ -38,6 +42,8 @@ __global__ void rms_norm_kernel(const float* __restrict__ x, const float* __rest
 // dst[i, :] = src[idx[i], :]   (rows of activations brought into expert order), 16 bytes per thread and step
 __global__ void gather_rows_kernel(const uint4* __restrict__ src, const int* __restrict__ idx,
                                    uint4* __restrict__ dst, int row_vecs) {
+    pdl_wait();
+    pdl_launch_dependents();
     const size_t i = blockIdx.x;
     const uint4* in = src + (size_t)idx[i] * row_vecs;
     uint4* out = dst + i * row_vecs;
@@ -49,8 +55,8 @@ SPITE_API int spite_gather_rows(const void* src, const int* idx, void* dst, int 
     if (!src || !idx || !dst || n_rows < 0 || row_bytes <= 0) return SPITE_BAD_ARG;
     if (row_bytes % 16 || (((uintptr_t)src | (uintptr_t)dst) & 15)) return SPITE_UNSUPPORTED;
     if (n_rows == 0) return SPITE_OK;
-    gather_rows_kernel<<<n_rows, 128, 0, (cudaStream_t)stream>>>((const uint4*)src, idx, (uint4*)dst,
-                                                                 (int)(row_bytes / 16));
+    SPITE_LAUNCH(gather_rows_kernel, n_rows, 128, 0, (cudaStream_t)stream, (const uint4*)src, idx, (uint4*)dst,
+                 (int)(row_bytes / 16));
     return spite_launch_status();
 }
 
@@ -61,9 +67,9 @@ SPITE_API int spite_embed(int dtype, const void* table, const int* tokens, float
     cudaStream_t st = (cudaStream_t)stream;
     const int threads = d >= 1024 ? 256 : 128;
     if (dtype == SPITE_DT_F32)
-        embed_kernel<float><<<n_tokens, threads, 0, st>>>((const float*)table, tokens, h, d, vocab);
+        SPITE_LAUNCH(embed_kernel<float>, n_tokens, threads, 0, st, (const float*)table, tokens, h, d, vocab);
     else if (dtype == SPITE_DT_BF16)
-        embed_kernel<__nv_bfloat16><<<n_tokens, threads, 0, st>>>((const __nv_bfloat16*)table, tokens, h, d, vocab);
+        SPITE_LAUNCH(embed_kernel<__nv_bfloat16>, n_tokens, threads, 0, st, (const __nv_bfloat16*)table, tokens, h, d, vocab);
     else
         return SPITE_BAD_ARG;
     return spite_launch_status();
@@ -76,9 +82,9 @@ SPITE_API int spite_rms_norm(int out_dtype, const float* x, const float* gain, c
     cudaStream_t st = (cudaStream_t)stream;
     const int threads = d >= 2048 ? 512 : (d >= 512 ? 256 : 128);
     if (out_dtype == SPITE_DT_F32)
-        rms_norm_kernel<float><<<n_rows, threads, 0, st>>>(x, gain, rows, (float*)y, d, eps);
+        SPITE_LAUNCH(rms_norm_kernel<float>, n_rows, threads, 0, st, x, gain, rows, (float*)y, d, eps);
     else if (out_dtype == SPITE_DT_BF16)
-        rms_norm_kernel<__nv_bfloat16><<<n_rows, threads, 0, st>>>(x, gain, rows, (__nv_bfloat16*)y, d, eps);
+        SPITE_LAUNCH(rms_norm_kernel<__nv_bfloat16>, n_rows, threads, 0, st, x, gain, rows, (__nv_bfloat16*)y, d, eps);
     else
         return SPITE_BAD_ARG;
     return spite_launch_status();

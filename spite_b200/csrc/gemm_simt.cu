@@ -19,6 +19,8 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const GemmParams p) {
     __shared__ float As[BK][BM + 4];
     __shared__ float Ws[DUAL ? 2 : 1][BK][BN + 4];
     __shared__ int a_row_s[BM];
+    pdl_wait();
+    pdl_launch_dependents();
 
     int group, row0, rows;
     if (!locate_row_tile(p, blockIdx.y, BM, group, row0, rows)) return;
@@ -113,10 +115,10 @@ int launch(const GemmParams& p, cudaStream_t st) {
     dim3 grid((p.N + BN - 1) / BN, row_tiles);
     if (grid.y > 65535) return SPITE_UNSUPPORTED;
     switch (p.epilogue) {
-        case EPI_STORE: gemm_simt_kernel<T, EPI_STORE><<<grid, 256, 0, st>>>(p); break;
-        case EPI_STORE_F32: gemm_simt_kernel<T, EPI_STORE_F32><<<grid, 256, 0, st>>>(p); break;
-        case EPI_ADD_F32: gemm_simt_kernel<T, EPI_ADD_F32><<<grid, 256, 0, st>>>(p); break;
-        case EPI_SWIGLU: gemm_simt_kernel<T, EPI_SWIGLU><<<grid, 256, 0, st>>>(p); break;
+        case EPI_STORE: SPITE_LAUNCH((gemm_simt_kernel<T, EPI_STORE>), grid, 256, 0, st, p); break;
+        case EPI_STORE_F32: SPITE_LAUNCH((gemm_simt_kernel<T, EPI_STORE_F32>), grid, 256, 0, st, p); break;
+        case EPI_ADD_F32: SPITE_LAUNCH((gemm_simt_kernel<T, EPI_ADD_F32>), grid, 256, 0, st, p); break;
+        case EPI_SWIGLU: SPITE_LAUNCH((gemm_simt_kernel<T, EPI_SWIGLU>), grid, 256, 0, st, p); break;
         default: return SPITE_BAD_ARG;
     }
     return spite_launch_status();

@@ -35,7 +35,7 @@ __device__ __forceinline__ void mma16816(float (&d)[4], unsigned a0, unsigned a1
 
 __device__ __forceinline__ uint4 ld_stream(const void* p) {     // read once: do not keep in L1
     uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+    asm volatile("ld.global.nc.L1::no_allocate.L2::256B.v4.u32 {%0,%1,%2,%3}, [%4];\n"
                  : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
     return v;
 }
@@ -56,20 +56,35 @@ __global__ void __launch_bounds__(WARPS * 32, (NT <= 1 ? 2 : 1)) gemm_skinny_ker
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, c = lane & 3;
     const int n_tiles = (p.N + ROWS - 1) / ROWS;
+    // Routed calls read the group sizes, which the step's router wrote: wait for it first.
+    // One-group calls know their items without any earlier kernel's data: they start their
+    // first weight loads and wait only before they touch the tokens.
+    if (p.group_offsets) { pdl_wait(); pdl_launch_dependents(); }
 
     // (group, chunk of TOK tokens) pairs that have tokens: a group with more than TOK tokens
     // streams its weights once per chunk
-    if (threadIdx.x == 0) {
+    if (warp == 0) {
+        // lanes read the group sizes side by side (one round trip to memory for 32 groups),
+        // then the list is written in group order
         int n = 0;
-        if (p.group_offsets) {
-            for (int e = 0; e < p.n_groups && n < MAX_ACTIVE; ++e) {
-                const int m = p.group_offsets[e + 1] - p.group_offsets[e];
-                for (int ch = 0; ch * TOK < m && n < MAX_ACTIVE; ++ch) active_s[n++] = e | (ch << 16);
+        const int groups = p.group_offsets ? p.n_groups : 1;
+        for (int e0 = 0; e0 < groups; e0 += 32) {
+            const int e = e0 + lane;
+            int m = 0;
+            if (e < groups) m = p.group_offsets ? p.group_offsets[e + 1] - p.group_offsets[e] : p.M;
+            const int chunks = (m + TOK - 1) / TOK;
+            int before = chunks;                                 // inclusive scan of the chunk counts
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int v = __shfl_up_sync(0xffffffffu, before, o);
+                if (lane >= o) before += v;
             }
-        } else {
-            for (int ch = 0; ch * TOK < p.M && n < MAX_ACTIVE; ++ch) active_s[n++] = ch << 16;
+            const int start = n + before - chunks;
+            for (int ch = 0; ch < chunks; ++ch)
+                if (start + ch < MAX_ACTIVE) active_s[start + ch] = e | (ch << 16);
+            n += __shfl_sync(0xffffffffu, before, 31);
         }
-        n_active_s = n;
+        if (lane == 0) n_active_s = min(n, MAX_ACTIVE);
     }
     __syncthreads();
     const int total = n_active_s * n_tiles;
@@ -125,15 +140,17 @@ __global__ void __launch_bounds__(WARPS * 32, (NT <= 1 ? 2 : 1)) gemm_skinny_ker
     uint4 xbuf[U][NT];
 
     // first U steps of an item into the ring
-    auto fill_ring = [&]() {
+    auto fill_ring = [&](bool with_weights) {
 #pragma unroll
         for (int u = 0; u < U; ++u) {
             if (u < n_my) {
                 const size_t off = (size_t)(s_begin + u) * 32;
+                if (with_weights) {
 #pragma unroll
-                for (int f = 0; f < NFRAG; ++f)
+                    for (int f = 0; f < NFRAG; ++f)
 #pragma unroll
-                    for (int h = 0; h < 2; ++h) wbuf[u][f][h] = ld_stream(wrow[f][h] + off);
+                        for (int h = 0; h < 2; ++h) wbuf[u][f][h] = ld_stream(wrow[f][h] + off);
+                }
 #pragma unroll
                 for (int j = 0; j < NT; ++j)
                     xbuf[u][j] = xrow[j] ? *(const uint4*)(xrow[j] + off) : make_uint4(0, 0, 0, 0);
@@ -141,8 +158,20 @@ __global__ void __launch_bounds__(WARPS * 32, (NT <= 1 ? 2 : 1)) gemm_skinny_ker
         }
     };
     weight_rows(cur, wrow);
+    if (!p.group_offsets) {
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+            if (u < n_my) {
+#pragma unroll
+                for (int f = 0; f < NFRAG; ++f)
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) wbuf[u][f][h] = ld_stream(wrow[f][h] + (size_t)(s_begin + u) * 32);
+            }
+        pdl_wait();
+        pdl_launch_dependents();
+    }
     token_rows(cur, xrow);
-    fill_ring();
+    fill_ring(p.group_offsets != nullptr);          // one-group calls have their weights on the way already
 
     for (; i_cur < total; i_cur += gridDim.x) {
         float acc[NFRAG][NT][4];
@@ -189,7 +218,7 @@ __global__ void __launch_bounds__(WARPS * 32, (NT <= 1 ? 2 : 1)) gemm_skinny_ker
             cur = item_at(i_cur + gridDim.x);
             weight_rows(cur, wrow);
             token_rows(cur, xrow);
-            fill_ring();
+            fill_ring(true);
         }
         // partial sums of this warp: red[warp][fragment row][token]
         __syncthreads();
@@ -242,7 +271,7 @@ int launch_nt(const GemmParams& p, int n_blocks, cudaStream_t st) {
         if (smem > 44 * 1024 &&                                                                           \
             cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) \
             return SPITE_LAUNCH_FAILED;                                                                   \
-        k<<<grid, WARPS * 32, smem, st>>>(p);                                                             \
+        SPITE_LAUNCH(k, grid, WARPS * 32, smem, st, p);                                                   \
         break;                                                                                            \
     }
     switch (p.epilogue) {

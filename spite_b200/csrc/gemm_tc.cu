@@ -149,6 +149,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     SharedTail* tail = (SharedTail*)(smem + RING_BYTES);
+    pdl_wait();
+    pdl_launch_dependents();
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int num_kb = (p.K + BK - 1) / BK;
@@ -387,7 +389,7 @@ int launch(const GemmParams& p, int n_blocks, cudaStream_t st) {
     if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
         return SPITE_LAUNCH_FAILED;
     const int grid = (int)(total < n_blocks ? total : n_blocks);
-    k<<<grid, THREADS, smem, st>>>(ma, mw, p, bnh, row_tiles, (int)total, n_stages);
+    SPITE_LAUNCH(k, grid, THREADS, smem, st, ma, mw, p, bnh, row_tiles, (int)total, n_stages);
     return spite_launch_status();
 }
 

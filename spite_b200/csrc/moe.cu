@@ -24,6 +24,8 @@ __global__ void __launch_bounds__(256) route_kernel(const T* __restrict__ x, con
                                                     int* __restrict__ expert_ids, float* __restrict__ weights,
                                                     float* __restrict__ logits_out) {
     extern __shared__ __align__(16) float route_s[];         // [d] token, [n_experts] logits
+    pdl_wait();
+    pdl_launch_dependents();
     float* xs = route_s;
     float* lg = route_s + ((d + 3) & ~3);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -91,6 +93,8 @@ __global__ void __launch_bounds__(1024) sort_by_expert_kernel(const int* __restr
                                                               int* __restrict__ offsets,
                                                               int* __restrict__ sorted_rows) {
     __shared__ int counts[MAX_EXPERTS + 1];
+    pdl_wait();
+    pdl_launch_dependents();
     const int slot = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
     for (int e = threadIdx.x; e <= n_experts; e += blockDim.x) counts[e] = 0;
@@ -134,19 +138,20 @@ SPITE_API int spite_moe_route(int dtype, const void* x, const float* w_router, i
             if (smem > 48 * 1024)
                 attr = cudaFuncSetAttribute(route_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (attr != cudaSuccess) return SPITE_LAUNCH_FAILED;
-            route_kernel<float><<<n_tokens, 256, smem, st>>>((const float*)x, w_router, n_tokens, d, n_experts,
-                                                             top_k, expert_ids, weights, logits_out);
+            SPITE_LAUNCH(route_kernel<float>, n_tokens, 256, smem, st, (const float*)x, w_router, n_tokens, d, n_experts,
+                         top_k, expert_ids, weights, logits_out);
         } else if (dtype == SPITE_DT_BF16) {
             if (smem > 48 * 1024)
                 attr = cudaFuncSetAttribute(route_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (attr != cudaSuccess) return SPITE_LAUNCH_FAILED;
-            route_kernel<__nv_bfloat16><<<n_tokens, 256, smem, st>>>((const __nv_bfloat16*)x, w_router, n_tokens, d,
-                                                                     n_experts, top_k, expert_ids, weights, logits_out);
+            SPITE_LAUNCH(route_kernel<__nv_bfloat16>, n_tokens, 256, smem, st, (const __nv_bfloat16*)x, w_router, n_tokens, d,
+                         n_experts, top_k, expert_ids, weights, logits_out);
         } else {
             return SPITE_BAD_ARG;
         }
         if (cudaGetLastError() != cudaSuccess) return SPITE_LAUNCH_FAILED;
     }
-    sort_by_expert_kernel<<<top_k, 1024, 0, st>>>(expert_ids, n_tokens, n_experts, top_k, offsets, sorted_rows);
+    SPITE_LAUNCH(sort_by_expert_kernel, top_k, 1024, 0, st, (const int*)expert_ids, n_tokens, n_experts, top_k, offsets,
+                 sorted_rows);
     return spite_launch_status();
 }
