@@ -22,7 +22,6 @@
 namespace {
 
 constexpr int WARPS = 8;
-constexpr int NFRAG = 2;          // 16-row weight fragments per warp
 constexpr int MAX_GROUPS = 1024;
 constexpr int MAX_ACTIVE = MAX_GROUPS + 64;   // (group, token chunk) pairs of one call
 
@@ -44,10 +43,13 @@ struct Item {                     // one work item of a block
     int group, row_lo, m, tile;
 };
 
-template <int NT, int U, int EPI>
+// NFRAG: 16-row weight fragments per warp (2, or 1 for narrow matrices, which then have twice
+// as many items to spread over the multiprocessors; the SwiGLU form needs 2: gate and up).
+template <int NT, int U, int EPI, int NFRAG>
 __global__ void __launch_bounds__(WARPS * 32, (NT <= 1 ? 2 : 1)) gemm_skinny_kernel(const GemmParams p) {
     constexpr bool DUAL = (EPI == EPI_SWIGLU);
-    constexpr int ROWS = DUAL ? 16 : 32;                         // output columns (weight rows) per item
+    static_assert(!DUAL || NFRAG == 2, "the SwiGLU epilogue pairs a gate and an up fragment");
+    constexpr int ROWS = DUAL ? 16 : 16 * NFRAG;                 // output columns (weight rows) per item
     constexpr int TOK = NT * 8;
     extern __shared__ float red[];                               // [WARPS][NFRAG*16][TOK]
     __shared__ int active_s[MAX_ACTIVE];
@@ -259,15 +261,15 @@ __global__ void __launch_bounds__(WARPS * 32, (NT <= 1 ? 2 : 1)) gemm_skinny_ker
     }
 }
 
-template <int NT, int U>
-int launch_nt(const GemmParams& p, int n_blocks, cudaStream_t st) {
-    const int rows = p.epilogue == EPI_SWIGLU ? 16 : 32;
+template <int NT, int U, int NFRAG>
+int launch_nf(const GemmParams& p, int n_blocks, cudaStream_t st) {
+    const int rows = p.epilogue == EPI_SWIGLU ? 16 : 16 * NFRAG;
     const long long tiles = (long long)((p.N + rows - 1) / rows) * (p.group_offsets ? p.n_groups : 1);
     const int grid = (int)(tiles < n_blocks ? tiles : n_blocks);
     const size_t smem = (size_t)WARPS * NFRAG * 16 * NT * 8 * sizeof(float);
-#define SPITE_SKINNY_CASE(E)                                                                              \
+#define SPITE_SKINNY_CASE(E, NF)                                                                          \
     case E: {                                                                                             \
-        auto k = gemm_skinny_kernel<NT, U, E>;                                                            \
+        auto k = gemm_skinny_kernel<NT, U, E, NF>;                                                        \
         if (smem > 44 * 1024 &&                                                                           \
             cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) \
             return SPITE_LAUNCH_FAILED;                                                                   \
@@ -275,14 +277,22 @@ int launch_nt(const GemmParams& p, int n_blocks, cudaStream_t st) {
         break;                                                                                            \
     }
     switch (p.epilogue) {
-        SPITE_SKINNY_CASE(EPI_STORE)
-        SPITE_SKINNY_CASE(EPI_STORE_F32)
-        SPITE_SKINNY_CASE(EPI_ADD_F32)
-        SPITE_SKINNY_CASE(EPI_SWIGLU)
+        SPITE_SKINNY_CASE(EPI_STORE, NFRAG)
+        SPITE_SKINNY_CASE(EPI_STORE_F32, NFRAG)
+        SPITE_SKINNY_CASE(EPI_ADD_F32, NFRAG)
+        SPITE_SKINNY_CASE(EPI_SWIGLU, 2)
         default: return SPITE_BAD_ARG;
     }
 #undef SPITE_SKINNY_CASE
     return spite_launch_status();
+}
+
+// 32-row items throughout.  16-row items for narrow matrices (twice the items to spread) were
+// measured slower on B200 at 5120 x 5120 .. 7168 x 5120: the per-item reduction costs more than
+// the extra parallelism gains, so the one-fragment instantiation is not used.
+template <int NT, int U>
+int launch_nt(const GemmParams& p, int n_blocks, cudaStream_t st) {
+    return launch_nf<NT, U, 2>(p, n_blocks, st);
 }
 
 }  // namespace

@@ -1,97 +1,117 @@
 // Router of a mixture-of-experts feed-forward and the ordering of tokens by expert.
 //
-// route: logits = Wr x in float32 (crates/spite-models/src/moe.rs:65-66); the k
-//   largest raw logits are chosen, equal logits preferring the lower expert id
-//   (moe.rs:110-116, a stable descending sort); the weight is sigmoid(logit)
+// logits: l = Wr x in float32 (crates/spite-models/src/moe.rs:65-66).
+// select: the k largest raw logits are chosen, equal logits preferring the lower expert
+//   id (moe.rs:110-116, a stable descending sort); the weight is sigmoid(logit)
 //   (moe.rs:120).  No softmax, no renormalisation.
-// Choices are stored slot-major: expert_ids[slot][token], weights[slot][token].
+//   Choices are stored slot-major: expert_ids[slot][token], weights[slot][token].
 // sort: for every choice slot a stable counting sort of the tokens by expert:
 //   offsets[slot][e] .. offsets[slot][e+1] are the places of expert e's tokens in
 //   sorted_rows[slot][:], in ascending token order.  No host round trip: the grouped
 //   products read these arrays on the device.
+//
+// Two kernels.  The first computes the logits with many blocks (8 tokens x 2 experts a
+// block, its 8 warps splitting the width), so that a decode step of a few tokens still
+// spreads over several multiprocessors and a prompt portion reads the router's weights
+// once per 8 tokens.  The second, one block per choice slot, selects and sorts.
+// A logit is summed in an order fixed by the width alone.
 #include "common.cuh"
 
 namespace {
 
 constexpr int MAX_EXPERTS = 1024;
+constexpr int TB = 8;                  // tokens per block of the logits kernel
+constexpr int EB = 2;                  // experts per block
+constexpr int WARPS = 8;
 
-// grid tokens, block 256: the token's row is staged in shared memory as float32, every
-// warp takes experts e = warp, warp + 8, ...; warp 0 then picks the k largest logits.
-// A logit is summed in an order fixed by the width d alone.
+__device__ __forceinline__ void load4(const float* p, float (&v)[4]) {
+    const float4 t = *(const float4*)p;
+    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+}
+__device__ __forceinline__ void load4(const __nv_bfloat16* p, float (&v)[4]) {
+    const uint2 t = *(const uint2*)p;
+    const __nv_bfloat162 a = *(const __nv_bfloat162*)&t.x, b = *(const __nv_bfloat162*)&t.y;
+    v[0] = __low2float(a); v[1] = __high2float(a); v[2] = __low2float(b); v[3] = __high2float(b);
+}
+
+// grid (ceil(tokens / TB), ceil(experts / EB)), block 256
 template <typename T>
-__global__ void __launch_bounds__(256) route_kernel(const T* __restrict__ x, const float* __restrict__ wr,
-                                                    int n_tokens, int d, int n_experts, int top_k,
-                                                    int* __restrict__ expert_ids, float* __restrict__ weights,
-                                                    float* __restrict__ logits_out) {
-    extern __shared__ __align__(16) float route_s[];         // [d] token, [n_experts] logits
+__global__ void __launch_bounds__(WARPS * 32) route_logits_kernel(const T* __restrict__ x, const float* __restrict__ wr,
+                                                                 int n_tokens, int d, int n_experts,
+                                                                 float* __restrict__ logits) {
+    __shared__ float part[WARPS][EB * TB];
     pdl_wait();
     pdl_launch_dependents();
-    float* xs = route_s;
-    float* lg = route_s + ((d + 3) & ~3);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int t = blockIdx.x;
-    const T* xr = x + (size_t)t * d;
-    for (int k = threadIdx.x; k < d; k += blockDim.x) xs[k] = to_f32(xr[k]);
-    __syncthreads();
-    const bool vec = (d % 4 == 0) && (((uintptr_t)wr & 15) == 0);
-    for (int e = warp; e < n_experts; e += 8) {
-        const float* w = wr + (size_t)e * d;
-        float s0 = 0.f, s1 = 0.f;
-        if (vec) {
-            const float4* w4 = (const float4*)w;
-            const float4* x4 = (const float4*)xs;
-            const int n4 = d >> 2;
-            int k = lane;
-            for (; k + 32 < n4; k += 64) {
-                const float4 a = w4[k], b = w4[k + 32];
-                const float4 xa = x4[k], xb = x4[k + 32];
-                s0 = fmaf(xa.x, a.x, s0); s0 = fmaf(xa.y, a.y, s0); s0 = fmaf(xa.z, a.z, s0); s0 = fmaf(xa.w, a.w, s0);
-                s1 = fmaf(xb.x, b.x, s1); s1 = fmaf(xb.y, b.y, s1); s1 = fmaf(xb.z, b.z, s1); s1 = fmaf(xb.w, b.w, s1);
+    const int t0 = blockIdx.x * TB, e0 = blockIdx.y * EB;
+    float acc[EB][TB];
+#pragma unroll
+    for (int e = 0; e < EB; ++e)
+#pragma unroll
+        for (int t = 0; t < TB; ++t) acc[e][t] = 0.f;
+
+    const bool vec = (d % 4 == 0) && (((uintptr_t)wr & 15) == 0) && (((uintptr_t)x & 15) == 0);
+    if (vec) {
+        const int n4 = d >> 2;                                // groups of four elements
+        const int lo = (int)((long long)n4 * warp / WARPS), hi = (int)((long long)n4 * (warp + 1) / WARPS);
+        for (int k4 = lo + lane; k4 < hi; k4 += 32) {
+            float w[EB][4];
+#pragma unroll
+            for (int e = 0; e < EB; ++e) {
+                if (e0 + e < n_experts) load4(wr + (size_t)(e0 + e) * d + 4 * k4, w[e]);
+                else w[e][0] = w[e][1] = w[e][2] = w[e][3] = 0.f;
             }
-            for (; k < n4; k += 32) {
-                const float4 a = w4[k];
-                const float4 xa = x4[k];
-                s0 = fmaf(xa.x, a.x, s0); s0 = fmaf(xa.y, a.y, s0); s0 = fmaf(xa.z, a.z, s0); s0 = fmaf(xa.w, a.w, s0);
+#pragma unroll
+            for (int t = 0; t < TB; ++t) {
+                if (t0 + t < n_tokens) {
+                    float xv[4];
+                    load4(x + (size_t)(t0 + t) * d + 4 * k4, xv);
+#pragma unroll
+                    for (int e = 0; e < EB; ++e)
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) acc[e][t] = fmaf(xv[i], w[e][i], acc[e][t]);
+                }
             }
-        } else {
-            for (int k = lane; k < d; k += 32) s0 = fmaf(xs[k], w[k], s0);
         }
-        const float sum = warp_sum(s0 + s1);
-        if (lane == 0) {
-            lg[e] = sum;
-            if (logits_out) logits_out[(size_t)t * n_experts + e] = sum;
+    } else {
+        const int lo = (int)((long long)d * warp / WARPS), hi = (int)((long long)d * (warp + 1) / WARPS);
+        for (int k = lo + lane; k < hi; k += 32) {
+#pragma unroll
+            for (int t = 0; t < TB; ++t) {
+                if (t0 + t < n_tokens) {
+                    const float xv = to_f32(x[(size_t)(t0 + t) * d + k]);
+#pragma unroll
+                    for (int e = 0; e < EB; ++e)
+                        if (e0 + e < n_experts) acc[e][t] = fmaf(xv, wr[(size_t)(e0 + e) * d + k], acc[e][t]);
+                }
+            }
         }
     }
-    __syncthreads();
-    if (warp != 0) return;
-    for (int slot = 0; slot < top_k; ++slot) {
-        float best = -INFINITY;
-        int best_e = 0x7fffffff;
-        for (int e = lane; e < n_experts; e += 32) {
-            const float v = lg[e];
-            if (v > best || (v == best && e < best_e)) { best = v; best_e = e; }
-        }
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-            const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
-            if (ov > best || (ov == best && oe < best_e)) { best = ov; best_e = oe; }
+    for (int e = 0; e < EB; ++e)
+#pragma unroll
+        for (int t = 0; t < TB; ++t) {
+            const float s = warp_sum(acc[e][t]);
+            if (lane == 0) part[warp][e * TB + t] = s;
         }
-        if (best_e == 0x7fffffff) best_e = 0;                // all logits NaN: still a valid id
-        if (lane == 0) {
-            expert_ids[(size_t)slot * n_tokens + t] = best_e;
-            weights[(size_t)slot * n_tokens + t] = 1.0f / (1.0f + expf(-best));
-            lg[best_e] = -INFINITY;
+    __syncthreads();
+    if (threadIdx.x < EB * TB) {
+        const int e = threadIdx.x / TB, t = threadIdx.x % TB;
+        if (e0 + e < n_experts && t0 + t < n_tokens) {
+            float s = 0.f;
+#pragma unroll
+            for (int w = 0; w < WARPS; ++w) s += part[w][threadIdx.x];
+            logits[(size_t)(t0 + t) * n_experts + e0 + e] = s;
         }
-        __syncwarp();
     }
 }
 
-// grid top_k, block 1024: block `slot` sorts the tokens by their slot-th expert.
-__global__ void __launch_bounds__(1024) sort_by_expert_kernel(const int* __restrict__ expert_ids, int n_tokens,
-                                                              int n_experts, int top_k,
-                                                              int* __restrict__ offsets,
-                                                              int* __restrict__ sorted_rows) {
+// grid top_k, block 1024: block `slot` picks every token's slot-th expert and sorts the tokens by it.
+__global__ void __launch_bounds__(1024) select_and_sort_kernel(const float* __restrict__ logits, int n_tokens,
+                                                               int n_experts, int top_k,
+                                                               int* __restrict__ expert_ids, float* __restrict__ weights,
+                                                               int* __restrict__ offsets,
+                                                               int* __restrict__ sorted_rows) {
     __shared__ int counts[MAX_EXPERTS + 1];
     pdl_wait();
     pdl_launch_dependents();
@@ -99,8 +119,30 @@ __global__ void __launch_bounds__(1024) sort_by_expert_kernel(const int* __restr
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
     for (int e = threadIdx.x; e <= n_experts; e += blockDim.x) counts[e] = 0;
     __syncthreads();
-    for (int t = threadIdx.x; t < n_tokens; t += blockDim.x)
-        atomicAdd(&counts[expert_ids[(size_t)slot * n_tokens + t] + 1], 1);
+    int* ids = expert_ids + (size_t)slot * n_tokens;
+    for (int t = threadIdx.x; t < n_tokens; t += blockDim.x) {
+        // the slot-th element in the order (logit descending, expert id ascending)
+        const float* l = logits + (size_t)t * n_experts;
+        float prev_v = INFINITY;
+        int prev_e = -1;
+        float best_v = 0.f;
+        int best_e = 0;
+        for (int s = 0; s <= slot; ++s) {
+            best_v = -INFINITY;
+            best_e = -1;
+            for (int e = 0; e < n_experts; ++e) {
+                const float v = l[e];
+                const bool after_prev = v < prev_v || (v == prev_v && e > prev_e);
+                if (after_prev && (best_e < 0 || v > best_v)) { best_v = v; best_e = e; }
+            }
+            if (best_e < 0) { best_e = 0; best_v = l[0]; }    // logits that do not compare (NaN): still a valid id
+            prev_v = best_v;
+            prev_e = best_e;
+        }
+        ids[t] = best_e;
+        weights[(size_t)slot * n_tokens + t] = 1.0f / (1.0f + expf(-best_v));
+        atomicAdd(&counts[best_e + 1], 1);
+    }
     __syncthreads();
     if (threadIdx.x == 0)
         for (int e = 0; e < n_experts; ++e) counts[e + 1] += counts[e];
@@ -113,7 +155,7 @@ __global__ void __launch_bounds__(1024) sort_by_expert_kernel(const int* __restr
         if (counts[e + 1] == base) continue;
         for (int t0 = 0; t0 < n_tokens; t0 += 32) {
             const int t = t0 + lane;
-            const bool mine = t < n_tokens && expert_ids[(size_t)slot * n_tokens + t] == e;
+            const bool mine = t < n_tokens && ids[t] == e;
             const unsigned mask = __ballot_sync(0xffffffffu, mine);
             if (mine) rows[base + __popc(mask & ((1u << lane) - 1u))] = t;
             base += __popc(mask);
@@ -123,35 +165,28 @@ __global__ void __launch_bounds__(1024) sort_by_expert_kernel(const int* __restr
 
 }  // namespace
 
+// `logits` [tokens, experts] float32 is always written (the caller owns it).
 SPITE_API int spite_moe_route(int dtype, const void* x, const float* w_router, int n_tokens, int d,
                               int n_experts, int top_k, int* expert_ids, float* weights,
-                              float* logits_out, int* offsets, int* sorted_rows, void* stream) {
-    if (!x || !w_router || !expert_ids || !weights || !offsets || !sorted_rows) return SPITE_BAD_ARG;
+                              float* logits, int* offsets, int* sorted_rows, void* stream) {
+    if (!x || !w_router || !expert_ids || !weights || !logits || !offsets || !sorted_rows) return SPITE_BAD_ARG;
     if (n_tokens < 0 || d <= 0 || n_experts < 1 || top_k < 1 || top_k > n_experts) return SPITE_BAD_ARG;
     if (n_experts > MAX_EXPERTS) return SPITE_UNSUPPORTED;
     cudaStream_t st = (cudaStream_t)stream;
     if (n_tokens > 0) {
-        const size_t smem = ((size_t)((d + 3) & ~3) + n_experts) * sizeof(float);
-        if (smem > 200 * 1024) return SPITE_UNSUPPORTED;
-        cudaError_t attr = cudaSuccess;
-        if (dtype == SPITE_DT_F32) {
-            if (smem > 48 * 1024)
-                attr = cudaFuncSetAttribute(route_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            if (attr != cudaSuccess) return SPITE_LAUNCH_FAILED;
-            SPITE_LAUNCH(route_kernel<float>, n_tokens, 256, smem, st, (const float*)x, w_router, n_tokens, d, n_experts,
-                         top_k, expert_ids, weights, logits_out);
-        } else if (dtype == SPITE_DT_BF16) {
-            if (smem > 48 * 1024)
-                attr = cudaFuncSetAttribute(route_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            if (attr != cudaSuccess) return SPITE_LAUNCH_FAILED;
-            SPITE_LAUNCH(route_kernel<__nv_bfloat16>, n_tokens, 256, smem, st, (const __nv_bfloat16*)x, w_router, n_tokens, d,
-                         n_experts, top_k, expert_ids, weights, logits_out);
-        } else {
+        dim3 grid((n_tokens + TB - 1) / TB, (n_experts + EB - 1) / EB);
+        if (grid.y > 65535) return SPITE_UNSUPPORTED;
+        if (dtype == SPITE_DT_F32)
+            SPITE_LAUNCH(route_logits_kernel<float>, grid, WARPS * 32, 0, st, (const float*)x, w_router, n_tokens, d,
+                         n_experts, logits);
+        else if (dtype == SPITE_DT_BF16)
+            SPITE_LAUNCH(route_logits_kernel<__nv_bfloat16>, grid, WARPS * 32, 0, st, (const __nv_bfloat16*)x, w_router,
+                         n_tokens, d, n_experts, logits);
+        else
             return SPITE_BAD_ARG;
-        }
         if (cudaGetLastError() != cudaSuccess) return SPITE_LAUNCH_FAILED;
     }
-    SPITE_LAUNCH(sort_by_expert_kernel, top_k, 1024, 0, st, (const int*)expert_ids, n_tokens, n_experts, top_k, offsets,
-                 sorted_rows);
+    SPITE_LAUNCH(select_and_sort_kernel, top_k, 1024, 0, st, (const float*)logits, n_tokens, n_experts, top_k,
+                 expert_ids, weights, offsets, sorted_rows);
     return spite_launch_status();
 }

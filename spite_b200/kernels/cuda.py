@@ -342,7 +342,7 @@ class CudaKernels(KernelSet):
         wts = torch.empty((top_k, M), dtype=torch.float32, device=dev)
         offsets = torch.empty((top_k, E + 1), dtype=torch.int32, device=dev)
         rows = torch.empty((top_k, M), dtype=torch.int32, device=dev)
-        logits = torch.empty((M, E), dtype=torch.float32, device=dev) if want_logits else None
+        logits = torch.empty((M, E), dtype=torch.float32, device=dev)
         st = self._lib("moe").spite_moe_route(
             self._dt, C.c_void_p(x.data_ptr()), C.c_void_p(w_router.data_ptr()), M, d, E, top_k,
             C.c_void_p(ids.data_ptr()), C.c_void_p(wts.data_ptr()), C.c_void_p(_ptr(logits)),
@@ -350,7 +350,7 @@ class CudaKernels(KernelSet):
         self.launches += 1
         self.launches += 1
         _check(st, "moe_route")
-        return Routing(ids, wts, offsets, rows, logits)
+        return Routing(ids, wts, offsets, rows, logits if want_logits else None)
 
     # ------------------------------------------------------------------ sampling
     def argmax(self, logits):
