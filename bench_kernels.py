@@ -106,7 +106,7 @@ def main(argv=None):
         out.update(peaks=src, **extra)
         print(json.dumps(out), flush=True)
 
-    want = lambda fam: not args.only or args.only == fam
+    want = lambda fam: not args.only or fam in args.only.split(",")
 
     # ---- plain products
     shapes = [("qkv", (nq + 2 * nkv) * hd, d), ("o_proj", d, nq * hd), ("shared_down", d, F), ("lm_head", V, d)]

@@ -26,9 +26,10 @@
 // beforehand); `a_rows`, if set, only indexes `row_scale`.  Edges in M, N and K are
 // covered by TMA's zero fill on loads and by bounds checks on stores.
 #include "gemm.cuh"
-#include <cuda.h>
+#include "tcgen05.cuh"
 
 namespace {
+using namespace tc;
 
 constexpr int BM = 128, BK = 64, UMMA_K = 16, MAX_STAGES = 8;
 constexpr int A_BYTES = BM * BK * 2;                     // 16 KiB
@@ -36,88 +37,9 @@ constexpr int B_BYTES = 256 * BK * 2;                    // room for 256 weight 
 constexpr int RING_BYTES = 4 * (A_BYTES + B_BYTES);      // 192 KiB of stages: 4 of the widest tile, up to 8 of narrower ones
 constexpr int ACC_COLS = 256, TMEM_COLS = 512;
 constexpr int THREADS = 192;
-constexpr long long WAIT_CYCLES = 4000000000ll;          // about two seconds
+constexpr int MAX_LISTED = 1024;                         // row tiles of a grouped product kept as a list in shared memory
 
 __device__ int g_tc_error = 0;
-
-// ---------------------------------------------------------------- PTX wrappers
-__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(unsigned bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(unsigned bar, unsigned parity) {
-    unsigned ok;
-    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.b32 %0, 1, 0, p;\n}\n"
-                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-// Waits for the phase of `parity`; gives up when the abort flag is up or time has run out.
-__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatile int* abort_flag, int code) {
-    if (mbar_try(bar, parity)) return true;
-    const long long t0 = clock64();
-    while (true) {
-        if (mbar_try(bar, parity)) return true;
-        if (*abort_flag) return false;
-        if (clock64() - t0 > WAIT_CYCLES) {
-            *abort_flag = 1;
-            atomicCAS(&g_tc_error, 0, code);
-            return false;
-        }
-    }
-}
-__device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap* map, int x, int y, unsigned bar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
-                 ::"r"(dst), "l"((unsigned long long)map), "r"(x), "r"(y), "r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(unsigned bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_mma(unsigned d_tmem, unsigned long long a_desc, unsigned long long b_desc,
-                                       unsigned idesc, unsigned accumulate) {
-    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
-                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
-                 ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void tc_ld32(float (&v)[32], unsigned taddr) {
-    unsigned r[32];
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-                 "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-                 : "r"(taddr) : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-}
-
-// Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: rows of 128
-// bytes, 8-row groups 1024 bytes apart (stride byte offset), descriptor version 1.
-__device__ __forceinline__ unsigned long long smem_desc(unsigned addr) {
-    unsigned long long d = 0;
-    d |= (unsigned long long)((addr & 0x3FFFF) >> 4);            // start address
-    d |= (unsigned long long)1 << 16;                            // leading byte offset (unused with swizzle)
-    d |= (unsigned long long)(1024 >> 4) << 32;                  // stride byte offset
-    d |= (unsigned long long)1 << 46;                            // version
-    d |= (unsigned long long)2 << 61;                            // SWIZZLE_128B
-    return d;
-}
-
-// kind::f16 instruction descriptor: float32 accumulator, bfloat16 A and B, both K-major.
-__host__ __device__ constexpr unsigned make_idesc(int m, int n) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(n >> 3) << 17) | ((unsigned)(m >> 4) << 24);
-}
 
 struct SharedTail {
     unsigned long long full[MAX_STAGES];
@@ -126,17 +48,30 @@ struct SharedTail {
     unsigned long long acc_empty[2];
     unsigned tmem_base;
     int abort_flag;
+    int n_row_tiles;                                     // row tiles that hold rows (grouped products: counted in the kernel)
+    int rt_group[MAX_LISTED], rt_row0[MAX_LISTED], rt_rows[MAX_LISTED];
 };
 
 // The tile with running index `idx`: column tile idx / row_tiles, row tile idx % row_tiles.
+// A grouped product cuts every group into row tiles of its own.  Their list is built once per
+// block in shared memory, so that only tiles that hold rows are dealt out to the blocks; a
+// product with more row tiles than the list takes (`listed` false) scans the group offsets instead
+// and skips the empty tiles at the end of each column.
 struct Tile {
     int group, row0, rows, n0;
     bool ok;
 };
-__device__ __forceinline__ Tile tile_at(const GemmParams& p, int idx, int row_tiles, int cols_per_tile) {
+__device__ __forceinline__ Tile tile_at(const GemmParams& p, const SharedTail* tail, bool listed, int idx,
+                                        int row_tiles, int cols_per_tile) {
     Tile t;
+    const int rt = idx % row_tiles;
     t.n0 = (idx / row_tiles) * cols_per_tile;
-    t.ok = locate_row_tile(p, idx % row_tiles, BM, t.group, t.row0, t.rows);
+    if (listed) {
+        t.group = tail->rt_group[rt]; t.row0 = tail->rt_row0[rt]; t.rows = tail->rt_rows[rt];
+        t.ok = true;
+    } else {
+        t.ok = locate_row_tile(p, rt, BM, t.group, t.row0, t.rows);
+    }
     return t;
 }
 
@@ -144,7 +79,7 @@ __device__ __forceinline__ Tile tile_at(const GemmParams& p, int idx, int row_ti
 template <int EPI>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-               const GemmParams p, const int bnh, const int row_tiles, const int total_tiles, const int n_stages) {
+               const GemmParams p, const int bnh, const int max_row_tiles, const int col_tiles, const int n_stages) {
     constexpr bool DUAL = (EPI == EPI_SWIGLU);
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -163,17 +98,42 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         for (int s = 0; s < n_stages; ++s) { mbar_init(smem_u32(&tail->full[s]), 1); mbar_init(smem_u32(&tail->empty[s]), 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(smem_u32(&tail->acc_full[b]), 1); mbar_init(smem_u32(&tail->acc_empty[b]), 4); }
         tail->abort_flag = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        mbar_init_fence();
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n"
-                     ::"r"(smem_u32(&tail->tmem_base)), "r"(TMEM_COLS) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+        tmem_alloc(&tail->tmem_base, TMEM_COLS);
     }
-    tc_fence_before();
+    const bool listed = p.group_offsets != nullptr && max_row_tiles <= MAX_LISTED;
+    if (warp == 2 && listed) {
+        // the row tiles of all groups in group order: 32 groups at a time, places by a warp scan
+        int base = 0;
+        for (int g0 = 0; g0 < p.n_groups; g0 += 32) {
+            const int g = g0 + lane;
+            int lo = 0, hi = 0;
+            if (g < p.n_groups) { lo = p.group_offsets[g]; hi = p.group_offsets[g + 1]; }
+            const int cnt = hi > lo ? (hi - lo + BM - 1) / BM : 0;
+            int incl = cnt;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int v = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += v;
+            }
+            const int at = base + incl - cnt;
+            for (int i = 0; i < cnt && at + i < MAX_LISTED; ++i) {
+                tail->rt_group[at + i] = g;
+                tail->rt_row0[at + i] = lo + i * BM;
+                tail->rt_rows[at + i] = min(BM, hi - lo - i * BM);
+            }
+            base += __shfl_sync(0xffffffffu, incl, 31);
+        }
+        if (lane == 0) tail->n_row_tiles = min(base, MAX_LISTED);
+    }
+    fence_before();
     __syncthreads();
-    tc_fence_after();
+    fence_after();
     const unsigned tmem = tail->tmem_base;
+    const int row_tiles = listed ? tail->n_row_tiles : max_row_tiles;
+    const int total_tiles = row_tiles * col_tiles;
 
     if (warp == 0) {
         if (lane == 0) {
@@ -183,12 +143,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             unsigned ph = 0;
             bool ok = true;
             for (int idx = blockIdx.x; idx < total_tiles && ok; idx += gridDim.x) {
-                const Tile t = tile_at(p, idx, row_tiles, cols_per_tile);
+                const Tile t = tile_at(p, tail, listed, idx, row_tiles, cols_per_tile);
                 if (!t.ok) continue;
                 const int wy0 = t.group * w_rows + t.n0;
                 const int wy1 = DUAL ? t.group * w_rows + p.N + t.n0 : wy0 + bnh;
                 for (int kb = 0; kb < num_kb; ++kb, ++it, s = (s + 1 == n_stages ? 0 : s + 1), ph ^= (s == 0)) {
-                    ok = mbar_wait(smem_u32(&tail->empty[s]), ph ^ 1, abort_flag, 1);
+                    ok = mbar_wait(smem_u32(&tail->empty[s]), ph ^ 1, abort_flag, &g_tc_error, 1);
                     if (!ok) break;
                     const unsigned bar = smem_u32(&tail->full[s]);
                     const unsigned dst = smem_u32(smem + s * stage_tx);
@@ -200,11 +160,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             }
             if (*abort_flag) {
                 // copies in flight must land before the block gives its shared memory back
-                for (int j = max(0, it - n_stages); j < it; ++j) {
-                    const long long t0 = clock64();
-                    while (!mbar_try(smem_u32(&tail->full[j % n_stages]), (j / n_stages) & 1) &&
-                           clock64() - t0 < WAIT_CYCLES) {}
-                }
+                for (int j = max(0, it - n_stages); j < it; ++j)
+                    mbar_drain(smem_u32(&tail->full[j % n_stages]), (j / n_stages) & 1);
             }
         }
     } else if (warp == 1) {
@@ -215,25 +172,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             unsigned ph = 0;
             bool ok = true;
             for (int idx = blockIdx.x; idx < total_tiles && ok; idx += gridDim.x) {
-                const Tile t = tile_at(p, idx, row_tiles, cols_per_tile);
+                const Tile t = tile_at(p, tail, listed, idx, row_tiles, cols_per_tile);
                 if (!t.ok) continue;
                 const int buf = lt & 1;
-                ok = mbar_wait(smem_u32(&tail->acc_empty[buf]), ((lt >> 1) & 1) ^ 1, abort_flag, 4);
+                ok = mbar_wait(smem_u32(&tail->acc_empty[buf]), ((lt >> 1) & 1) ^ 1, abort_flag, &g_tc_error, 4);
                 if (!ok) break;
-                tc_fence_after();
+                fence_after();
                 const unsigned d_tmem = tmem + buf * ACC_COLS;
                 for (int kb = 0; kb < num_kb; ++kb, s = (s + 1 == n_stages ? 0 : s + 1), ph ^= (s == 0)) {
-                    ok = mbar_wait(smem_u32(&tail->full[s]), ph, abort_flag, 2);
+                    ok = mbar_wait(smem_u32(&tail->full[s]), ph, abort_flag, &g_tc_error, 2);
                     if (!ok) break;
-                    tc_fence_after();
+                    fence_after();
                     const unsigned a_addr = smem_u32(smem + s * stage_tx);
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; ++k)
-                        tc_mma(d_tmem, smem_desc(a_addr + k * UMMA_K * 2), smem_desc(a_addr + A_BYTES + k * UMMA_K * 2),
+                        mma(d_tmem, smem_desc_k_major(a_addr + k * UMMA_K * 2), smem_desc_k_major(a_addr + A_BYTES + k * UMMA_K * 2),
                                idesc, (kb > 0 || k > 0) ? 1u : 0u);
-                    tc_commit(smem_u32(&tail->empty[s]));      // the stage is free once these MMAs have read it
+                    commit(smem_u32(&tail->empty[s]));      // the stage is free once these MMAs have read it
                 }
-                if (ok) tc_commit(smem_u32(&tail->acc_full[buf]));   // this accumulator is complete
+                if (ok) commit(smem_u32(&tail->acc_full[buf]));   // this accumulator is complete
                 ++lt;
             }
         }
@@ -244,12 +201,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         int lt = 0;
         bool ok = true;
         for (int idx = blockIdx.x; idx < total_tiles && ok; idx += gridDim.x) {
-            const Tile t = tile_at(p, idx, row_tiles, cols_per_tile);
+            const Tile t = tile_at(p, tail, listed, idx, row_tiles, cols_per_tile);
             if (!t.ok) continue;
             const int buf = lt & 1;
-            ok = mbar_wait(smem_u32(&tail->acc_full[buf]), (lt >> 1) & 1, abort_flag, 3);
+            ok = mbar_wait(smem_u32(&tail->acc_full[buf]), (lt >> 1) & 1, abort_flag, &g_tc_error, 3);
             if (!ok) break;
-            tc_fence_after();
+            fence_after();
             const int li = t.row0 + r;
             const bool row_ok = r < t.rows;
             int crow = li, srow = li;
@@ -265,9 +222,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll 1
             for (int c0 = 0; c0 < cols_per_tile; c0 += 32) {
                 float v[32];
-                tc_ld32(v, lane_addr + c0);                    // warp-collective: every lane takes part
+                ld32(v, lane_addr + c0);                    // warp-collective: every lane takes part
                 float u[32];
-                if (DUAL) tc_ld32(u, lane_addr + bnh + c0);
+                if (DUAL) ld32(u, lane_addr + bnh + c0);
                 const int n = t.n0 + c0;
                 if (!row_ok || n >= p.N) continue;
                 const size_t o = (size_t)crow * p.ldc + n;
@@ -311,48 +268,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 }
             }
             // this warp has read its lanes of the accumulator: hand it back to the tensor cores
-            tc_fence_before();
+            fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&tail->acc_empty[buf]));
             ++lt;
         }
     }
-    tc_fence_before();
+    fence_before();
     __syncthreads();
     if (warp == 1) {
-        tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+        fence_after();
+        tmem_free(tmem, TMEM_COLS);
     }
 }
 
 // ---------------------------------------------------------------- host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    if (!fn) {
-        void* ptr = nullptr;
-        cudaDriverEntryPointQueryResult res;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &res) == cudaSuccess &&
-            res == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiledFn)ptr;
-    }
-    return fn;
-}
-
 // A row-major [rows, cols] bfloat16 matrix with leading dimension ld; boxes of 64 columns x box_rows rows.
-bool make_map(CUtensorMap* map, const void* base, long long rows, long long cols, long long ld, int box_rows) {
-    EncodeTiledFn fn = encode_fn();
-    if (!fn) return false;
+bool make_matrix_map(CUtensorMap* map, const void* base, long long rows, long long cols, long long ld, int box_rows) {
     cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
     cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
     cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
-    cuuint32_t estr[2] = {1, 1};
-    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    return make_map(map, base, 2, dims, strides, box);
 }
 
 // Half-tile height that makes the tile waves fullest: fewest rounds of n_blocks tiles, weighted by
@@ -380,7 +316,7 @@ int launch(const GemmParams& p, int n_blocks, cudaStream_t st) {
     if (total > 0x7fffffff) return SPITE_UNSUPPORTED;
     const long long w_rows = (long long)(EPI == EPI_SWIGLU ? 2 : 1) * p.N * p.n_groups;
     CUtensorMap ma, mw;
-    if (!make_map(&ma, p.A, p.M, p.K, p.lda, BM) || !make_map(&mw, p.W, w_rows, p.K, p.K, bnh))
+    if (!make_matrix_map(&ma, p.A, p.M, p.K, p.lda, BM) || !make_matrix_map(&mw, p.W, w_rows, p.K, p.K, bnh))
         return SPITE_LAUNCH_FAILED;
     const size_t smem = (size_t)RING_BYTES + sizeof(SharedTail) + 1024;
     int n_stages = RING_BYTES / (A_BYTES + 2 * bnh * BK * 2);
@@ -389,7 +325,7 @@ int launch(const GemmParams& p, int n_blocks, cudaStream_t st) {
     if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
         return SPITE_LAUNCH_FAILED;
     const int grid = (int)(total < n_blocks ? total : n_blocks);
-    SPITE_LAUNCH(k, grid, THREADS, smem, st, ma, mw, p, bnh, row_tiles, (int)total, n_stages);
+    SPITE_LAUNCH(k, grid, THREADS, smem, st, ma, mw, p, bnh, row_tiles, (int)(total / row_tiles), n_stages);
     return spite_launch_status();
 }
 

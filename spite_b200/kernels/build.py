@@ -33,6 +33,7 @@ LIBRARIES = {
     "attention": (["attention.cu"], []),
     "attention_mma": (["attention_mma.cu"], []),
     "attention_rows": (["attention_rows.cu"], []),
+    "attention_tc": (["attention_tc.cu"], []),
     "moe": (["moe.cu"], []),
     "sampling": (["sampling.cu"], []),
 }

@@ -86,6 +86,9 @@ class CudaKernels(KernelSet):
         self.launches = 0          # kernels launched so far (for measurement reports)
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.use_tcgen05 = os.environ.get("SPITE_NO_TCGEN05", "") == ""
+        self.use_tcgen05_attention = os.environ.get("SPITE_NO_TCGEN05_ATTENTION", "") == ""
+        # fewest tokens of a request in a step that go to the tcgen05 attention kernel (0: one full tile of rows)
+        self.attention_tc_min_tokens = int(os.environ.get("SPITE_ATTENTION_TC_MIN_TOKENS", "0"))
         # row counts up to which the weight-streaming kernel is preferred over the tcgen05 one
         self.skinny_max_rows = int(os.environ.get("SPITE_SKINNY_MAX_ROWS", "16"))
         self.skinny_tall_rows = int(os.environ.get("SPITE_SKINNY_TALL_ROWS", "0"))
@@ -178,6 +181,10 @@ class CudaKernels(KernelSet):
         st = self._lib("gemm_simt").spite_gemm_simt(self._dt, C.byref(p), self._stream())
         self.launches += 1
         _check(st, what)
+
+    def attention_tc_error(self) -> int:
+        """Error code left by a tcgen05 attention block that gave up waiting (0: none); clears it. Synchronises."""
+        return int(self._lib("attention_tc").spite_attention_tc_error())
 
     def gemm_tc_error(self) -> int:
         """Error code left by a tcgen05 block that gave up waiting (0: none); clears it. Synchronises."""
@@ -280,20 +287,35 @@ class CudaKernels(KernelSet):
             # rows; segments of few tokens (decode) to the kernel with 16 rows a block whose
             # warps and blocks split the keys.
             big_from = -(-32 // group) if c.page_size % 32 == 0 else 1 << 30
-            tpb, tpb_rows = max(1, 16 // group), max(1, 64 // group)
-            n_small = n_big = 0
+            tpb, tpb_rows, tpb_tc = max(1, 16 // group), max(1, 64 // group), max(1, 128 // group)
+            # tcgen05 kernel (128 rows a block): head sizes 64 and 128, pages of a multiple of 64 keys
+            tc_from = 1 << 30
+            if c.head_dim in (64, 128) and c.page_size % 64 == 0 and self.use_tcgen05_attention:
+                tc_from = max(big_from, self.attention_tc_min_tokens or tpb_tc)
+            n_small = n_big = n_tc = 0
             longest = 1
             for s in batch.segments:
+                if s.n_tokens >= tc_from:
+                    n_tc += -(-s.n_tokens // tpb_tc)
+                    continue
                 if s.n_tokens >= big_from:
                     n_big += -(-s.n_tokens // tpb_rows)
                     continue
                 n_small += -(-s.n_tokens // tpb)
                 last = s.start_pos + s.n_tokens - 1
                 longest = max(longest, last - window.lowest_visible(max(s.start_pos, last - tpb + 1)) + 1)
+            if n_tc:
+                x = AttnMmaExtra(cu_seqlens=batch.cu_seqlens.data_ptr(), o_part=None, ml_part=None,
+                                 n_segments=len(batch.segments), tokens_per_block=tpb_tc, n_splits=1,
+                                 seg_min_tokens=tc_from, seg_max_tokens=0x7fffffff)
+                st = self._lib("attention_tc").spite_paged_attention_tc(
+                    C.byref(p), C.byref(b), C.byref(c), C.byref(x), n_tc, self._stream())
+                self.launches += 1
+                _check(st, "paged_attention (tcgen05, prompt portions)")
             if n_big:
                 x = AttnMmaExtra(cu_seqlens=batch.cu_seqlens.data_ptr(), o_part=None, ml_part=None,
                                  n_segments=len(batch.segments), tokens_per_block=tpb_rows, n_splits=1,
-                                 seg_min_tokens=big_from, seg_max_tokens=0x7fffffff)
+                                 seg_min_tokens=big_from, seg_max_tokens=tc_from - 1)
                 st = self._lib("attention_rows").spite_paged_attention_rows(
                     C.byref(p), C.byref(b), C.byref(c), C.byref(x), n_big, self._stream())
                 self.launches += 1

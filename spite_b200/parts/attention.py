@@ -23,7 +23,7 @@ from .base import Mixer, ParamSpec, build_part, register_mixer
 @register_mixer("paged_attention")
 class PagedAttention(Mixer):
     graph_safe = True
-    kernel_libraries = ("gemm_simt", "attention", "attention_mma", "attention_rows")
+    kernel_libraries = ("gemm_simt", "attention", "attention_mma", "attention_rows", "attention_tc")
 
     def __init__(self, ctx, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  position: PartSpec, window=("full", 0), qk_norm_eps=None, temperature_tuning=None,

@@ -228,6 +228,66 @@ def test_paged_attention(ks, nq, nkv, hd, window, P):
     assert float(w_far[far - win.lowest_visible(300)]) > 0.5
 
 
+def dense_attention_reference(q, k_all, v_all, specs, nq, nkv, win, scale):
+    """softmax(q k^T) v per request with a dense mask, float64; q [M, nq, hd] and the keys already rounded."""
+    out = torch.empty(q.shape, dtype=torch.float64)
+    group, off = nq // nkv, 0
+    for s, (start, n) in enumerate(specs):
+        pos = torch.arange(start, start + n)
+        lo = torch.tensor([win.lowest_visible(int(p)) for p in pos])
+        j = torch.arange(start + n)
+        mask = (j[None, :] <= pos[:, None]) & (j[None, :] >= lo[:, None])
+        for h in range(nq):
+            sc = (q[off:off + n, h].double() @ k_all[s][:, h // group].double().T) * scale
+            w = torch.softmax(sc.masked_fill(~mask, float("-inf")), dim=-1)
+            out[off:off + n, h] = w @ v_all[s][:, h // group].double()
+        off += n
+    return out
+
+
+@pytest.mark.parametrize("nq,nkv,hd,window,P", [
+    (10, 2, 128, ("full", 0), 64), (8, 8, 128, ("chunk", 128), 64), (6, 1, 64, ("chunk", 96), 64),
+    (16, 1, 128, ("sliding", 100), 128), (40, 8, 128, ("chunk", 256), 64), (3, 3, 64, ("full", 0), 128)])
+def test_paged_attention_tcgen05(nq, nkv, hd, window, P):
+    """Prompt portions that go to the tcgen05 kernel: several 128-row tiles per request, portions that
+    start deep in a context, windows that end inside a 64-key tile, pages behind the window given back."""
+    from spite_b200.kernels.cuda import CudaKernels
+    ks = CudaKernels(torch.bfloat16, DEV)
+    win = Window(*window)
+    specs = [(0, 300), (200, 130), (1000, 64), (0, 1), (517, 40)]
+    n_pages = sum(-(-(s + n) // P) for s, n in specs) + 5
+    batch, tables = make_batch(specs, P, n_pages, 40, DEV)
+    M = batch.n_tokens
+    g = torch.Generator().manual_seed(41)
+    k_all = [torch.randn((s + n, nkv, hd), generator=g).to(torch.bfloat16) for s, n in specs]
+    v_all = [torch.randn((s + n, nkv, hd), generator=g).to(torch.bfloat16) for s, n in specs]
+    q = torch.randn((M, nq, hd), generator=g)
+    # a far key carries the attention of one row deep in the first portion
+    far = 3 if win.kind == "full" else win.lowest_visible(290) + 1
+    q[290] = k_all[0][far, 0, :].float() * (16.0 / math.sqrt(hd))
+    q = q.to(torch.bfloat16)
+    kv = torch.zeros((2, n_pages, nkv, P, hd), dtype=torch.bfloat16)
+    fill_cache(kv, tables, [(s + n, 0) for s, n in specs], k_all, v_all, P)
+    if win.kind != "full":
+        # pages that lie wholly behind the window of a portion's first token are given back: the kernel may
+        # not read them, so poison what they held and drop them from the table
+        bt = batch.block_tables[0]
+        for s, (start, n) in enumerate(specs):
+            for pg in range(win.lowest_visible(start) // P):
+                kv[:, tables[s][pg]] = float("nan")
+                bt[s, pg] = -1
+    out = torch.empty((M, nq * hd), dtype=torch.bfloat16, device=DEV)
+    scale = 1.0 / math.sqrt(hd)
+    ks.paged_attention(q.reshape(M, nq * hd).to(DEV), out, batch, LayerCache(0, kv.to(DEV), None, P, False),
+                       num_heads=nq, window=win, softmax_scale=scale)
+    assert ks.attention_tc_error() == 0
+    ref = dense_attention_reference(q, k_all, v_all, specs, nq, nkv, win, scale)
+    close(out.view(M, nq, hd), ref, TOL[torch.bfloat16], f"tcgen05 attention {window}")
+    lo = win.lowest_visible(290)
+    w_far = torch.softmax((k_all[0][lo:291, 0].double() @ q[290, 0].double()) * scale, 0)
+    assert float(w_far[far - lo]) > 0.5
+
+
 # ---------------------------------------------------------------------------- router
 @pytest.mark.parametrize("M,d,E,k", [(1, 48, 3, 1), (37, 96, 8, 1), (200, 200, 16, 2), (5, 64, 128, 4)])
 def test_moe_route(ks, M, d, E, k):
