@@ -18,6 +18,7 @@ __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)_
 __device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
 }
+__device__ __forceinline__ void mbar_inval(unsigned bar) { asm volatile("mbarrier.inval.shared::cta.b64 [%0];\n" ::"r"(bar) : "memory"); }
 __device__ __forceinline__ void mbar_init_fence() { asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory"); }
 __device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
@@ -31,13 +32,17 @@ __device__ __forceinline__ bool mbar_try(unsigned bar, unsigned parity) {
                  : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
-// Waits for the phase of `parity`; gives up when the abort flag is up or time has run out.
+// Waits for the phase of `parity`; gives up when the abort flag is up or time has run out.  The
+// flag and the clock are looked at once in 32 polls, so that a waiting warp takes few issue slots
+// from the warps that compute (mbarrier.try_wait itself suspends the thread for a while).
 __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatile int* abort_flag, int* error_word,
                                           int code) {
     if (mbar_try(bar, parity)) return true;
     const long long t0 = clock64();
     while (true) {
-        if (mbar_try(bar, parity)) return true;
+#pragma unroll 1
+        for (int i = 0; i < 32; ++i)
+            if (mbar_try(bar, parity)) return true;
         if (*abort_flag) return false;
         if (clock64() - t0 > WAIT_CYCLES) {
             *abort_flag = 1;

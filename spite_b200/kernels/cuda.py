@@ -288,7 +288,7 @@ class CudaKernels(KernelSet):
             # warps and blocks split the keys.
             big_from = -(-32 // group) if c.page_size % 32 == 0 else 1 << 30
             tpb, tpb_rows, tpb_tc = max(1, 16 // group), max(1, 64 // group), max(1, 128 // group)
-            # tcgen05 kernel (128 rows a block): head sizes 64 and 128, pages of a multiple of 64 keys
+            # tcgen05 kernel (two tiles of 128 rows a block): head sizes 64 and 128, pages of a multiple of 64 keys
             tc_from = 1 << 30
             if c.head_dim in (64, 128) and c.page_size % 64 == 0 and self.use_tcgen05_attention:
                 tc_from = max(big_from, self.attention_tc_min_tokens or tpb_tc)
@@ -296,7 +296,7 @@ class CudaKernels(KernelSet):
             longest = 1
             for s in batch.segments:
                 if s.n_tokens >= tc_from:
-                    n_tc += -(-s.n_tokens // tpb_tc)
+                    n_tc += -(-s.n_tokens // (2 * tpb_tc))        # a block serves two tiles of 128 rows
                     continue
                 if s.n_tokens >= big_from:
                     n_big += -(-s.n_tokens // tpb_rows)
@@ -309,7 +309,7 @@ class CudaKernels(KernelSet):
                                  n_segments=len(batch.segments), tokens_per_block=tpb_tc, n_splits=1,
                                  seg_min_tokens=tc_from, seg_max_tokens=0x7fffffff)
                 st = self._lib("attention_tc").spite_paged_attention_tc(
-                    C.byref(p), C.byref(b), C.byref(c), C.byref(x), n_tc, self._stream())
+                    C.byref(p), C.byref(b), C.byref(c), C.byref(x), n_tc, self.sm_count, self._stream())
                 self.launches += 1
                 _check(st, "paged_attention (tcgen05, prompt portions)")
             if n_big:
