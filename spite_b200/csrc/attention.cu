@@ -3,7 +3,7 @@
 //
 //  * qk_prepare: position encoding of q and k, weightless per-head norm, the
 //    temperature factor of layers without rotation, and the append of k and v to
-//    their pages, in one pass over the projection's output.
+//    their pages, in one pass over the projection's output (one warp per head).
 //  * paged_attention: one warp per (token, query head) walks the visible keys in
 //    tiles of 32, keeps a running maximum and sum (all in float32) and gathers the
 //    values.  It serves prompt portions and decoded tokens alike, since every key of
@@ -12,73 +12,89 @@
 
 namespace {
 
-// grid (tokens, ceil(heads_total / 4)), block 128: one warp per head of q, k or v.
+// Two neighbouring elements with one load or store.
+__device__ __forceinline__ void load_pair(const float* p, float& a, float& b) { const float2 v = *(const float2*)p; a = v.x; b = v.y; }
+__device__ __forceinline__ void load_pair(const __nv_bfloat16* p, float& a, float& b) {
+    const __nv_bfloat162 v = *(const __nv_bfloat162*)p;
+    a = __low2float(v); b = __high2float(v);
+}
+__device__ __forceinline__ void store_pair(float* p, float a, float b) { *(float2*)p = make_float2(a, b); }
+__device__ __forceinline__ void store_pair(__nv_bfloat16* p, float a, float b) { *(__nv_bfloat162*)p = __floats2bfloat162_rn(a, b); }
+
+// grid (tokens, ceil(heads_total / heads_per_block)), block 32 * warps: a warp takes the heads
+// blockIdx.y * heads_per_block + warp, + warps, ... of q, k and v, one at a time.
 template <typename T>
-__global__ void __launch_bounds__(128) qk_prepare_kernel(const QkPrepareParams p, const StepTokens b,
-                                                         const PagedCache c) {
+__global__ void __launch_bounds__(256) qk_prepare_kernel(const QkPrepareParams p, const StepTokens b,
+                                                         const PagedCache c, const int heads_per_block) {
     pdl_wait();
     pdl_launch_dependents();
     const int t = blockIdx.x;
-    const int lane = threadIdx.x & 31;
-    const int head = blockIdx.y * 4 + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
     const int nq = p.num_heads, nkv = c.num_kv_heads, hd = c.head_dim;
-    if (head >= nq + 2 * nkv) return;
+    const int heads_total = nq + 2 * nkv;
+    const int head_end = min(heads_total, (int)(blockIdx.y + 1) * heads_per_block);
     const int pos = b.positions[t];
-    const T* in = (const T*)p.qkv + (size_t)t * (nq + 2 * nkv) * hd + (size_t)head * hd;
-    const bool is_q = head < nq, is_v = head >= nq + nkv;
+    int page = -1;
+    if (p.write_cache) {
+        page = b.block_table[(size_t)b.seg_of_token[t] * b.table_width + pos / c.page_size];
+        if (page >= c.n_pages) page = -1;                     // the host never lets this happen
+    }
+    // the temperature factor of this position (llama4.rs:177-183)
+    float temp = 1.f;
+    if (p.temperature_floor > 0) temp = logf((float)((pos + 1) / p.temperature_floor) + 1.0f) * p.temperature_scale + 1.0f;
 
-    T* dst;
-    if (is_q) {
-        dst = (T*)p.q_out + ((size_t)t * nq + head) * hd;
-    } else {
-        if (!p.write_cache) return;
-        const int seg = b.seg_of_token[t];
-        const int page = b.block_table[(size_t)seg * b.table_width + pos / c.page_size];
-        if (page < 0 || page >= c.n_pages) return;       // the host never lets this happen
-        const int kvh = is_v ? head - nq - nkv : head - nq;
-        dst = (T*)c.kv + (is_v ? c.v_offset : 0) +
-              (((size_t)page * nkv + kvh) * c.page_size + pos % c.page_size) * hd;
-    }
-    if (is_v) {
-        for (int i = lane; i < hd; i += 32) dst[i] = in[i];
-        return;
-    }
-    // q or k: rotate neighbouring pairs (2i, 2i+1) by pos * inv_freq[i]
-    // (rotation: crates/spite-rope/src/lib.rs:83-91; norm after it: llama4.rs:161-176)
-    constexpr int MAXP = 4;                                  // pairs per lane: head_dim <= 256
-    float x0[MAXP], x1[MAXP];
-    float ss = 0.f;
-#pragma unroll
-    for (int r = 0; r < MAXP; ++r) {
-        const int i = lane + 32 * r;
-        x0[r] = x1[r] = 0.f;
-        if (2 * i < hd) {
-            float a = to_f32(in[2 * i]), bb = to_f32(in[2 * i + 1]);
-            if (p.inv_freq) {
-                float sn, cs;
-                sincosf((float)pos * p.inv_freq[i], &sn, &cs);
-                const float ra = a * cs - bb * sn, rb = a * sn + bb * cs;
-                a = ra; bb = rb;
-            }
-            x0[r] = a; x1[r] = bb;
-            ss += a * a + bb * bb;
+    for (int head = blockIdx.y * heads_per_block + warp; head < head_end; head += n_warps) {
+        const T* in = (const T*)p.qkv + (size_t)t * heads_total * hd + (size_t)head * hd;
+        const bool is_q = head < nq, is_v = head >= nq + nkv;
+        T* dst;
+        if (is_q) {
+            dst = (T*)p.q_out + ((size_t)t * nq + head) * hd;
+        } else {
+            if (page < 0) continue;                          // nothing to append (or no page: the host never lets this happen)
+            const int kvh = is_v ? head - nq - nkv : head - nq;
+            dst = (T*)c.kv + (is_v ? c.v_offset : 0) +
+                  (((size_t)page * nkv + kvh) * c.page_size + pos % c.page_size) * hd;
         }
-    }
-    float mul = 1.f;
-    if (p.qk_norm_eps > 0.f) {
-        ss = warp_sum(ss);
-        mul = 1.0f / sqrtf(ss / (float)hd + p.qk_norm_eps);
-    }
-    if (is_q && p.temperature_floor > 0) {                   // llama4.rs:177-183
-        const float fl = (float)((pos + 1) / p.temperature_floor);
-        mul *= logf(fl + 1.0f) * p.temperature_scale + 1.0f;
-    }
+        if (is_v) {
+            for (int i = lane; 2 * i < hd; i += 32) {
+                float a, bb;
+                load_pair(in + 2 * i, a, bb);
+                store_pair(dst + 2 * i, a, bb);
+            }
+            continue;
+        }
+        // q or k: rotate neighbouring pairs (2i, 2i+1) by pos * inv_freq[i]
+        // (rotation: crates/spite-rope/src/lib.rs:83-91; norm after it: llama4.rs:161-176)
+        constexpr int MAXP = 4;                              // pairs per lane: head_dim <= 256
+        float x0[MAXP], x1[MAXP];
+        float ss = 0.f;
 #pragma unroll
-    for (int r = 0; r < MAXP; ++r) {
-        const int i = lane + 32 * r;
-        if (2 * i < hd) {
-            dst[2 * i] = from_f32<T>(x0[r] * mul);
-            dst[2 * i + 1] = from_f32<T>(x1[r] * mul);
+        for (int r = 0; r < MAXP; ++r) {
+            const int i = lane + 32 * r;
+            x0[r] = x1[r] = 0.f;
+            if (2 * i < hd) {
+                float a, bb;
+                load_pair(in + 2 * i, a, bb);
+                if (p.inv_freq) {
+                    float sn, cs;
+                    sincosf((float)pos * p.inv_freq[i], &sn, &cs);
+                    const float ra = a * cs - bb * sn, rb = a * sn + bb * cs;
+                    a = ra; bb = rb;
+                }
+                x0[r] = a; x1[r] = bb;
+                ss += a * a + bb * bb;
+            }
+        }
+        float mul = 1.f;
+        if (p.qk_norm_eps > 0.f) {
+            ss = warp_sum(ss);
+            mul = 1.0f / sqrtf(ss / (float)hd + p.qk_norm_eps);
+        }
+        if (is_q) mul *= temp;
+#pragma unroll
+        for (int r = 0; r < MAXP; ++r) {
+            const int i = lane + 32 * r;
+            if (2 * i < hd) store_pair(dst + 2 * i, x0[r] * mul, x1[r] * mul);
         }
     }
 }
@@ -174,11 +190,16 @@ SPITE_API int spite_qk_prepare(int dtype, const QkPrepareParams* p, const StepTo
     if (chk != SPITE_OK) return chk;
     if (b->n_tokens == 0) return SPITE_OK;
     const int heads = p->num_heads + 2 * c->num_kv_heads;
-    dim3 grid(b->n_tokens, (heads + 3) / 4);
+    // few tokens: four heads a block, so that the step still fills the device; many: a block per token
+    const bool many = b->n_tokens >= 1024;
+    const int heads_per_block = many ? heads : 4;
+    const int threads = many ? 256 : 128;
+    dim3 grid(b->n_tokens, (heads + heads_per_block - 1) / heads_per_block);
     if (grid.y > 65535) return SPITE_UNSUPPORTED;
+    if (((uintptr_t)p->qkv | (uintptr_t)p->q_out | (uintptr_t)c->kv) & 7) return SPITE_UNSUPPORTED;   // pairs move as one word
     cudaStream_t st = (cudaStream_t)stream;
-    if (dtype == SPITE_DT_F32) SPITE_LAUNCH(qk_prepare_kernel<float>, grid, 128, 0, st, *p, *b, *c);
-    else if (dtype == SPITE_DT_BF16) SPITE_LAUNCH(qk_prepare_kernel<__nv_bfloat16>, grid, 128, 0, st, *p, *b, *c);
+    if (dtype == SPITE_DT_F32) SPITE_LAUNCH(qk_prepare_kernel<float>, grid, threads, 0, st, *p, *b, *c, heads_per_block);
+    else if (dtype == SPITE_DT_BF16) SPITE_LAUNCH(qk_prepare_kernel<__nv_bfloat16>, grid, threads, 0, st, *p, *b, *c, heads_per_block);
     else return SPITE_BAD_ARG;
     return spite_launch_status();
 }

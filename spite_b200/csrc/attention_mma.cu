@@ -267,32 +267,43 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_kernel(const AttentionPar
     }
 }
 
-// grid tokens * heads, block 128: merge the splits of one (token, head)
-__global__ void __launch_bounds__(128) attn_merge_kernel(const float* __restrict__ o_part,
-                                                         const float* __restrict__ ml_part,
-                                                         __nv_bfloat16* __restrict__ out, int n_splits, int hd,
-                                                         int num_heads, const int* __restrict__ seg_of_token,
-                                                         const int* __restrict__ cu_seqlens, int seg_min, int seg_max) {
+// grid tokens * heads, block 128: merge the splits of one (token, head).  Thread s takes split s's
+// maximum and sum (at most MERGE_THREADS splits); the weights 2^.. of the splits go through shared
+// memory, then every thread sums its output elements over the splits in ascending order.
+constexpr int MERGE_THREADS = 128;
+__global__ void __launch_bounds__(MERGE_THREADS) attn_merge_kernel(const float* __restrict__ o_part,
+                                                                   const float* __restrict__ ml_part,
+                                                                   __nv_bfloat16* __restrict__ out, int n_splits, int hd,
+                                                                   int num_heads, const int* __restrict__ seg_of_token,
+                                                                   const int* __restrict__ cu_seqlens, int seg_min, int seg_max) {
+    __shared__ float w_s[MERGE_THREADS];
+    __shared__ float scratch[33];
     pdl_wait();
     pdl_launch_dependents();
     const size_t row = blockIdx.x;
     const int seg = seg_of_token[row / num_heads];
     const int seg_n = cu_seqlens[seg + 1] - cu_seqlens[seg];
     if (seg_n < seg_min || seg_n > seg_max) return;
-    float m = -INFINITY;
-    for (int s = 0; s < n_splits; ++s) m = fmaxf(m, ml_part[(row * n_splits + s) * 2]);
-    float l = 0.f;
-    for (int s = 0; s < n_splits; ++s) {
-        const float ms = ml_part[(row * n_splits + s) * 2];
-        if (ms > -INFINITY) l += ml_part[(row * n_splits + s) * 2 + 1] * expf(ms - m);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    float ms = -INFINITY, ls = 0.f;
+    if (tid < n_splits) {
+        const float2 ml = *(const float2*)(ml_part + (row * n_splits + tid) * 2);
+        ms = ml.x; ls = ml.y;
     }
-    for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+    float m = warp_max(ms);
+    if (lane == 0) scratch[warp] = m;
+    __syncthreads();
+    m = fmaxf(fmaxf(scratch[0], scratch[1]), fmaxf(scratch[2], scratch[3]));
+    const float w = ms > -INFINITY ? expf(ms - m) : 0.f;
+    w_s[tid] = w;
+    const float l = block_sum(ls * w, scratch);             // syncs: w_s is visible afterwards
+    const float inv = 1.0f / fmaxf(l, 1e-30f);
+    const float* o = o_part + row * n_splits * hd;
+    for (int d = tid; d < hd; d += MERGE_THREADS) {
         float acc = 0.f;
-        for (int s = 0; s < n_splits; ++s) {
-            const float ms = ml_part[(row * n_splits + s) * 2];
-            if (ms > -INFINITY) acc += o_part[(row * n_splits + s) * hd + d] * expf(ms - m);
-        }
-        out[row * hd + d] = __float2bfloat16_rn(acc / fmaxf(l, 1e-30f));
+#pragma unroll 4
+        for (int s = 0; s < n_splits; ++s) acc = fmaf(o[(size_t)s * hd + d], w_s[s], acc);
+        out[row * hd + d] = __float2bfloat16_rn(acc * inv);
     }
 }
 
@@ -327,7 +338,7 @@ SPITE_API int spite_paged_attention_mma(const AttentionParams* p, const StepToke
     if (c->head_dim % 16 || c->head_dim > 128 || G > 16 || c->page_size % 16) return SPITE_UNSUPPORTED;
     if (x->tokens_per_block * G > 16) return SPITE_BAD_ARG;
     if (x->n_splits > 1 && (!x->o_part || !x->ml_part)) return SPITE_BAD_ARG;
-    if (x->n_splits > 65535 || c->num_kv_heads > 65535) return SPITE_UNSUPPORTED;
+    if (x->n_splits > MERGE_THREADS || c->num_kv_heads > 65535) return SPITE_UNSUPPORTED;
     if (b->n_tokens == 0 || n_blocks == 0) return SPITE_OK;
     cudaStream_t st = (cudaStream_t)stream;
     int rc;
@@ -342,7 +353,7 @@ SPITE_API int spite_paged_attention_mma(const AttentionParams* p, const StepToke
         default: rc = launch<8>(*p, *b, *c, *x, n_blocks, st); break;
     }
     if (rc != SPITE_OK || x->n_splits == 1) return rc;
-    SPITE_LAUNCH(attn_merge_kernel, b->n_tokens * p->num_heads, 128, 0, st, (const float*)x->o_part,
+    SPITE_LAUNCH(attn_merge_kernel, b->n_tokens * p->num_heads, MERGE_THREADS, 0, st, (const float*)x->o_part,
                  (const float*)x->ml_part, (__nv_bfloat16*)p->out, x->n_splits, c->head_dim, p->num_heads,
                  b->seg_of_token, x->cu_seqlens, x->seg_min_tokens, x->seg_max_tokens);
     return spite_launch_status();

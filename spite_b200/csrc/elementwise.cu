@@ -22,6 +22,47 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
 
 // y[i, :] = x[r, :] * rsqrt(mean(x[r]^2) + eps) * gain      r = rows ? rows[i] : i
 // (crates/spite-models/src/dense.rs:175-181; the sum runs in float32)
+// One block per row.  The row stays in registers between the sum and the scaling: every thread
+// holds up to VPT groups of four elements, loaded with one 16-byte read each.
+__device__ __forceinline__ void store4(float* p, float a, float b, float c, float d) { *(float4*)p = make_float4(a, b, c, d); }
+__device__ __forceinline__ void store4(__nv_bfloat16* p, float a, float b, float c, float d) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+    *(uint2*)p = make_uint2(*(unsigned*)&lo, *(unsigned*)&hi);
+}
+
+template <typename T, int VPT>
+__global__ void rms_norm_vec_kernel(const float* __restrict__ x, const float* __restrict__ gain,
+                                    const int* __restrict__ rows, T* __restrict__ y, int d, float eps) {
+    pdl_wait();
+    pdl_launch_dependents();
+    __shared__ float scratch[33];
+    const int i = blockIdx.x;
+    const int r = rows ? rows[i] : i;
+    const float4* in = (const float4*)(x + (size_t)r * d);
+    const int d4 = d >> 2;
+    float4 v[VPT];
+    float s = 0.f;
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+        const int c = threadIdx.x + k * blockDim.x;
+        v[k] = c < d4 ? in[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) s += (v[k].x * v[k].x + v[k].y * v[k].y) + (v[k].z * v[k].z + v[k].w * v[k].w);
+    s = block_sum(s, scratch);
+    const float scale = 1.0f / sqrtf(s / (float)d + eps);
+    T* out = y + (size_t)i * d;
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+        const int c = threadIdx.x + k * blockDim.x;
+        if (c < d4) {
+            const float4 g = ((const float4*)gain)[c];
+            store4(out + 4 * c, v[k].x * scale * g.x, v[k].y * scale * g.y, v[k].z * scale * g.z, v[k].w * scale * g.w);
+        }
+    }
+}
+
+// The same for widths that are no multiple of four, or too wide for the registers: two passes over the row.
 template <typename T>
 __global__ void rms_norm_kernel(const float* __restrict__ x, const float* __restrict__ gain,
                                 const int* __restrict__ rows, T* __restrict__ y, int d, float eps) {
@@ -80,12 +121,29 @@ SPITE_API int spite_rms_norm(int out_dtype, const float* x, const float* gain, c
     if (!x || !gain || !y || n_rows < 0 || d <= 0 || !(eps > 0.f)) return SPITE_BAD_ARG;
     if (n_rows == 0) return SPITE_OK;
     cudaStream_t st = (cudaStream_t)stream;
+    if (out_dtype != SPITE_DT_F32 && out_dtype != SPITE_DT_BF16) return SPITE_BAD_ARG;
+    const bool f32 = out_dtype == SPITE_DT_F32;
+    const bool aligned = d % 4 == 0 && ((((uintptr_t)x | (uintptr_t)gain | (uintptr_t)y) & 15) == 0);
+    if (aligned && d <= 256 * 4 * 8) {
+        // threads and groups per thread so that every thread has work: 128 x 1 up to 256 x 8
+        const int d4 = d / 4;
+        const int threads = d4 <= 128 ? 128 : 256;
+        const int vpt = (d4 + threads - 1) / threads;
+#define SPITE_RMS(V)                                                                                              \
+        if (f32) SPITE_LAUNCH((rms_norm_vec_kernel<float, V>), n_rows, threads, 0, st, x, gain, rows, (float*)y, d, eps); \
+        else SPITE_LAUNCH((rms_norm_vec_kernel<__nv_bfloat16, V>), n_rows, threads, 0, st, x, gain, rows, (__nv_bfloat16*)y, d, eps)
+        if (vpt <= 1) { SPITE_RMS(1); }
+        else if (vpt <= 2) { SPITE_RMS(2); }
+        else if (vpt <= 4) { SPITE_RMS(4); }
+        else if (vpt <= 5) { SPITE_RMS(5); }
+        else { SPITE_RMS(8); }
+#undef SPITE_RMS
+        return spite_launch_status();
+    }
     const int threads = d >= 2048 ? 512 : (d >= 512 ? 256 : 128);
-    if (out_dtype == SPITE_DT_F32)
+    if (f32)
         SPITE_LAUNCH(rms_norm_kernel<float>, n_rows, threads, 0, st, x, gain, rows, (float*)y, d, eps);
-    else if (out_dtype == SPITE_DT_BF16)
-        SPITE_LAUNCH(rms_norm_kernel<__nv_bfloat16>, n_rows, threads, 0, st, x, gain, rows, (__nv_bfloat16*)y, d, eps);
     else
-        return SPITE_BAD_ARG;
+        SPITE_LAUNCH(rms_norm_kernel<__nv_bfloat16>, n_rows, threads, 0, st, x, gain, rows, (__nv_bfloat16*)y, d, eps);
     return spite_launch_status();
 }

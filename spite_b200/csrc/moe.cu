@@ -10,10 +10,9 @@
 //   sorted_rows[slot][:], in ascending token order.  No host round trip: the grouped
 //   products read these arrays on the device.
 //
-// Two kernels.  The first computes the logits with many blocks (8 tokens x 2 experts a
-// block, its 8 warps splitting the width), so that a decode step of a few tokens still
-// spreads over several multiprocessors and a prompt portion reads the router's weights
-// once per 8 tokens.  The second, one block per choice slot, selects and sorts.
+// Two kernels.  The first computes the logits (8 tokens x 2 experts at a time, the block's 8
+// warps splitting the width): for a decode step one pair of experts a block, so that a few tokens
+// still spread over several multiprocessors; for a prompt portion up to 32 experts a block.  The second, one block per choice slot, selects and sorts.
 // A logit is summed in an order fixed by the width alone.
 #include "common.cuh"
 
@@ -34,74 +33,80 @@ __device__ __forceinline__ void load4(const __nv_bfloat16* p, float (&v)[4]) {
     v[0] = __low2float(a); v[1] = __high2float(a); v[2] = __low2float(b); v[3] = __high2float(b);
 }
 
-// grid (ceil(tokens / TB), ceil(experts / EB)), block 256
+// grid (ceil(tokens / TB), ceil(experts / experts_per_block)), block 256.  A block computes the logits
+// of TB tokens for experts_per_block experts, EB at a time; from the second pair on its tokens come
+// out of the first-level cache.
 template <typename T>
 __global__ void __launch_bounds__(WARPS * 32) route_logits_kernel(const T* __restrict__ x, const float* __restrict__ wr,
-                                                                 int n_tokens, int d, int n_experts,
+                                                                 int n_tokens, int d, int n_experts, int experts_per_block,
                                                                  float* __restrict__ logits) {
     __shared__ float part[WARPS][EB * TB];
     pdl_wait();
     pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int t0 = blockIdx.x * TB, e0 = blockIdx.y * EB;
-    float acc[EB][TB];
-#pragma unroll
-    for (int e = 0; e < EB; ++e)
-#pragma unroll
-        for (int t = 0; t < TB; ++t) acc[e][t] = 0.f;
-
+    const int t0 = blockIdx.x * TB;
+    const int e_end = min(n_experts, (int)(blockIdx.y + 1) * experts_per_block);
     const bool vec = (d % 4 == 0) && (((uintptr_t)wr & 15) == 0) && (((uintptr_t)x & 15) == 0);
-    if (vec) {
-        const int n4 = d >> 2;                                // groups of four elements
-        const int lo = (int)((long long)n4 * warp / WARPS), hi = (int)((long long)n4 * (warp + 1) / WARPS);
-        for (int k4 = lo + lane; k4 < hi; k4 += 32) {
-            float w[EB][4];
+    for (int e0 = blockIdx.y * experts_per_block; e0 < e_end; e0 += EB) {
+        float acc[EB][TB];
 #pragma unroll
-            for (int e = 0; e < EB; ++e) {
-                if (e0 + e < n_experts) load4(wr + (size_t)(e0 + e) * d + 4 * k4, w[e]);
-                else w[e][0] = w[e][1] = w[e][2] = w[e][3] = 0.f;
+        for (int e = 0; e < EB; ++e)
+#pragma unroll
+            for (int t = 0; t < TB; ++t) acc[e][t] = 0.f;
+
+        if (vec) {
+            const int n4 = d >> 2;                            // groups of four elements
+            const int lo = (int)((long long)n4 * warp / WARPS), hi = (int)((long long)n4 * (warp + 1) / WARPS);
+            for (int k4 = lo + lane; k4 < hi; k4 += 32) {
+                float w[EB][4];
+#pragma unroll
+                for (int e = 0; e < EB; ++e) {
+                    if (e0 + e < e_end) load4(wr + (size_t)(e0 + e) * d + 4 * k4, w[e]);
+                    else w[e][0] = w[e][1] = w[e][2] = w[e][3] = 0.f;
+                }
+#pragma unroll
+                for (int t = 0; t < TB; ++t) {
+                    if (t0 + t < n_tokens) {
+                        float xv[4];
+                        load4(x + (size_t)(t0 + t) * d + 4 * k4, xv);
+#pragma unroll
+                        for (int e = 0; e < EB; ++e)
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) acc[e][t] = fmaf(xv[i], w[e][i], acc[e][t]);
+                    }
+                }
             }
+        } else {
+            const int lo = (int)((long long)d * warp / WARPS), hi = (int)((long long)d * (warp + 1) / WARPS);
+            for (int k = lo + lane; k < hi; k += 32) {
 #pragma unroll
-            for (int t = 0; t < TB; ++t) {
-                if (t0 + t < n_tokens) {
-                    float xv[4];
-                    load4(x + (size_t)(t0 + t) * d + 4 * k4, xv);
+                for (int t = 0; t < TB; ++t) {
+                    if (t0 + t < n_tokens) {
+                        const float xv = to_f32(x[(size_t)(t0 + t) * d + k]);
 #pragma unroll
-                    for (int e = 0; e < EB; ++e)
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) acc[e][t] = fmaf(xv[i], w[e][i], acc[e][t]);
+                        for (int e = 0; e < EB; ++e)
+                            if (e0 + e < e_end) acc[e][t] = fmaf(xv, wr[(size_t)(e0 + e) * d + k], acc[e][t]);
+                    }
                 }
             }
         }
-    } else {
-        const int lo = (int)((long long)d * warp / WARPS), hi = (int)((long long)d * (warp + 1) / WARPS);
-        for (int k = lo + lane; k < hi; k += 32) {
+        __syncthreads();                                      // the sums of the pair before have been read
+#pragma unroll
+        for (int e = 0; e < EB; ++e)
 #pragma unroll
             for (int t = 0; t < TB; ++t) {
-                if (t0 + t < n_tokens) {
-                    const float xv = to_f32(x[(size_t)(t0 + t) * d + k]);
-#pragma unroll
-                    for (int e = 0; e < EB; ++e)
-                        if (e0 + e < n_experts) acc[e][t] = fmaf(xv, wr[(size_t)(e0 + e) * d + k], acc[e][t]);
-                }
+                const float s = warp_sum(acc[e][t]);
+                if (lane == 0) part[warp][e * TB + t] = s;
             }
-        }
-    }
+        __syncthreads();
+        if (threadIdx.x < EB * TB) {
+            const int e = threadIdx.x / TB, t = threadIdx.x % TB;
+            if (e0 + e < e_end && t0 + t < n_tokens) {
+                float s = 0.f;
 #pragma unroll
-    for (int e = 0; e < EB; ++e)
-#pragma unroll
-        for (int t = 0; t < TB; ++t) {
-            const float s = warp_sum(acc[e][t]);
-            if (lane == 0) part[warp][e * TB + t] = s;
-        }
-    __syncthreads();
-    if (threadIdx.x < EB * TB) {
-        const int e = threadIdx.x / TB, t = threadIdx.x % TB;
-        if (e0 + e < n_experts && t0 + t < n_tokens) {
-            float s = 0.f;
-#pragma unroll
-            for (int w = 0; w < WARPS; ++w) s += part[w][threadIdx.x];
-            logits[(size_t)(t0 + t) * n_experts + e0 + e] = s;
+                for (int w = 0; w < WARPS; ++w) s += part[w][threadIdx.x];
+                logits[(size_t)(t0 + t) * n_experts + e0 + e] = s;
+            }
         }
     }
 }
@@ -174,14 +179,18 @@ SPITE_API int spite_moe_route(int dtype, const void* x, const float* w_router, i
     if (n_experts > MAX_EXPERTS) return SPITE_UNSUPPORTED;
     cudaStream_t st = (cudaStream_t)stream;
     if (n_tokens > 0) {
-        dim3 grid((n_tokens + TB - 1) / TB, (n_experts + EB - 1) / EB);
+        // a decode step spreads the experts over blocks; a prompt portion has blocks enough from its tokens,
+        // and a block that goes through all experts reads its tokens from memory once
+        int per_block = EB;
+        if (n_tokens >= 1024) per_block = ((n_experts < 32 ? n_experts : 32) + EB - 1) / EB * EB;
+        dim3 grid((n_tokens + TB - 1) / TB, (n_experts + per_block - 1) / per_block);
         if (grid.y > 65535) return SPITE_UNSUPPORTED;
         if (dtype == SPITE_DT_F32)
             SPITE_LAUNCH(route_logits_kernel<float>, grid, WARPS * 32, 0, st, (const float*)x, w_router, n_tokens, d,
-                         n_experts, logits);
+                         n_experts, per_block, logits);
         else if (dtype == SPITE_DT_BF16)
             SPITE_LAUNCH(route_logits_kernel<__nv_bfloat16>, grid, WARPS * 32, 0, st, (const __nv_bfloat16*)x, w_router,
-                         n_tokens, d, n_experts, logits);
+                         n_tokens, d, n_experts, per_block, logits);
         else
             return SPITE_BAD_ARG;
         if (cudaGetLastError() != cudaSuccess) return SPITE_LAUNCH_FAILED;
