@@ -43,6 +43,16 @@ __global__ void __launch_bounds__(256) qk_prepare_kernel(const QkPrepareParams p
     float temp = 1.f;
     if (p.temperature_floor > 0) temp = logf((float)((pos + 1) / p.temperature_floor) + 1.0f) * p.temperature_scale + 1.0f;
 
+    // the rotation of pair i is the same for every head: cos and sin of pos * inv_freq[i], once per warp
+    constexpr int MAXP = 4;                                  // pairs per lane: head_dim <= 256
+    float cs[MAXP], sn[MAXP];
+#pragma unroll
+    for (int r = 0; r < MAXP; ++r) {
+        const int i = lane + 32 * r;
+        cs[r] = 1.f; sn[r] = 0.f;
+        if (p.inv_freq && 2 * i < hd) sincosf((float)pos * p.inv_freq[i], &sn[r], &cs[r]);
+    }
+
     for (int head = blockIdx.y * heads_per_block + warp; head < head_end; head += n_warps) {
         const T* in = (const T*)p.qkv + (size_t)t * heads_total * hd + (size_t)head * hd;
         const bool is_q = head < nq, is_v = head >= nq + nkv;
@@ -65,7 +75,6 @@ __global__ void __launch_bounds__(256) qk_prepare_kernel(const QkPrepareParams p
         }
         // q or k: rotate neighbouring pairs (2i, 2i+1) by pos * inv_freq[i]
         // (rotation: crates/spite-rope/src/lib.rs:83-91; norm after it: llama4.rs:161-176)
-        constexpr int MAXP = 4;                              // pairs per lane: head_dim <= 256
         float x0[MAXP], x1[MAXP];
         float ss = 0.f;
 #pragma unroll
@@ -76,9 +85,7 @@ __global__ void __launch_bounds__(256) qk_prepare_kernel(const QkPrepareParams p
                 float a, bb;
                 load_pair(in + 2 * i, a, bb);
                 if (p.inv_freq) {
-                    float sn, cs;
-                    sincosf((float)pos * p.inv_freq[i], &sn, &cs);
-                    const float ra = a * cs - bb * sn, rb = a * sn + bb * cs;
+                    const float ra = a * cs[r] - bb * sn[r], rb = a * sn[r] + bb * cs[r];
                     a = ra; bb = rb;
                 }
                 x0[r] = a; x1[r] = bb;

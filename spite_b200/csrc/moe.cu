@@ -11,8 +11,8 @@
 //   products read these arrays on the device.
 //
 // Two kernels.  The first computes the logits (8 tokens x 2 experts at a time, the block's 8
-// warps splitting the width): for a decode step one pair of experts a block, so that a few tokens
-// still spread over several multiprocessors; for a prompt portion up to 32 experts a block.  The second, one block per choice slot, selects and sorts.
+// warps splitting the width), one pair of experts a block, so that a few tokens still spread over
+// several multiprocessors.  The second, one block per choice slot, selects and sorts.
 // A logit is summed in an order fixed by the width alone.
 #include "common.cuh"
 
@@ -179,10 +179,9 @@ SPITE_API int spite_moe_route(int dtype, const void* x, const float* w_router, i
     if (n_experts > MAX_EXPERTS) return SPITE_UNSUPPORTED;
     cudaStream_t st = (cudaStream_t)stream;
     if (n_tokens > 0) {
-        // a decode step spreads the experts over blocks; a prompt portion has blocks enough from its tokens,
-        // and a block that goes through all experts reads its tokens from memory once
-        int per_block = EB;
-        if (n_tokens >= 1024) per_block = ((n_experts < 32 ? n_experts : 32) + EB - 1) / EB * EB;
+        // one pair of experts a block: measured faster than blocks that take several pairs and reuse
+        // their tokens from the first-level cache (31 us against 40 and 53 us for 2048 tokens, 16 experts)
+        const int per_block = EB;
         dim3 grid((n_tokens + TB - 1) / TB, (n_experts + per_block - 1) / per_block);
         if (grid.y > 65535) return SPITE_UNSUPPORTED;
         if (dtype == SPITE_DT_F32)
