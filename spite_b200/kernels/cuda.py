@@ -5,6 +5,7 @@ device or without the compiled libraries every call raises.
 """
 from __future__ import annotations
 
+import collections
 import ctypes as C
 import os
 
@@ -84,6 +85,7 @@ class CudaKernels(KernelSet):
         self._dt = _DT[dtype]
         self._libs = {}
         self.launches = 0          # kernels launched so far (for measurement reports)
+        self.launches_by_library = collections.Counter()   # the same, by kernel library
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.use_tcgen05 = os.environ.get("SPITE_NO_TCGEN05", "") == ""
         self.use_tcgen05_attention = os.environ.get("SPITE_NO_TCGEN05_ATTENTION", "") == ""
@@ -94,6 +96,10 @@ class CudaKernels(KernelSet):
         self.skinny_tall_rows = int(os.environ.get("SPITE_SKINNY_TALL_ROWS", "0"))
 
     # ------------------------------------------------------------------ helpers
+    def _count(self, library, n=1):
+        self.launches += n
+        self.launches_by_library[library] += n
+
     def _lib(self, name):
         lib = self._libs.get(name)
         if lib is None:
@@ -119,7 +125,7 @@ class CudaKernels(KernelSet):
         st = self._lib("elementwise").spite_embed(
             self._dt, C.c_void_p(table.data_ptr()), C.c_void_p(token_ids.data_ptr()),
             C.c_void_p(out_h.data_ptr()), token_ids.numel(), d, V, self._stream())
-        self.launches += 1
+        self._count("elementwise", 1)
         _check(st, "embed")
 
     def rms_norm(self, h, gain, eps, out, rows=None):
@@ -130,7 +136,7 @@ class CudaKernels(KernelSet):
         st = self._lib("elementwise").spite_rms_norm(
             _DT[out.dtype], C.c_void_p(h.data_ptr()), C.c_void_p(gain.data_ptr()),
             C.c_void_p(_ptr(rows)), C.c_void_p(out.data_ptr()), n, d, C.c_float(eps), self._stream())
-        self.launches += 1
+        self._count("elementwise", 1)
         _check(st, "rms_norm")
 
     # ------------------------------------------------------------------ matrix products
@@ -150,7 +156,7 @@ class CudaKernels(KernelSet):
                 st = self._lib("gemm_skinny").spite_gemm_skinny(C.byref(p), int(max_rows_per_group), 2 * self.sm_count,
                                                                 self._stream())
                 if st != -2:                       # -2: shape outside the kernel's domain, fall through
-                    self.launches += 1
+                    self._count("gemm_skinny", 1)
                     _check(st, what)
                     return
             if tc_ok:
@@ -161,13 +167,13 @@ class CudaKernels(KernelSet):
                         C.c_void_p(gather_src.data_ptr()), C.c_void_p(p.a_rows), C.c_void_p(keep.data_ptr()),
                         gather_src.shape[0], C.c_longlong(gather_src.shape[1] * gather_src.element_size()),
                         self._stream())
-                    self.launches += 1
+                    self._count("elementwise", 1)
                     _check(st, "gather_rows")
                     p = GemmParams.from_buffer_copy(p)
                     p.A = keep.data_ptr()          # rows are in place now; a_rows only indexes the row scale
                 st = self._lib("gemm_tc").spite_gemm_tc(C.byref(p), self.sm_count, self._stream())
                 if st != -2:
-                    self.launches += 1
+                    self._count("gemm_tc", 1)
                     _check(st, what + " (tcgen05)")
                     return
                 p = orig
@@ -175,11 +181,11 @@ class CudaKernels(KernelSet):
                     st = self._lib("gemm_skinny").spite_gemm_skinny(C.byref(p), int(max_rows_per_group),
                                                                     2 * self.sm_count, self._stream())
                     if st != -2:
-                        self.launches += 1
+                        self._count("gemm_skinny", 1)
                         _check(st, what)
                         return
         st = self._lib("gemm_simt").spite_gemm_simt(self._dt, C.byref(p), self._stream())
-        self.launches += 1
+        self._count("gemm_simt", 1)
         _check(st, what)
 
     def attention_tc_error(self) -> int:
@@ -270,7 +276,7 @@ class CudaKernels(KernelSet):
                             temperature_scale=scale, num_heads=num_heads, write_cache=int(cache.write))
         b, c = self._step_tokens(batch, cache.group), self._paged(cache)
         st = self._lib("attention").spite_qk_prepare(self._dt, C.byref(p), C.byref(b), C.byref(c), self._stream())
-        self.launches += 1
+        self._count("attention", 1)
         _check(st, "qk_prepare")
 
     def paged_attention(self, q, out, batch, cache, *, num_heads, window, softmax_scale):
@@ -310,7 +316,7 @@ class CudaKernels(KernelSet):
                                  seg_min_tokens=tc_from, seg_max_tokens=0x7fffffff)
                 st = self._lib("attention_tc").spite_paged_attention_tc(
                     C.byref(p), C.byref(b), C.byref(c), C.byref(x), n_tc, self.sm_count, self._stream())
-                self.launches += 1
+                self._count("attention_tc", 1)
                 _check(st, "paged_attention (tcgen05, prompt portions)")
             if n_big:
                 x = AttnMmaExtra(cu_seqlens=batch.cu_seqlens.data_ptr(), o_part=None, ml_part=None,
@@ -318,7 +324,7 @@ class CudaKernels(KernelSet):
                                  seg_min_tokens=big_from, seg_max_tokens=tc_from - 1)
                 st = self._lib("attention_rows").spite_paged_attention_rows(
                     C.byref(p), C.byref(b), C.byref(c), C.byref(x), n_big, self._stream())
-                self.launches += 1
+                self._count("attention_rows", 1)
                 _check(st, "paged_attention (tensor cores, prompt portions)")
             if not n_small:
                 return
@@ -346,12 +352,12 @@ class CudaKernels(KernelSet):
                              seg_min_tokens=0, seg_max_tokens=big_from - 1)
             st = self._lib("attention_mma").spite_paged_attention_mma(
                 C.byref(p), C.byref(b), C.byref(c), C.byref(x), n_small, self._stream())
-            self.launches += 1 + (splits > 1)
+            self._count("attention_mma", 1 + (splits > 1))
             _check(st, "paged_attention (tensor cores)")
             return
         st = self._lib("attention").spite_paged_attention(self._dt, C.byref(p), C.byref(b), C.byref(c),
                                                           self._stream())
-        self.launches += 1
+        self._count("attention", 1)
         _check(st, "paged_attention")
 
     # ------------------------------------------------------------------ mixture of experts
@@ -369,8 +375,7 @@ class CudaKernels(KernelSet):
             self._dt, C.c_void_p(x.data_ptr()), C.c_void_p(w_router.data_ptr()), M, d, E, top_k,
             C.c_void_p(ids.data_ptr()), C.c_void_p(wts.data_ptr()), C.c_void_p(_ptr(logits)),
             C.c_void_p(offsets.data_ptr()), C.c_void_p(rows.data_ptr()), self._stream())
-        self.launches += 1
-        self.launches += 1
+        self._count("moe", 2)
         _check(st, "moe_route")
         return Routing(ids, wts, offsets, rows, logits if want_logits else None)
 
@@ -381,7 +386,7 @@ class CudaKernels(KernelSet):
         out = torch.empty(R, dtype=torch.int32, device=logits.device)
         st = self._lib("sampling").spite_argmax(C.c_void_p(logits.data_ptr()), R, V,
                                                 C.c_void_p(out.data_ptr()), self._stream())
-        self.launches += 1
+        self._count("sampling", 1)
         _check(st, "argmax")
         return out
 
@@ -398,6 +403,6 @@ class CudaKernels(KernelSet):
                          context_offsets=_ptr(context_offsets), rng_state=rng_state.data_ptr(),
                          out_tokens=out.data_ptr(), vocab=V)
         st = self._lib("sampling").spite_sample(C.byref(p), R, self._stream())
-        self.launches += 1
+        self._count("sampling", 1)
         _check(st, "sample")
         return out

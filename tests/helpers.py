@@ -35,7 +35,18 @@ CONFIG_B = dict(
     floor_scale=8192, attn_scale=0.1, rms_norm_eps=1e-6, max_position_embeddings=2048)
 STD_B = 0.05
 
-CONFIGS = {"A": (CONFIG_A, STD_A, 11), "B": (CONFIG_B, STD_B, 23)}
+# Sizes that reach the tcgen05 kernels: head size 64, widths that are multiples of 8, three query heads
+# per kv head; chunk 96 ends inside a 64-key tile; layer 1 has no rotation and sees every key
+CONFIG_C = dict(
+    architectures=["Llama4ForCausalLM"], num_hidden_layers=2, hidden_size=128, num_attention_heads=6,
+    num_key_value_heads=2, head_dim=64, interleave_moe_layer_step=1, num_local_experts=3,
+    num_experts_per_tok=1, intermediate_size=72, intermediate_size_mlp=144, vocab_size=300,
+    tie_word_embeddings=False, rope_theta=10000.0, rope_scaling=None, attention_chunk_size=96,
+    no_rope_layer_interval=2, use_qk_norm=True, attn_temperature_tuning=True, floor_scale=50,
+    attn_scale=0.2, rms_norm_eps=1e-5, max_position_embeddings=4096)
+STD_C = 0.03
+
+CONFIGS = {"A": (CONFIG_A, STD_A, 11), "B": (CONFIG_B, STD_B, 23), "C": (CONFIG_C, STD_C, 31)}
 
 
 def write_model(folder, name: str, dtype=torch.bfloat16) -> Path:

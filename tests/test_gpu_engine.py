@@ -108,6 +108,31 @@ def test_long_decoding(setup):
     H.compare_with_plain(H.run_steps(_engine(model, steps, 16), steps), path, {"l": toks}, tol)
 
 
+def test_sizes_of_the_tcgen05_kernels(tmp_path):
+    """A third configuration whose head size, widths and prompt lengths reach the tcgen05 attention and
+    product kernels (the two tiny ones stay below them): whole prompts, large portions beside small ones,
+    and mixed batches with pages of 64 used again; a chunk edge inside a 64-key tile, a layer that sees all."""
+    from spite_b200.engine import Model
+    path = H.write_model(tmp_path / "modelC", "C")
+    model = Model.from_folder(path, dtype="bfloat16", device="cuda:0")
+    lengths = {"a": 300, "b": 130, "c": 97, "d": 64, "e": 45}
+    requests = {r: H.decisive_tokens(path, n, 40 + i, 0.02) for i, (r, n) in enumerate(lengths.items())}
+    steps = H.steps_whole(requests)
+    H.compare_with_plain(H.run_steps(_engine(model, steps, 64), steps), path, requests, TOL["bfloat16"])
+    assert model.kernels.attention_tc_error() == 0 and model.kernels.gemm_tc_error() == 0
+    by_library = model.kernels.launches_by_library
+    assert by_library["attention_tc"] > 0 and by_library["gemm_tc"] > 0, dict(by_library)
+    steps = H.steps_portions(requests, 3, sizes=(2, 5, 43, 64, 90, 128))
+    H.compare_with_plain(H.run_steps(_engine(model, steps, 64), steps), path, requests, TOL["bfloat16"])
+    n_prompt = {r: len(t) - 8 for r, t in requests.items()}
+    steps = H.steps_mixed(requests, n_prompt, 5, sizes=(2, 9, 50, 70))
+    eng = _engine(model, steps, 64)
+    assert eng.n_pages * 64 < sum(H._round64(len(t)) for t in requests.values())
+    H.compare_with_plain(H.run_steps(eng, steps), path, requests, TOL["bfloat16"])
+    assert model.kernels.attention_tc_error() == 0 and model.kernels.gemm_tc_error() == 0
+    assert all(by_library[lib] > 0 for lib in ("attention_tc", "attention_rows", "attention_mma", "gemm_skinny"))
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_trace_run_program(folder, dtype, tmp_path):
     """`bin/trace_run` as a user runs it: JSON lines in, `done <step>` lines and .f32 files out."""
