@@ -288,6 +288,40 @@ def test_paged_attention_tcgen05(nq, nkv, hd, window, P):
     assert float(w_far[far - lo]) > 0.5
 
 
+@pytest.mark.parametrize("n_tokens,library", [(1, "attention_mma"), (9, "attention_rows"), (60, "attention_tc")])
+def test_paged_attention_long_context(n_tokens, library):
+    """The last tokens of a 40,000-token context on each bfloat16 attention kernel: thousands of key tiles,
+    key splits and their merge for the single token, hundreds of pages in random order."""
+    from spite_b200.kernels.cuda import CudaKernels
+    ks = CudaKernels(torch.bfloat16, DEV)
+    nq, nkv, hd, P, C = 10, 2, 128, 64, 40000
+    n_pages = C // P + 3
+    batch, tables = make_batch([(C - n_tokens, n_tokens)], P, n_pages, 50, DEV)
+    g = torch.Generator(device=DEV).manual_seed(51)
+    kv = torch.randn((2, n_pages, nkv, P, hd), generator=g, device=DEV).to(torch.bfloat16)
+    q = torch.randn((n_tokens, nq, hd), generator=g, device=DEV)
+    # the first key carries the attention of the last token's first head
+    tbl = torch.tensor(tables[0], device=DEV)
+    q[-1, 0] = kv[0, tbl[0], 0, 0].float() * (24.0 / math.sqrt(hd))
+    q = q.to(torch.bfloat16)
+    out = torch.empty((n_tokens, nq * hd), dtype=torch.bfloat16, device=DEV)
+    scale = 1.0 / math.sqrt(hd)
+    ks.paged_attention(q.reshape(n_tokens, nq * hd), out, batch, LayerCache(0, kv, None, P, False), num_heads=nq,
+                       window=Window("full", 0), softmax_scale=scale)
+    assert ks.launches_by_library[library] > 0, dict(ks.launches_by_library)
+    K = kv[0][tbl].permute(1, 0, 2, 3).reshape(nkv, -1, hd).double()      # [kv heads, positions, head size]
+    V = kv[1][tbl].permute(1, 0, 2, 3).reshape(nkv, -1, hd).double()
+    ref = torch.empty((n_tokens, nq, hd), dtype=torch.float64, device=DEV)
+    for t in range(n_tokens):
+        pos = C - n_tokens + t
+        for h in range(nq):
+            w = torch.softmax((K[h // (nq // nkv), :pos + 1] @ q[t, h].double()) * scale, 0)
+            ref[t, h] = w @ V[h // (nq // nkv), :pos + 1]
+            if t == n_tokens - 1 and h == 0:
+                assert float(w[0]) > 0.5
+    close(out.view(n_tokens, nq, hd), ref, TOL[torch.bfloat16], f"attention over {C} keys ({library})")
+
+
 # ---------------------------------------------------------------------------- router
 @pytest.mark.parametrize("M,d,E,k", [(1, 48, 3, 1), (37, 96, 8, 1), (200, 200, 16, 2), (5, 64, 128, 4)])
 def test_moe_route(ks, M, d, E, k):
