@@ -255,7 +255,9 @@ def run_ours(args):
                    "global_batch": B, "seq_len": ctx, "page_size": page, "parallelism": "single-gpu",
                    "l2": "inputs larger than L2 (weights read per step exceed 126 MB)",
                    "cache": "random-filled to context"},
-        "e2e": {"value": round(e2e, 2), "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * B},
+        "e2e": {"value": round(e2e, 2), "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * B,
+                "ids_read": "one step late (decode steps are launched from the ids on the device)"
+                if sched.counters["steps_ahead"] else "every step"},
         "gpu_launches": launches,
         "clocks": clocks.summary(),
         "prefill": prefill,

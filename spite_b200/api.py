@@ -25,7 +25,7 @@ class LLM:
 
     def __init__(self, model, *, dtype="bfloat16", device="cuda:0", ctx: int | None = None,
                  cache_tokens: int | None = None, page_size: int = 64, max_requests: int = 64,
-                 max_batch_tokens: int = 2048, kernels=None):
+                 max_batch_tokens: int = 2048, kernels=None, decode_ahead: bool | None = None):
         if not isinstance(model, Model):
             model = Model.from_folder(Path(model), dtype=dtype, device=device, kernels=kernels)
         self.model = model
@@ -36,6 +36,7 @@ class LLM:
                              max_requests=max_requests, max_positions=self.ctx)
         self.sampler = Sampler(model.kernels)
         self.max_batch_tokens = max_batch_tokens
+        self.decode_ahead = decode_ahead     # None: on where decode steps run from CUDA graphs
         eos = getattr(model.config, "eos_token_id", None) or ()
         self.eos_token_ids = tuple(eos)
 
@@ -43,6 +44,7 @@ class LLM:
         kw.setdefault("max_batch_tokens", self.max_batch_tokens)
         kw.setdefault("ctx", self.ctx)
         kw.setdefault("eos_token_ids", self.eos_token_ids)
+        kw.setdefault("decode_ahead", self.decode_ahead)
         return Scheduler(self.engine, self.sampler, **kw)
 
     def generate(self, prompts, *, max_tokens: int = 512, temperature: float = 1.0, seed: int = DEFAULT_SEED,

@@ -75,9 +75,18 @@ class Engine:
         return new <= self.cache.slots.n_free and self.cache.can_reserve(wants)
 
     # ------------------------------------------------------------------ the step
-    def step(self, entries) -> torch.Tensor:
+    def step(self, entries, device_tokens: torch.Tensor | None = None) -> torch.Tensor:
+        """Run one step.  `device_tokens` (int32 [len(entries)] on the device), if given, supplies the
+        token of every entry from the device (the ids sampled by the step before, which the host has
+        not read yet); every entry then brings one placeholder token, and the step must be one that
+        is a decode step (one token an entry)."""
         entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
         vocab = self.model.plan.vocab_size
+        if device_tokens is not None:
+            if any(len(e.tokens) != 1 for e in entries):
+                raise StepError("tokens from the device need a decode step: one token an entry")
+            if device_tokens.dtype != torch.int32 or device_tokens.numel() != len(entries):
+                raise StepError("device_tokens must be int32 with one id per entry")
         seen = set()
         for e in entries:
             if e.req_id in seen:
@@ -126,13 +135,15 @@ class Engine:
                   for g in range(self.storage.n_groups)]
         try:
             if self.cuda_graphs and all(len(e.tokens) == 1 for e in entries):
-                logits = self._decode_step_from_graph(segments, [e.tokens[0] for e in entries], tables)
+                logits = self._decode_step_from_graph(segments, [e.tokens[0] for e in entries], tables, device_tokens)
                 rows = [i for i, e in enumerate(entries) if e.want]
                 if len(rows) < len(entries):
                     logits = logits[torch.tensor(rows, dtype=torch.long, device=logits.device)]
             else:
                 batch = build_step_batch(segments, [e.tokens for e in entries], [e.want for e in entries],
                                          tables, self.model.device)
+                if device_tokens is not None:
+                    batch.token_ids.copy_(device_tokens)
                 logits = self.model.forward(batch, self.storage)
         except Exception:
             for r in reserved:
@@ -147,7 +158,7 @@ class Engine:
         return logits
 
     # ------------------------------------------------------------------ decode steps from CUDA graphs
-    def _decode_step_from_graph(self, segments, tokens, tables) -> torch.Tensor:
+    def _decode_step_from_graph(self, segments, tokens, tables, device_tokens=None) -> torch.Tensor:
         """A step of single tokens.  The first step of a shape runs eagerly (it loads and warms
         every kernel), the second is captured, later ones replay the capture.  The returned
         logits live in the graph's memory and are valid until the next step of that shape."""
@@ -163,6 +174,8 @@ class Engine:
             st = _GraphState(StaticDecodeBatch(S, [width] * self.storage.n_groups, self.model.device, bucket))
             self._graphs[key] = st
         batch = st.static.fill(segments, tokens, tables)
+        if device_tokens is not None:
+            batch.token_ids.copy_(device_tokens)              # stream-ordered after the copy from the host
         if st.graph is None:
             if st.eager_runs == 0:
                 st.eager_runs = 1

@@ -16,6 +16,17 @@ generator state is kept, so it samples what it would have sampled).  A request
 that is alone and still cannot get a page ends with reason `cache_full`.  The
 rule is deterministic.
 
+Decoding ahead.  On a GPU, when a step is made of decoded tokens only, all of them greedy, the
+scheduler does not wait for the sampled ids: it leaves the step in flight (argmax on the device, a
+copy to pinned memory under way) and launches the next step with the ids taken from the device,
+so the GPU never waits for the host between decode steps.  The ids are read one step late.  What
+the late reading changes: a request that ends on an end-of-generation or stop token has one more
+step run for it, whose row is thrown away (its cache is freed as usual; rows of a batch do not
+depend on each other), and a waiting request is admitted one step later than it could have been.
+Ends by token count are known ahead and are not run past.  Whenever the next step is not such a
+step (a prompt portion to run, a request to admit, pages to find by preemption), the step in
+flight is read first and the plain path above takes over.  The tokens produced are the same.
+
 Counterpart in giveen/spite: the scheduler skeleton (slot table, `BatchRequest`,
 `BatchOutput`, `FinishReason`; `step` unimplemented,
 crates/spite-scheduler/src/lib.rs:30-152) and the generate loop's stopping rule
@@ -27,7 +38,7 @@ import enum
 from collections import deque
 from dataclasses import dataclass, field
 
-from ..sampling.sampler import SampleRow, SamplingParams
+from ..sampling.sampler import SampleRow, SamplingParams, is_plain_greedy
 from .executor import ContextOverflow, StepEntry
 
 
@@ -78,9 +89,19 @@ class StepPlan:
     ended: list                 # (Request, FinishReason) ended by the plan itself
 
 
+@dataclass
+class _InFlight:
+    """A decode step whose sampled ids are still on the device."""
+    requests: list              # row i of `device_tokens` belongs to requests[i]
+    device_tokens: object       # int32 [R] on the device
+    host_tokens: object         # pinned int32 buffer the copy lands in
+    copied: object              # event recorded after the copy
+    dead: set = field(default_factory=set)   # ids of requests that ended before this step was read
+
+
 class Scheduler:
     def __init__(self, engine, sampler, *, max_batch_tokens: int = 2048, max_portion: int | None = None,
-                 ctx: int | None = None, eos_token_ids=()):
+                 ctx: int | None = None, eos_token_ids=(), decode_ahead: bool | None = None):
         if max_batch_tokens < 1:
             raise ValueError("max_batch_tokens must be positive")
         self.engine = engine
@@ -92,7 +113,12 @@ class Scheduler:
         self.waiting: deque = deque()
         self.running: list = []          # in order of admission
         self.finished: dict = {}
-        self.counters = {"steps": 0, "tokens": 0, "preemptions": 0}
+        self.counters = {"steps": 0, "tokens": 0, "preemptions": 0, "steps_ahead": 0}
+        if decode_ahead is None:
+            decode_ahead = bool(getattr(engine, "cuda_graphs", False))
+        self.decode_ahead = bool(decode_ahead)
+        self._in_flight: _InFlight | None = None
+        self._pinned: list = []          # two pinned id buffers, used in turn
 
     # ------------------------------------------------------------------ intake
     def submit(self, request: Request):
@@ -116,6 +142,64 @@ class Scheduler:
 
     def active_count(self) -> int:
         return len(self.waiting) + len(self.running)
+
+    # ------------------------------------------------------------------ decoding ahead
+    def _ends_by_count(self, r: Request) -> bool:
+        """Will the token that is in flight for `r` be its last (by max_tokens or the context)?"""
+        n = len(r.output) + 1
+        return n >= r.params.max_tokens or len(r.prompt) + n >= self.ctx
+
+    def _leave_in_flight(self, requests, logits) -> _InFlight:
+        import torch
+        ids = self.sampler.greedy_on_device(logits)
+        if not self._pinned:                 # two buffers: one step is read while the next one's copy runs
+            n = max(len(requests), self.engine.cache.slots.n_slots)
+            self._pinned = [torch.empty(n, dtype=torch.int32) for _ in range(2)]
+            if ids.is_cuda:
+                self._pinned = [t.pin_memory() for t in self._pinned]
+        self._pinned.reverse()
+        host = self._pinned[0]
+        host[:len(requests)].copy_(ids, non_blocking=True)
+        copied = None
+        if ids.is_cuda:
+            copied = torch.cuda.Event()
+            copied.record()
+        return _InFlight(list(requests), ids, host, copied)
+
+    def _read(self, step: _InFlight) -> list:
+        """Wait for the ids of a step in flight and take them in."""
+        if step.copied is not None:
+            step.copied.synchronize()
+        tokens = step.host_tokens[:len(step.requests)].tolist()
+        return [self._accept(r, int(tok)) for r, tok in zip(step.requests, tokens) if r.id not in step.dead]
+
+    def _launch_ahead(self) -> _InFlight | None:
+        """The step after the one in flight, if it is a pure decode step of requests of that one."""
+        cur = self._in_flight
+        go_on = [r for r in cur.requests if r.id not in cur.dead and not self._ends_by_count(r)]
+        if not go_on or len(self.running) != len([r for r in cur.requests if r.id not in cur.dead]):
+            return None                      # nothing left to decode, or someone else (a prompt) is running
+        cache = self.engine.cache
+        wants = {r.id: 1 for r in go_on}
+        if not cache.can_reserve(wants):
+            return None                      # pages must be found by preemption: the plain path decides
+        if self.waiting:
+            head = self.waiting[0]
+            n = min(len(head.all_tokens()), self.max_batch_tokens - len(go_on), self.max_portion)
+            if n >= 1 and self.engine.can_run({**wants, head.id: n}):
+                return None                  # the head of the queue can be admitted now
+        import torch
+        ids = cur.device_tokens
+        if len(go_on) != len(cur.requests):
+            rows = [i for i, r in enumerate(cur.requests) if r in go_on]
+            ids = ids[torch.tensor(rows, dtype=torch.long, device=ids.device)]
+        logits = self.engine.step([StepEntry(r.id, [0], [0]) for r in go_on], device_tokens=ids)
+        self.counters["steps"] += 1
+        self.counters["steps_ahead"] += 1
+        self.counters["tokens"] += len(go_on)
+        for r in go_on:
+            r.n_fed += 1
+        return self._leave_in_flight(go_on, logits)
 
     # ------------------------------------------------------------------ planning
     def plan_step(self) -> StepPlan:
@@ -186,9 +270,20 @@ class Scheduler:
 
     # ------------------------------------------------------------------ running
     def step(self) -> list:
-        """Plan and run one step; returns what each request produced in it."""
+        """Plan and run one step; returns what each request produced (with decoding ahead: what was
+        read in this call, which is the step before the one launched)."""
+        outputs = []
+        if self._in_flight is not None:
+            ahead = self._launch_ahead()
+            outputs = self._read(self._in_flight)
+            self._in_flight = ahead
+            if ahead is not None:
+                ahead.dead = {r.id for r in ahead.requests if r.state is RequestState.DONE}
+                return outputs
+            if not self.active_count():
+                return outputs
         plan = self.plan_step()
-        outputs = [StepOutput(r.id, None, True, why) for r, why in plan.ended]
+        outputs += [StepOutput(r.id, None, True, why) for r, why in plan.ended]
         if not plan.entries:
             return outputs
         logits = self.engine.step([StepEntry(r.id, toks, [len(toks) - 1] if want else [])
@@ -200,6 +295,12 @@ class Scheduler:
             self.counters["tokens"] += len(toks)
             if want:
                 sampled.append(r)
+        if (self.decode_ahead and len(sampled) == len(plan.entries) == len(self.running)
+                and all(is_plain_greedy(r.params) for r in sampled)):
+            # every running request gets a token from this step and none needs the host to sample:
+            # leave the ids on the device and let the next call launch the next step before reading them
+            self._in_flight = self._leave_in_flight(sampled, logits)
+            return outputs
         tokens, states = self.sampler.sample(
             logits, [SampleRow(r.params, r.all_tokens(), r.rng_state) for r in sampled])
         for r, tok, st in zip(sampled, tokens, states):

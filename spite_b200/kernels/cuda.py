@@ -93,6 +93,7 @@ class CudaKernels(KernelSet):
         self.attention_tc_min_tokens = int(os.environ.get("SPITE_ATTENTION_TC_MIN_TOKENS", "0"))
         # row counts up to which the weight-streaming kernel is preferred over the tcgen05 one
         self.skinny_max_rows = int(os.environ.get("SPITE_SKINNY_MAX_ROWS", "16"))
+        self.skinny_blocks = int(float(os.environ.get("SPITE_SKINNY_BLOCKS_PER_SM", "2")) * self.sm_count)
         self.skinny_tall_rows = int(os.environ.get("SPITE_SKINNY_TALL_ROWS", "0"))
 
     # ------------------------------------------------------------------ helpers
@@ -153,7 +154,7 @@ class CudaKernels(KernelSet):
             few = p.M <= self.skinny_max_rows and not (not grouped and p.N >= 65536 and p.M > self.skinny_tall_rows)
             tc_ok = self.use_tcgen05 and p.K % 8 == 0 and p.lda % 8 == 0
             if few or (not tc_ok and max_rows_per_group <= 64):
-                st = self._lib("gemm_skinny").spite_gemm_skinny(C.byref(p), int(max_rows_per_group), 2 * self.sm_count,
+                st = self._lib("gemm_skinny").spite_gemm_skinny(C.byref(p), int(max_rows_per_group), self.skinny_blocks,
                                                                 self._stream())
                 if st != -2:                       # -2: shape outside the kernel's domain, fall through
                     self._count("gemm_skinny", 1)
@@ -179,7 +180,7 @@ class CudaKernels(KernelSet):
                 p = orig
                 if max_rows_per_group <= 64:       # refused (alignment): the streaming kernel may still take it
                     st = self._lib("gemm_skinny").spite_gemm_skinny(C.byref(p), int(max_rows_per_group),
-                                                                    2 * self.sm_count, self._stream())
+                                                                    self.skinny_blocks, self._stream())
                     if st != -2:
                         self._count("gemm_skinny", 1)
                         _check(st, what)

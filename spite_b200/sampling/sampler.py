@@ -65,9 +65,19 @@ class SampleRow:
     rng_state: int           # unsigned 64-bit
 
 
+def is_plain_greedy(params: SamplingParams) -> bool:
+    """Greedy decoding that is the argmax alone: temperature 0 and no repetition penalty (the
+    filters never remove the maximum)."""
+    return params.temperature <= 0 and abs(params.repetition_penalty - 1.0) < 1.2e-7
+
+
 class Sampler:
     def __init__(self, kernels):
         self.k = kernels
+
+    def greedy_on_device(self, logits: torch.Tensor) -> torch.Tensor:
+        """The argmax of every row as int32 on the device; nothing is read back."""
+        return self.k.argmax(logits)
 
     def sample(self, logits: torch.Tensor, rows: list) -> tuple[list, list]:
         """`logits` [R, vocab] float32 on the device, `rows` R `SampleRow`s.
@@ -76,9 +86,7 @@ class Sampler:
         if R == 0:
             return [], []
         dev = logits.device
-        plain_greedy = all(r.params.temperature <= 0 and abs(r.params.repetition_penalty - 1.0) < 1.2e-7
-                           for r in rows)
-        if plain_greedy:
+        if all(is_plain_greedy(r.params) for r in rows):
             # the filters never remove the maximum, so greedy decoding is the argmax alone
             return self.k.argmax(logits).tolist(), [r.rng_state for r in rows]
         ctx, offs = [], [0]

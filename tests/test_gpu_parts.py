@@ -336,3 +336,8 @@ def test_greedy_generation_through_the_entry_point(folder, dtype):
             assert i == 11
     assert generate(path, prompts[1:2], max_tokens=5, temperature=0.0, dtype=dtype, device=DEV,
                     cache_tokens=128, page_size=16, max_requests=2) == [got[1][:5]]
+    # the decode steps above were launched ahead of the reading of their ids; the plain loop gives the same
+    assert llm.last_counters["steps_ahead"] > 0
+    llm.decode_ahead = False
+    assert llm.generate(prompts, max_tokens=12, temperature=0.0) == got
+    assert llm.last_counters["steps_ahead"] == 0

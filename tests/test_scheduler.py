@@ -175,3 +175,38 @@ def test_no_slot_means_waiting_not_failing(model):
     assert [r.id for r in s.running] == [1] and [r.id for r in s.waiting] == [2]
     done = s.run_until_done()
     assert done[2].output == plain_greedy(model, PROMPTS[2], 3)
+
+
+@pytest.mark.parametrize("budget,pages,slots", [(2048, 512, 4), (24, 160, 3), (64, 96, 4), (7, 512, 2)])
+def test_decoding_ahead_produces_the_same_tokens(model, budget, pages, slots):
+    """With the sampled ids read one step late (decode steps launched from the ids on the device), every
+    request ends with the same tokens and reason as with the plain loop: ends by count, by an
+    end-of-generation and a stop token (which cost one discarded step), preemption when pages run out,
+    and requests that wait for a slot."""
+    ref = plain_greedy(model, PROMPTS[1], 12)
+
+    def run(ahead):
+        s = make(model, max_batch_tokens=budget, cache_tokens=pages, max_requests=slots,
+                 eos_token_ids=[ref[7]], decode_ahead=ahead)
+        s.submit(Request(0, PROMPTS[0][:40], greedy(14)))
+        s.submit(Request(1, PROMPTS[1], greedy(12)))                               # ends on the eos token
+        s.submit(Request(2, PROMPTS[2], greedy(9, stop_token_ids=(ref[4],))))
+        s.submit(Request(3, PROMPTS[1], greedy(5)))
+        s.submit(Request(4, PROMPTS[3], greedy(3)))
+        outs = []
+        while s.active_count():
+            outs += s.step()
+            s.engine.cache.check_invariants()
+        assert s._in_flight is None
+        assert s.engine.cache.free_pages() == [s.engine.n_pages] * 2
+        emitted = {i: [o.token for o in outs if o.request_id == i and o.token is not None] for i in range(5)}
+        return s, emitted
+
+    plain_run, plain_emitted = run(False)
+    ahead_run, ahead_emitted = run(True)
+    assert plain_run.counters["steps_ahead"] == 0 and ahead_run.counters["steps_ahead"] > 0
+    for i in range(5):
+        assert ahead_run.finished[i].output == plain_run.finished[i].output, i
+        assert ahead_run.finished[i].finish_reason is plain_run.finished[i].finish_reason, i
+        assert ahead_emitted[i] == plain_emitted[i] == plain_run.finished[i].output, i
+    assert plain_run.finished[1].finish_reason is FinishReason.EOS_TOKEN
