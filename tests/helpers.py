@@ -46,7 +46,19 @@ CONFIG_C = dict(
     attn_scale=0.2, rms_norm_eps=1e-5, max_position_embeddings=4096)
 STD_C = 0.03
 
-CONFIGS = {"A": (CONFIG_A, STD_A, 11), "B": (CONFIG_B, STD_B, 23), "C": (CONFIG_C, STD_C, 31)}
+# Awkward sizes: a width that is no multiple of 8, a head size that is no multiple of 16, seven query heads
+# on one kv head, an odd vocabulary, five experts, a window shorter than a page
+CONFIG_D = dict(
+    architectures=["Llama4ForCausalLM"], num_hidden_layers=3, hidden_size=100, num_attention_heads=7,
+    num_key_value_heads=1, head_dim=24, interleave_moe_layer_step=1, num_local_experts=5,
+    num_experts_per_tok=1, intermediate_size=44, intermediate_size_mlp=60, vocab_size=301,
+    tie_word_embeddings=True, rope_theta=1000.0, rope_scaling=None, attention_chunk_size=9,
+    no_rope_layer_interval=3, use_qk_norm=True, attn_temperature_tuning=False, floor_scale=8192,
+    attn_scale=0.1, rms_norm_eps=1e-4, max_position_embeddings=1024)
+STD_D = 0.05
+
+CONFIGS = {"A": (CONFIG_A, STD_A, 11), "B": (CONFIG_B, STD_B, 23), "C": (CONFIG_C, STD_C, 31),
+           "D": (CONFIG_D, STD_D, 47)}
 
 
 def write_model(folder, name: str, dtype=torch.bfloat16) -> Path:

@@ -134,6 +134,22 @@ def test_sizes_of_the_tcgen05_kernels(tmp_path):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_awkward_sizes(tmp_path, dtype):
+    """Sizes that the fast kernels refuse (width 100, head size 24, seven heads on one kv head, vocabulary
+    301): the general kernels take over, in both precisions, with the same answers."""
+    from spite_b200.engine import Model
+    path = H.write_model(tmp_path / "modelD", "D")
+    model = Model.from_folder(path, dtype=dtype, device="cuda:0")
+    lengths = {"a": 70, "b": 33}
+    if dtype == "float32":
+        requests = {r: H.random_tokens(301, n, 60 + i) for i, (r, n) in enumerate(lengths.items())}
+    else:
+        requests = {r: H.decisive_tokens(path, n, 60 + i, 0.03) for i, (r, n) in enumerate(lengths.items())}
+    for steps in (H.steps_whole(requests), H.steps_last_decoded(requests, 20), H.steps_portions(requests, 1)):
+        H.compare_with_plain(H.run_steps(_engine(model, steps, 16), steps), path, requests, TOL[dtype])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_trace_run_program(folder, dtype, tmp_path):
     """`bin/trace_run` as a user runs it: JSON lines in, `done <step>` lines and .f32 files out."""
     path, name = folder
