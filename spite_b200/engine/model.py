@@ -70,7 +70,9 @@ class Model:
         return out
 
     def kernel_libraries(self) -> list[str]:
-        libs = {"elementwise", "gemm_simt", "gemm_skinny", "gemm_tc"}
+        libs = {"elementwise", "gemm_simt"}
+        if self.dtype == torch.bfloat16:
+            libs |= {"gemm_skinny", "gemm_tc"}
         for _, part in self.parts():
             libs.update(part.kernel_libraries)
         return sorted(libs)

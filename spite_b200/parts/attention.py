@@ -34,6 +34,13 @@ class PagedAttention(Mixer):
         if head_dim % 2 or head_dim > 256:
             raise ConfigError(f"head_dim {head_dim} must be even and at most 256")
         self.d, self.nq, self.nkv, self.hd = int(hidden_size), int(num_heads), int(num_kv_heads), int(head_dim)
+        # only the attention kernels that these sizes can reach are compiled for the model
+        libs = ["gemm_simt", "attention"]
+        if ctx.dtype == torch.bfloat16 and self.hd % 16 == 0 and self.hd <= 128 and self.nq // self.nkv <= 16:
+            libs += ["attention_mma", "attention_rows"]
+            if self.hd in (64, 128):
+                libs.append("attention_tc")
+        self.kernel_libraries = tuple(libs)
         self.window = window if isinstance(window, Window) else Window(window[0], int(window[1]))
         self.position = build_part("position", position, ctx)
         self.qk_norm_eps = None if qk_norm_eps is None else float(qk_norm_eps)
