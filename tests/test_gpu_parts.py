@@ -311,6 +311,130 @@ def test_a_toy_mixer_with_state_is_registered_built_and_stepped():
     eng.cache.check_invariants()
 
 
+# ---------------------------------------------------------------------------- a toy routed feed-forward, a toy position encoding
+@dataclass(frozen=True)
+class ToyRoutedConfig:
+    hidden: int = 40
+    vocab: int = 83
+
+    @classmethod
+    def from_dict(cls, d):
+        return cls(d.get("hidden", 40), d.get("vocab", 83))
+
+    def plan(self):
+        from spite_b200.config import BlockSpec, LayerCall, ModelPlan, PartSpec
+        norm = PartSpec("rms_norm", {"size": self.hidden, "eps": 1e-5})
+        attn = PartSpec("paged_attention", dict(hidden_size=self.hidden, num_heads=4, num_kv_heads=2, head_dim=12,
+                                                position=PartSpec("toy_harmonic_rotation", {"head_dim": 12, "base": 0.37}),
+                                                window=("full", 0)))
+        ffn = PartSpec("toy_top2_with_bypass", {"hidden_size": self.hidden, "num_experts": 3, "expert_size": 24})
+        blocks = (BlockSpec("prenorm_residual", norm, attn, norm, ffn),) * 2
+        return ModelPlan(self.hidden, self.vocab, blocks, tuple(LayerCall(i, i) for i in range(2)), norm,
+                         tie_word_embeddings=True, max_positions=256)
+
+
+def test_a_toy_routed_feed_forward_and_a_toy_position_encoding_are_registered_built_and_stepped():
+    """Two more parts defined here, from the kernel set's operations alone: a feed-forward that sends every
+    token to its two best experts of three (sigmoid weights on the input, as the kernels apply them) beside
+    an ungated linear bypass, and a position encoding with harmonic frequencies base / (i + 1).  The model
+    is graph-safe, so its decode steps replay from CUDA graphs; whole prompts, portions and single tokens
+    agree with a plain computation of the same model."""
+    from spite_b200.config import config_from_dict, register_architecture
+    from spite_b200.engine import Engine, Model
+    from spite_b200.parts import FeedForward, ParamSpec, PositionEncoding, register_feed_forward, register_position
+
+    @register_position("toy_harmonic_rotation")
+    class ToyHarmonicRotation(PositionEncoding):
+        graph_safe = True
+
+        def __init__(self, ctx, head_dim, base):
+            super().__init__(ctx)
+            self._freq = torch.tensor([base / (i + 1) for i in range(head_dim // 2)], dtype=torch.float32,
+                                      device=ctx.device)
+
+        def frequencies(self):
+            return self._freq
+
+    @register_feed_forward("toy_top2_with_bypass")
+    class ToyTop2WithBypass(FeedForward):
+        graph_safe = True
+        kernel_libraries = ("gemm_simt", "moe")
+
+        def __init__(self, ctx, hidden_size, num_experts, expert_size):
+            super().__init__(ctx)
+            self.d, self.E, self.f = hidden_size, num_experts, expert_size
+
+        def param_specs(self):
+            return {"router": ParamSpec((self.E, self.d)), "gate_up": ParamSpec((self.E, 2 * self.f, self.d)),
+                    "down": ParamSpec((self.E, self.d, self.f)), "bypass": ParamSpec((self.d, self.d))}
+
+        def bind(self, params):
+            dt = self.ctx.dtype
+            self.router = params["router"].float().contiguous()
+            self.gate_up, self.down = params["gate_up"].to(dt).contiguous(), params["down"].to(dt).contiguous()
+            self.bypass = params["bypass"].to(dt).contiguous()
+
+        def forward(self, x, h, batch):
+            k = self.k
+            routing = k.moe_route(x, self.router, 2)
+            for slot in range(2):
+                a = torch.empty((x.shape[0], self.f), dtype=x.dtype, device=x.device)
+                k.grouped_linear_swiglu(x, self.gate_up, routing.sorted_rows[slot], routing.offsets[slot],
+                                        routing.weights[slot], a)
+                k.grouped_linear_accumulate(a, self.down, routing.sorted_rows[slot], routing.offsets[slot], h)
+            k.linear(x, self.bypass, h, accumulate=True)
+
+    register_architecture("ToyRoutedForTests")(ToyRoutedConfig)
+    cfg = config_from_dict({"architectures": ["ToyRoutedForTests"]})
+    model = Model.from_config(cfg, dtype="float32", device=DEV).init_random(seed=9, std=0.2)
+    assert model.graph_safe()
+
+    def plain_toy(tokens):
+        T = len(tokens)
+        h = model.embed_table[torch.tensor(tokens, device=DEV)].float().cpu()
+        pos = torch.arange(T)
+        for blk in model.blocks:
+            m, ff = blk.mixer, blk.ffn
+            x = plain.rms_norm(h, blk.mixer_norm.weight.cpu(), 1e-5)
+            qkv = (x @ m.wqkv.float().cpu().T).view(T, 8, 12)
+            freq = torch.tensor([0.37 / (i + 1) for i in range(6)])
+            q, k, v = qkv[:, :4], qkv[:, 4:6], qkv[:, 6:]
+            q, k = plain.apply_rotary(q, pos, freq), plain.apply_rotary(k, pos, freq)
+            mask = pos[None, :] <= pos[:, None]
+            h = h + plain.attention(q, k, v, mask).reshape(T, 48) @ m.wo.float().cpu().T
+            x = plain.rms_norm(h, blk.ffn_norm.weight.cpu(), 1e-5)
+            logits = x @ ff.router.cpu().T
+            order = torch.sort(logits, dim=-1, descending=True, stable=True)
+            y = x @ ff.bypass.float().cpu().T
+            for slot in range(2):
+                for t in range(T):
+                    e, w = int(order.indices[t, slot]), torch.sigmoid(order.values[t, slot])
+                    gu = (x[t] * w) @ ff.gate_up[e].float().cpu().T
+                    y[t] += (plain.silu(gu[:24]) * gu[24:]) @ ff.down[e].float().cpu().T
+            h = h + y
+        return plain.rms_norm(h, model.final_norm.weight.cpu(), 1e-5) @ model.embed_table.float().cpu().T
+
+    a, b = H.random_tokens(83, 45, 3), H.random_tokens(83, 28, 4)
+    ref_a, ref_b = plain_toy(a), plain_toy(b)
+    scale = float(ref_a.abs().max())
+    eng = Engine(model, cache_tokens=192, page_size=16, max_requests=3)
+    assert eng.cuda_graphs
+    whole = eng.step([("a", a, list(range(45)))]).cpu()
+    eng.finish("a")
+    assert float((whole - ref_a).abs().max()) / scale < 2e-5
+    got_a, got_b, ia, ib = [], [], 0, 0
+    for na, nb in [(9, 0), (2, 6), (1, 1), (1, 1), (1, 1), (14, 1), (1, 1), (1, 1), (1, 0), (1, 16), (13, 0)]:
+        entries = ([("a", a[ia:ia + na], list(range(na)))] if na else []) + ([("b", b[ib:ib + nb], list(range(nb)))] if nb else [])
+        out = eng.step(entries).cpu()
+        got_a.append(out[:na]); got_b.append(out[na:na + nb])
+        ia, ib = ia + na, ib + nb
+    assert ia == 45 and ib == 28 and eng.graph_replays > 0
+    assert float((torch.cat(got_a) - ref_a).abs().max()) / scale < 2e-5
+    assert float((torch.cat(got_b) - ref_b).abs().max()) / scale < 2e-5
+    eng.finish("a"); eng.finish("b")
+    eng.cache.check_invariants()
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_greedy_generation_through_the_entry_point(folder, dtype):
     from spite_b200 import LLM, generate
