@@ -20,7 +20,9 @@
 //              the output by the sum.
 // While one row tile's threads compute a softmax, the tensor cores work on the other tile's
 // products.  (A kernel that allocates tensor memory gets one block per multiprocessor, so the
-// overlap has to come from within the block.)
+// overlap has to come from within the block.)  Blocks are persistent, one per multiprocessor:
+// the work items (pair of row tiles, kv head) are dealt out round by round in alternating
+// direction, heaviest first, and between items the block renews its barriers.
 // The output accumulates in tensor memory.  A row's reference maximum moves only when the
 // tile's maximum exceeds it by more than 8 (in log2 units): then the row's part of O and its
 // sum are multiplied by 2^(old - new) before the next product is added.  P stays below 2^8, and
@@ -138,246 +140,246 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     // (r + 1) * blocks - 1 to the blocks, in alternating direction, so that the shares come out alike.
     const int n_items = n_tile_pairs * nkv;
     for (int round = 0;; ++round) {
-    const int item = round * gridDim.x + ((round & 1) ? gridDim.x - 1 - blockIdx.x : blockIdx.x);
-    if (item >= n_items) break;
-    const int kvh = item % nkv;
-    int idx = n_tile_pairs - 1 - item / nkv, seg = -1, t0 = 0, nt = 0;
-    for (int s = 0; s < x.n_segments; ++s) {
-        const int lo = x.cu_seqlens[s], n = x.cu_seqlens[s + 1] - lo;
-        if (n < x.seg_min_tokens || n > x.seg_max_tokens) continue;   // another kernel serves this segment
-        const int blocks = (n + 2 * tpt - 1) / (2 * tpt);
-        if (idx < blocks) { seg = s; t0 = lo + idx * 2 * tpt; nt = min(2 * tpt, lo + n - t0); break; }
-        idx -= blocks;
-    }
-    if (seg < 0) break;                                   // the caller counted more tile pairs than there are
-    const int* table = b.block_table + (size_t)seg * b.table_width;
-    // key tiles of the item: from the first key the first token sees to the last token's own
-    const int k_begin = (window_lowest(p.window_kind, p.window_size, b.positions[t0]) / BN) * BN;
-    const int n_tiles = (b.positions[t0 + nt - 1] - k_begin) / BN + 1;
-
-    if (warp == 0) {
-        if (lane == 0) {
-            // ---- loader
-            const unsigned q_bar = smem_u32(&bars.q_full);
-            mbar_expect_tx(q_bar, (unsigned)(2 * NKB * q_box_tokens * G * 128));
-#pragma unroll
-            for (int g = 0; g < 2; ++g)
-#pragma unroll
-                for (int kb = 0; kb < NKB; ++kb)
-                    tma_load_3d(smem_u32(q_s + g * Q_BYTES + kb * BM * 128), &map_q, kb * 64, kvh * G, t0 + g * tpt, q_bar);
-            int issued_k = 0, issued_v = 0;
-            for (int i = 0; i < n_tiles; ++i) {
-                const int s = i % ST;
-                const unsigned ph = (i / ST) & 1;
-                const int j0 = k_begin + i * BN;
-                int page = table[j0 / c.page_size];
-                if (page < 0 || page >= c.n_pages) page = 0;   // a page behind every row's window: its keys are masked
-                const int y = (page * nkv + kvh) * c.page_size + j0 % c.page_size;
-                if (!mbar_wait(smem_u32(&bars.k_empty[s]), ph ^ 1, abort_flag, &g_attn_tc_error, 1)) break;
-                mbar_expect_tx(smem_u32(&bars.k_full[s]), KT_BYTES);
-#pragma unroll
-                for (int kb = 0; kb < NKB; ++kb)
-                    tma_load_2d(smem_u32(k_s + s * KT_BYTES + kb * BN * 128), &map_k, kb * 64, y, smem_u32(&bars.k_full[s]));
-                ++issued_k;
-                if (!mbar_wait(smem_u32(&bars.v_empty[s]), ph ^ 1, abort_flag, &g_attn_tc_error, 1)) break;
-                mbar_expect_tx(smem_u32(&bars.v_full[s]), KT_BYTES);
-#pragma unroll
-                for (int kb = 0; kb < NKB; ++kb)
-                    tma_load_2d(smem_u32(v_s + s * KT_BYTES + kb * BN * 128), &map_v, kb * 64, y, smem_u32(&bars.v_full[s]));
-                ++issued_v;
-            }
-            // the last releases of the stages must have arrived before the barriers are renewed for the next item
-            for (int j = max(0, n_tiles - ST); j < n_tiles && !*abort_flag; ++j) {
-                if (!mbar_wait(smem_u32(&bars.k_empty[j % ST]), (j / ST) & 1, abort_flag, &g_attn_tc_error, 1)) break;
-                if (!mbar_wait(smem_u32(&bars.v_empty[j % ST]), (j / ST) & 1, abort_flag, &g_attn_tc_error, 1)) break;
-            }
-            if (*abort_flag) {
-                // copies in flight must land before the block gives its shared memory back
-                mbar_drain(q_bar, 0);
-                for (int j = max(0, issued_k - ST); j < issued_k; ++j) mbar_drain(smem_u32(&bars.k_full[j % ST]), (j / ST) & 1);
-                for (int j = max(0, issued_v - ST); j < issued_v; ++j) mbar_drain(smem_u32(&bars.v_full[j % ST]), (j / ST) & 1);
-            }
+        const int item = round * gridDim.x + ((round & 1) ? gridDim.x - 1 - blockIdx.x : blockIdx.x);
+        if (item >= n_items) break;
+        const int kvh = item % nkv;
+        int idx = n_tile_pairs - 1 - item / nkv, seg = -1, t0 = 0, nt = 0;
+        for (int s = 0; s < x.n_segments; ++s) {
+            const int lo = x.cu_seqlens[s], n = x.cu_seqlens[s + 1] - lo;
+            if (n < x.seg_min_tokens || n > x.seg_max_tokens) continue;   // another kernel serves this segment
+            const int blocks = (n + 2 * tpt - 1) / (2 * tpt);
+            if (idx < blocks) { seg = s; t0 = lo + idx * 2 * tpt; nt = min(2 * tpt, lo + n - t0); break; }
+            idx -= blocks;
         }
-    } else {
-        // ---- one of the two row tiles
-        const int g = warp < 3 ? warp - 1 : (warp - 3) >> 2;
-        GroupBarriers& gb = bars.g[g];
-        const int tg0 = t0 + g * tpt;
-        const int ntg = max(0, min(tpt, nt - g * tpt));
-        // this row tile's own key tiles, [first, last] among the block's; the second tile of a block may hold no token
-        int first = 0, last = -1, p_first = 0, lo_last = 0;
-        if (ntg > 0) {
-            p_first = b.positions[tg0];
-            const int p_last = b.positions[tg0 + ntg - 1];
-            lo_last = window_lowest(p.window_kind, p.window_size, p_last);
-            first = (window_lowest(p.window_kind, p.window_size, p_first) / BN * BN - k_begin) / BN;
-            last = (p_last - k_begin) / BN;
-        }
-        const int n_own = last - first + 1;
-        const unsigned tmem_g = tmem + g * GROUP_COLS;
-        unsigned char* q_g = q_s + g * Q_BYTES;
-        unsigned char* p_g = p_s + g * P_BYTES;
+        if (seg < 0) break;                                   // the caller counted more tile pairs than there are
+        const int* table = b.block_table + (size_t)seg * b.table_width;
+        // key tiles of the item: from the first key the first token sees to the last token's own
+        const int k_begin = (window_lowest(p.window_kind, p.window_size, b.positions[t0]) / BN) * BN;
+        const int n_tiles = (b.positions[t0 + nt - 1] - k_begin) / BN + 1;
 
-        if (warp < 3) {
+        if (warp == 0) {
             if (lane == 0) {
-                // ---- tensor-core issue for this row tile
-                const unsigned idesc_s = make_idesc(BM, BN), idesc_pv = make_idesc(BM, HD, true);
-                bool ok = mbar_wait(smem_u32(&bars.q_full), 0, abort_flag, &g_attn_tc_error, 2);
-                // a key tile that this row tile does not need: wait until it has landed (so that the two
-                // row tiles never drift apart by more than the ring) and hand the stage back unread
-                auto pass_tile = [&](int i) {
+                // ---- loader
+                const unsigned q_bar = smem_u32(&bars.q_full);
+                mbar_expect_tx(q_bar, (unsigned)(2 * NKB * q_box_tokens * G * 128));
+#pragma unroll
+                for (int g = 0; g < 2; ++g)
+#pragma unroll
+                    for (int kb = 0; kb < NKB; ++kb)
+                        tma_load_3d(smem_u32(q_s + g * Q_BYTES + kb * BM * 128), &map_q, kb * 64, kvh * G, t0 + g * tpt, q_bar);
+                int issued_k = 0, issued_v = 0;
+                for (int i = 0; i < n_tiles; ++i) {
                     const int s = i % ST;
                     const unsigned ph = (i / ST) & 1;
-                    if (!mbar_wait(smem_u32(&bars.k_full[s]), ph, abort_flag, &g_attn_tc_error, 2)) return false;
-                    mbar_arrive(smem_u32(&bars.k_empty[s]));
-                    if (!mbar_wait(smem_u32(&bars.v_full[s]), ph, abort_flag, &g_attn_tc_error, 2)) return false;
-                    mbar_arrive(smem_u32(&bars.v_empty[s]));
-                    return true;
-                };
-                // scores of own tile li (key tile first + li) into score buffer li & 1
-                auto issue_scores = [&](int li) {
-                    const int i = first + li, s = i % ST, sb = li & 1;
-                    if (!mbar_wait(smem_u32(&bars.k_full[s]), (i / ST) & 1, abort_flag, &g_attn_tc_error, 2)) return false;
-                    if (!mbar_wait(smem_u32(&gb.s_free[sb]), ((li >> 1) & 1) ^ 1, abort_flag, &g_attn_tc_error, 2)) return false;
-                    fence_after();
-                    const unsigned qa = smem_u32(q_g), ka = smem_u32(k_s + s * KT_BYTES);
+                    const int j0 = k_begin + i * BN;
+                    int page = table[j0 / c.page_size];
+                    if (page < 0 || page >= c.n_pages) page = 0;   // a page behind every row's window: its keys are masked
+                    const int y = (page * nkv + kvh) * c.page_size + j0 % c.page_size;
+                    if (!mbar_wait(smem_u32(&bars.k_empty[s]), ph ^ 1, abort_flag, &g_attn_tc_error, 1)) break;
+                    mbar_expect_tx(smem_u32(&bars.k_full[s]), KT_BYTES);
 #pragma unroll
-                    for (int ks = 0; ks < HD / 16; ++ks)
-                        mma(tmem_g + sb * BN, smem_desc_k_major(qa + (ks / 4) * BM * 128 + (ks % 4) * 32),
-                            smem_desc_k_major(ka + (ks / 4) * BN * 128 + (ks % 4) * 32), idesc_s, ks > 0 ? 1u : 0u);
-                    commit(smem_u32(&gb.s_full[sb]));
-                    commit(smem_u32(&bars.k_empty[s]));
-                    return true;
-                };
-                for (int i = 0; i < first && ok; ++i) ok = pass_tile(i);
-                if (ok && n_own > 0) ok = issue_scores(0);
-                if (ok && n_own > 1) ok = issue_scores(1);
-                for (int li = 0; li < n_own && ok; ++li) {
-                    const int i = first + li, s = i % ST;
-                    ok = mbar_wait(smem_u32(&gb.p_ready), li & 1, abort_flag, &g_attn_tc_error, 2) &&
-                         mbar_wait(smem_u32(&bars.v_full[s]), (i / ST) & 1, abort_flag, &g_attn_tc_error, 2);
-                    if (!ok) break;
-                    fence_after();
-                    const unsigned pa = smem_u32(p_g), va = smem_u32(v_s + s * KT_BYTES);
+                    for (int kb = 0; kb < NKB; ++kb)
+                        tma_load_2d(smem_u32(k_s + s * KT_BYTES + kb * BN * 128), &map_k, kb * 64, y, smem_u32(&bars.k_full[s]));
+                    ++issued_k;
+                    if (!mbar_wait(smem_u32(&bars.v_empty[s]), ph ^ 1, abort_flag, &g_attn_tc_error, 1)) break;
+                    mbar_expect_tx(smem_u32(&bars.v_full[s]), KT_BYTES);
 #pragma unroll
-                    for (int ks = 0; ks < BN / 16; ++ks)
-                        mma(tmem_g + 2 * BN, smem_desc_k_major(pa + ks * 32), smem_desc(va + ks * 16 * 128, BN * 128, 1024),
-                            idesc_pv, (li > 0 || ks > 0) ? 1u : 0u);
-                    commit(smem_u32(&gb.pv_done));
-                    commit(smem_u32(&bars.v_empty[s]));
-                    if (li + 2 < n_own) ok = issue_scores(li + 2);
+                    for (int kb = 0; kb < NKB; ++kb)
+                        tma_load_2d(smem_u32(v_s + s * KT_BYTES + kb * BN * 128), &map_v, kb * 64, y, smem_u32(&bars.v_full[s]));
+                    ++issued_v;
                 }
-                for (int i = last + 1; i < n_tiles && ok; ++i) ok = pass_tile(i);
+                // the last releases of the stages must have arrived before the barriers are renewed for the next item
+                for (int j = max(0, n_tiles - ST); j < n_tiles && !*abort_flag; ++j) {
+                    if (!mbar_wait(smem_u32(&bars.k_empty[j % ST]), (j / ST) & 1, abort_flag, &g_attn_tc_error, 1)) break;
+                    if (!mbar_wait(smem_u32(&bars.v_empty[j % ST]), (j / ST) & 1, abort_flag, &g_attn_tc_error, 1)) break;
+                }
+                if (*abort_flag) {
+                    // copies in flight must land before the block gives its shared memory back
+                    mbar_drain(q_bar, 0);
+                    for (int j = max(0, issued_k - ST); j < issued_k; ++j) mbar_drain(smem_u32(&bars.k_full[j % ST]), (j / ST) & 1);
+                    for (int j = max(0, issued_v - ST); j < issued_v; ++j) mbar_drain(smem_u32(&bars.v_full[j % ST]), (j / ST) & 1);
+                }
             }
         } else {
-            // ---- softmax: one thread per row; warp w may read tensor-memory lanes [32 (w % 4), + 32)
-            const int quarter = warp & 3;
-            const int r = quarter * 32 + lane;
-            const bool row_ok = r < ntg * G;
-            const int tok = tg0 + (row_ok ? r / G : 0), head = kvh * G + (row_ok ? r % G : 0);
-            const int pos = row_ok ? b.positions[tok] : -1;   // a row without a token sees no key
-            const int lo = window_lowest(p.window_kind, p.window_size, max(pos, 0));
-            const float scale = p.softmax_scale * LOG2E;
-            const unsigned lane_base = tmem_g + ((unsigned)(quarter * 32) << 16);
-            float m_ref = -INFINITY, l = 0.f;
-            bool ok = true;
-            for (int li = 0; li < n_own; ++li) {
-                const int sb = li & 1;
-                ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&gb.s_full[sb]), (li >> 1) & 1, abort_flag, &g_attn_tc_error, 3));
-                if (!ok) break;
-                fence_after();
-                float s[BN];
-                {
-                    float t[32];
-                    ld32(t, lane_base + sb * BN);
+            // ---- one of the two row tiles
+            const int g = warp < 3 ? warp - 1 : (warp - 3) >> 2;
+            GroupBarriers& gb = bars.g[g];
+            const int tg0 = t0 + g * tpt;
+            const int ntg = max(0, min(tpt, nt - g * tpt));
+            // this row tile's own key tiles, [first, last] among the block's; the second tile of a block may hold no token
+            int first = 0, last = -1, p_first = 0, lo_last = 0;
+            if (ntg > 0) {
+                p_first = b.positions[tg0];
+                const int p_last = b.positions[tg0 + ntg - 1];
+                lo_last = window_lowest(p.window_kind, p.window_size, p_last);
+                first = (window_lowest(p.window_kind, p.window_size, p_first) / BN * BN - k_begin) / BN;
+                last = (p_last - k_begin) / BN;
+            }
+            const int n_own = last - first + 1;
+            const unsigned tmem_g = tmem + g * GROUP_COLS;
+            unsigned char* q_g = q_s + g * Q_BYTES;
+            unsigned char* p_g = p_s + g * P_BYTES;
+
+            if (warp < 3) {
+                if (lane == 0) {
+                    // ---- tensor-core issue for this row tile
+                    const unsigned idesc_s = make_idesc(BM, BN), idesc_pv = make_idesc(BM, HD, true);
+                    bool ok = mbar_wait(smem_u32(&bars.q_full), 0, abort_flag, &g_attn_tc_error, 2);
+                    // a key tile that this row tile does not need: wait until it has landed (so that the two
+                    // row tiles never drift apart by more than the ring) and hand the stage back unread
+                    auto pass_tile = [&](int i) {
+                        const int s = i % ST;
+                        const unsigned ph = (i / ST) & 1;
+                        if (!mbar_wait(smem_u32(&bars.k_full[s]), ph, abort_flag, &g_attn_tc_error, 2)) return false;
+                        mbar_arrive(smem_u32(&bars.k_empty[s]));
+                        if (!mbar_wait(smem_u32(&bars.v_full[s]), ph, abort_flag, &g_attn_tc_error, 2)) return false;
+                        mbar_arrive(smem_u32(&bars.v_empty[s]));
+                        return true;
+                    };
+                    // scores of own tile li (key tile first + li) into score buffer li & 1
+                    auto issue_scores = [&](int li) {
+                        const int i = first + li, s = i % ST, sb = li & 1;
+                        if (!mbar_wait(smem_u32(&bars.k_full[s]), (i / ST) & 1, abort_flag, &g_attn_tc_error, 2)) return false;
+                        if (!mbar_wait(smem_u32(&gb.s_free[sb]), ((li >> 1) & 1) ^ 1, abort_flag, &g_attn_tc_error, 2)) return false;
+                        fence_after();
+                        const unsigned qa = smem_u32(q_g), ka = smem_u32(k_s + s * KT_BYTES);
 #pragma unroll
-                    for (int e = 0; e < 32; ++e) s[e] = t[e];
-                    ld32(t, lane_base + sb * BN + 32);
+                        for (int ks = 0; ks < HD / 16; ++ks)
+                            mma(tmem_g + sb * BN, smem_desc_k_major(qa + (ks / 4) * BM * 128 + (ks % 4) * 32),
+                                smem_desc_k_major(ka + (ks / 4) * BN * 128 + (ks % 4) * 32), idesc_s, ks > 0 ? 1u : 0u);
+                        commit(smem_u32(&gb.s_full[sb]));
+                        commit(smem_u32(&bars.k_empty[s]));
+                        return true;
+                    };
+                    for (int i = 0; i < first && ok; ++i) ok = pass_tile(i);
+                    if (ok && n_own > 0) ok = issue_scores(0);
+                    if (ok && n_own > 1) ok = issue_scores(1);
+                    for (int li = 0; li < n_own && ok; ++li) {
+                        const int i = first + li, s = i % ST;
+                        ok = mbar_wait(smem_u32(&gb.p_ready), li & 1, abort_flag, &g_attn_tc_error, 2) &&
+                             mbar_wait(smem_u32(&bars.v_full[s]), (i / ST) & 1, abort_flag, &g_attn_tc_error, 2);
+                        if (!ok) break;
+                        fence_after();
+                        const unsigned pa = smem_u32(p_g), va = smem_u32(v_s + s * KT_BYTES);
 #pragma unroll
-                    for (int e = 0; e < 32; ++e) s[32 + e] = t[e];
-                }
-                fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(&gb.s_free[sb]));   // the tensor cores may overwrite this score tile
-                const int j0 = k_begin + (first + li) * BN;
-                const bool open = j0 >= lo_last && j0 + BN - 1 <= p_first;   // every key visible to every row with a token
-                // maximum of the raw scores (the scale is positive); four running values shorten the chain
-                float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-                if (!open) {                                   // a tile on a window's edge or on the diagonal
-#pragma unroll
-                    for (int e = 0; e < BN; ++e) {
-                        const int j = j0 + e;
-                        s[e] = (j >= lo && j <= pos) ? s[e] : -INFINITY;
+                        for (int ks = 0; ks < BN / 16; ++ks)
+                            mma(tmem_g + 2 * BN, smem_desc_k_major(pa + ks * 32), smem_desc(va + ks * 16 * 128, BN * 128, 1024),
+                                idesc_pv, (li > 0 || ks > 0) ? 1u : 0u);
+                        commit(smem_u32(&gb.pv_done));
+                        commit(smem_u32(&bars.v_empty[s]));
+                        if (li + 2 < n_own) ok = issue_scores(li + 2);
                     }
+                    for (int i = last + 1; i < n_tiles && ok; ++i) ok = pass_tile(i);
                 }
-#pragma unroll
-                for (int e = 0; e < BN; ++e) mx4[e & 3] = fmaxf(mx4[e & 3], s[e]);
-                const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale;
-                const bool need = mx > m_ref + RESCALE_STEP;
-                float corr = 1.f;
-                if (need) { corr = exp2f(m_ref - mx); l *= corr; m_ref = mx; }
-                const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref;
-                unsigned packed[BN / 2];
-                float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-                for (int e = 0; e < BN; e += 2) {
-                    const float a = ex2(fmaf(s[e], scale, neg_m)), bb = ex2(fmaf(s[e + 1], scale, neg_m));
-                    sum4[(e >> 1) & 3] += a + bb;
-                    packed[e / 2] = pack_bf16(a, bb);
-                }
-                const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-                l += sum;
-                if (li > 0) {
-                    // the product of the tile before must have read P and left O before either changes
-                    ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&gb.pv_done), (li - 1) & 1, abort_flag, &g_attn_tc_error, 3));
+            } else {
+                // ---- softmax: one thread per row; warp w may read tensor-memory lanes [32 (w % 4), + 32)
+                const int quarter = warp & 3;
+                const int r = quarter * 32 + lane;
+                const bool row_ok = r < ntg * G;
+                const int tok = tg0 + (row_ok ? r / G : 0), head = kvh * G + (row_ok ? r % G : 0);
+                const int pos = row_ok ? b.positions[tok] : -1;   // a row without a token sees no key
+                const int lo = window_lowest(p.window_kind, p.window_size, max(pos, 0));
+                const float scale = p.softmax_scale * LOG2E;
+                const unsigned lane_base = tmem_g + ((unsigned)(quarter * 32) << 16);
+                float m_ref = -INFINITY, l = 0.f;
+                bool ok = true;
+                for (int li = 0; li < n_own; ++li) {
+                    const int sb = li & 1;
+                    ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&gb.s_full[sb]), (li >> 1) & 1, abort_flag, &g_attn_tc_error, 3));
                     if (!ok) break;
                     fence_after();
-                    if (__any_sync(0xffffffffu, need)) {
-#pragma unroll 1
-                        for (int c0 = 0; c0 < HD; c0 += 32) {
-                            float o[32];
-                            ld32(o, lane_base + 2 * BN + c0);
+                    float s[BN];
+                    {
+                        float t[32];
+                        ld32(t, lane_base + sb * BN);
 #pragma unroll
-                            for (int e = 0; e < 32; ++e) o[e] *= corr;
-                            st32(lane_base + 2 * BN + c0, o);
+                        for (int e = 0; e < 32; ++e) s[e] = t[e];
+                        ld32(t, lane_base + sb * BN + 32);
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) s[32 + e] = t[e];
+                    }
+                    fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&gb.s_free[sb]));   // the tensor cores may overwrite this score tile
+                    const int j0 = k_begin + (first + li) * BN;
+                    const bool open = j0 >= lo_last && j0 + BN - 1 <= p_first;   // every key visible to every row with a token
+                    // maximum of the raw scores (the scale is positive); four running values shorten the chain
+                    float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+                    if (!open) {                                   // a tile on a window's edge or on the diagonal
+#pragma unroll
+                        for (int e = 0; e < BN; ++e) {
+                            const int j = j0 + e;
+                            s[e] = (j >= lo && j <= pos) ? s[e] : -INFINITY;
                         }
                     }
-                }
 #pragma unroll
-                for (int ch = 0; ch < 8; ++ch)
-                    *(uint4*)(p_g + r * 128 + ((ch ^ (r & 7)) << 4)) =
-                        make_uint4(packed[4 * ch], packed[4 * ch + 1], packed[4 * ch + 2], packed[4 * ch + 3]);
-                fence_proxy_async();
-                fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(&gb.p_ready));
-            }
-            if (ok && n_own > 0)
-                ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&gb.pv_done), (n_own - 1) & 1, abort_flag, &g_attn_tc_error, 3));
-            if (ok && n_own > 0) {
-                fence_after();
-                const float inv = 1.0f / fmaxf(l, 1e-30f);
-                __nv_bfloat16* dst = (__nv_bfloat16*)p.out + ((size_t)tok * nq + head) * HD;
+                    for (int e = 0; e < BN; ++e) mx4[e & 3] = fmaxf(mx4[e & 3], s[e]);
+                    const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale;
+                    const bool need = mx > m_ref + RESCALE_STEP;
+                    float corr = 1.f;
+                    if (need) { corr = exp2f(m_ref - mx); l *= corr; m_ref = mx; }
+                    const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref;
+                    unsigned packed[BN / 2];
+                    float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                    for (int e = 0; e < BN; e += 2) {
+                        const float a = ex2(fmaf(s[e], scale, neg_m)), bb = ex2(fmaf(s[e + 1], scale, neg_m));
+                        sum4[(e >> 1) & 3] += a + bb;
+                        packed[e / 2] = pack_bf16(a, bb);
+                    }
+                    const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+                    l += sum;
+                    if (li > 0) {
+                        // the product of the tile before must have read P and left O before either changes
+                        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&gb.pv_done), (li - 1) & 1, abort_flag, &g_attn_tc_error, 3));
+                        if (!ok) break;
+                        fence_after();
+                        if (__any_sync(0xffffffffu, need)) {
 #pragma unroll 1
-                for (int c0 = 0; c0 < HD; c0 += 32) {
-                    float o[32];
-                    ld32(o, lane_base + 2 * BN + c0);          // warp-collective: every lane takes part
-                    if (!row_ok) continue;
+                            for (int c0 = 0; c0 < HD; c0 += 32) {
+                                float o[32];
+                                ld32(o, lane_base + 2 * BN + c0);
 #pragma unroll
-                    for (int e = 0; e < 32; e += 8)
-                        *(uint4*)(dst + c0 + e) = make_uint4(pack_bf16(o[e] * inv, o[e + 1] * inv), pack_bf16(o[e + 2] * inv, o[e + 3] * inv),
-                                                             pack_bf16(o[e + 4] * inv, o[e + 5] * inv), pack_bf16(o[e + 6] * inv, o[e + 7] * inv));
+                                for (int e = 0; e < 32; ++e) o[e] *= corr;
+                                st32(lane_base + 2 * BN + c0, o);
+                            }
+                        }
+                    }
+#pragma unroll
+                    for (int ch = 0; ch < 8; ++ch)
+                        *(uint4*)(p_g + r * 128 + ((ch ^ (r & 7)) << 4)) =
+                            make_uint4(packed[4 * ch], packed[4 * ch + 1], packed[4 * ch + 2], packed[4 * ch + 3]);
+                    fence_proxy_async();
+                    fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&gb.p_ready));
+                }
+                if (ok && n_own > 0)
+                    ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&gb.pv_done), (n_own - 1) & 1, abort_flag, &g_attn_tc_error, 3));
+                if (ok && n_own > 0) {
+                    fence_after();
+                    const float inv = 1.0f / fmaxf(l, 1e-30f);
+                    __nv_bfloat16* dst = (__nv_bfloat16*)p.out + ((size_t)tok * nq + head) * HD;
+#pragma unroll 1
+                    for (int c0 = 0; c0 < HD; c0 += 32) {
+                        float o[32];
+                        ld32(o, lane_base + 2 * BN + c0);          // warp-collective: every lane takes part
+                        if (!row_ok) continue;
+#pragma unroll
+                        for (int e = 0; e < 32; e += 8)
+                            *(uint4*)(dst + c0 + e) = make_uint4(pack_bf16(o[e] * inv, o[e + 1] * inv), pack_bf16(o[e + 2] * inv, o[e + 3] * inv),
+                                                                 pack_bf16(o[e + 4] * inv, o[e + 5] * inv), pack_bf16(o[e + 6] * inv, o[e + 7] * inv));
+                    }
                 }
             }
         }
-    }
-    // end of the item: everything asynchronous has been waited for; renew the barriers
-    fence_before();
-    __syncthreads();
-    fence_after();
-    if (*abort_flag) break;
-    if (threadIdx.x == 0) init_barriers(true);
-    __syncthreads();
+        // end of the item: everything asynchronous has been waited for; renew the barriers
+        fence_before();
+        __syncthreads();
+        fence_after();
+        if (*abort_flag) break;
+        if (threadIdx.x == 0) init_barriers(true);
+        __syncthreads();
     }
     fence_before();
     __syncthreads();
