@@ -25,8 +25,7 @@
 // Rows of A are contiguous (a grouped product gets its rows gathered into expert order
 // beforehand); `a_rows`, if set, only indexes `row_scale`.  Edges in M, N and K are
 // covered by TMA's zero fill on loads and by bounds checks on stores.
-#include "gemm.cuh"
-#include "tcgen05.cuh"
+#include "gemm_tc_epilogue.cuh"
 
 namespace {
 using namespace tc;
@@ -207,66 +206,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             ok = mbar_wait(smem_u32(&tail->acc_full[buf]), (lt >> 1) & 1, abort_flag, &g_tc_error, 3);
             if (!ok) break;
             fence_after();
-            const int li = t.row0 + r;
-            const bool row_ok = r < t.rows;
-            int crow = li, srow = li;
-            float sc = 1.f;
-            if (row_ok) {
-                if (p.c_rows) crow = p.c_rows[li];
-                if (p.row_scale) {
-                    if (p.scale_by_a_row && p.a_rows) srow = p.a_rows[li];
-                    sc = p.row_scale[srow];
-                }
-            }
-            const unsigned lane_addr = tmem + buf * ACC_COLS + ((unsigned)(quarter * 32) << 16);
-#pragma unroll 1
-            for (int c0 = 0; c0 < cols_per_tile; c0 += 32) {
-                float v[32];
-                ld32(v, lane_addr + c0);                    // warp-collective: every lane takes part
-                float u[32];
-                if (DUAL) ld32(u, lane_addr + bnh + c0);
-                const int n = t.n0 + c0;
-                if (!row_ok || n >= p.N) continue;
-                const size_t o = (size_t)crow * p.ldc + n;
-                const bool full = (n + 32 <= p.N);
-                if (EPI == EPI_STORE || EPI == EPI_SWIGLU) {
-                    __nv_bfloat16* dst = (__nv_bfloat16*)p.C + o;
-                    float y[32];
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) y[i] = DUAL ? silu_f32(v[i] * sc) * (u[i] * sc) : v[i] * sc;
-                    if (full && ((uintptr_t)dst & 15) == 0) {
-#pragma unroll
-                        for (int i = 0; i < 32; i += 8) {
-                            uint4 q;
-                            __nv_bfloat162 h0 = __floats2bfloat162_rn(y[i], y[i + 1]), h1 = __floats2bfloat162_rn(y[i + 2], y[i + 3]);
-                            __nv_bfloat162 h2 = __floats2bfloat162_rn(y[i + 4], y[i + 5]), h3 = __floats2bfloat162_rn(y[i + 6], y[i + 7]);
-                            q.x = *(unsigned*)&h0; q.y = *(unsigned*)&h1; q.z = *(unsigned*)&h2; q.w = *(unsigned*)&h3;
-                            *(uint4*)(dst + i) = q;
-                        }
-                    } else {
-#pragma unroll
-                        for (int i = 0; i < 32; ++i)
-                            if (n + i < p.N) dst[i] = __float2bfloat16_rn(y[i]);
-                    }
-                } else {
-                    float* dst = (float*)p.C + o;
-                    if (full && ((uintptr_t)dst & 15) == 0) {
-#pragma unroll
-                        for (int i = 0; i < 32; i += 4) {
-                            float4 q = make_float4(v[i] * sc, v[i + 1] * sc, v[i + 2] * sc, v[i + 3] * sc);
-                            if (EPI == EPI_ADD_F32) {
-                                const float4 old = *(const float4*)(dst + i);
-                                q.x += old.x; q.y += old.y; q.z += old.z; q.w += old.w;
-                            }
-                            *(float4*)(dst + i) = q;
-                        }
-                    } else {
-#pragma unroll
-                        for (int i = 0; i < 32; ++i)
-                            if (n + i < p.N) dst[i] = (EPI == EPI_ADD_F32 ? dst[i] : 0.f) + v[i] * sc;
-                    }
-                }
-            }
+            drain_accumulator_row<EPI>(p, t.row0 + r, r < t.rows, t.n0, cols_per_tile, bnh,
+                                       tmem + buf * ACC_COLS + ((unsigned)(quarter * 32) << 16));
             // this warp has read its lanes of the accumulator: hand it back to the tensor cores
             fence_before();
             __syncwarp();
@@ -283,14 +224,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 }
 
 // ---------------------------------------------------------------- host side
-// A row-major [rows, cols] bfloat16 matrix with leading dimension ld; boxes of 64 columns x box_rows rows.
-bool make_matrix_map(CUtensorMap* map, const void* base, long long rows, long long cols, long long ld, int box_rows) {
-    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
-    return make_map(map, base, 2, dims, strides, box);
-}
-
 // Half-tile height that makes the tile waves fullest: fewest rounds of n_blocks tiles, weighted by
 // the tile's width plus a fixed cost for filling and draining the pipeline.
 int choose_bnh(const GemmParams& p, int row_tiles, int n_blocks) {

@@ -30,6 +30,7 @@ LIBRARIES = {
     "gemm_simt": (["gemm_simt.cu"], []),
     "gemm_skinny": (["gemm_skinny.cu"], []),
     "gemm_tc": (["gemm_tc.cu"], []),
+    "gemm_tc_pair": (["gemm_tc_pair.cu"], []),
     "attention": (["attention.cu"], []),
     "attention_mma": (["attention_mma.cu"], []),
     "attention_rows": (["attention_rows.cu"], []),

@@ -94,6 +94,8 @@ class CudaKernels(KernelSet):
         # row counts up to which the weight-streaming kernel is preferred over the tcgen05 one
         self.skinny_max_rows = int(os.environ.get("SPITE_SKINNY_MAX_ROWS", "16"))
         self.skinny_blocks = int(float(os.environ.get("SPITE_SKINNY_BLOCKS_PER_SM", "2")) * self.sm_count)
+        # one-group products of at least this many rows run on pairs of multiprocessors (0: never)
+        self.tc_pair_min_rows = int(os.environ.get("SPITE_TC_PAIR_MIN_ROWS", "256")) or (1 << 30)
         self.skinny_tall_rows = int(os.environ.get("SPITE_SKINNY_TALL_ROWS", "0"))
 
     # ------------------------------------------------------------------ helpers
@@ -172,6 +174,13 @@ class CudaKernels(KernelSet):
                     _check(st, "gather_rows")
                     p = GemmParams.from_buffer_copy(p)
                     p.A = keep.data_ptr()          # rows are in place now; a_rows only indexes the row scale
+                if not grouped and p.M >= self.tc_pair_min_rows:
+                    # a product of many rows on pairs of multiprocessors (tcgen05 cta_group::2)
+                    st = self._lib("gemm_tc_pair").spite_gemm_tc_pair(C.byref(p), self.sm_count // 2, self._stream())
+                    if st != -2:
+                        self._count("gemm_tc_pair", 1)
+                        _check(st, what + " (tcgen05, pairs)")
+                        return
                 st = self._lib("gemm_tc").spite_gemm_tc(C.byref(p), self.sm_count, self._stream())
                 if st != -2:
                     self._count("gemm_tc", 1)
@@ -195,7 +204,7 @@ class CudaKernels(KernelSet):
 
     def gemm_tc_error(self) -> int:
         """Error code left by a tcgen05 block that gave up waiting (0: none); clears it. Synchronises."""
-        return int(self._lib("gemm_tc").spite_gemm_tc_error())
+        return int(self._lib("gemm_tc").spite_gemm_tc_error()) or int(self._lib("gemm_tc_pair").spite_gemm_tc_pair_error())
 
     def linear(self, x, w, out, *, accumulate=False, row_scale=None):
         self._t(x, self.dtype, "x"); self._t(w, self.dtype, "w"); self._t(out, None, "out")

@@ -70,7 +70,7 @@ def test_rms_norm(ks, M, d, eps):
 # ---------------------------------------------------------------------------- matrix products
 @pytest.mark.parametrize("M,N,K", [(1, 40, 48), (5, 1000, 96), (130, 72, 200), (64, 64, 64), (67, 129, 33),
                                    (8, 200, 5120), (64, 96, 2048), (33, 50, 64), (17, 33, 128), (2, 31, 32),
-                                   (128, 128, 64), (256, 384, 512), (300, 200, 136), (1000, 520, 1024)])
+                                   (128, 128, 64), (256, 384, 512), (300, 200, 136), (1000, 520, 1024), (515, 7168, 192), (2048, 264, 320)])
 def test_linear(ks, M, N, K):
     x, w = rnd((M, K), ks.dtype, 4), rnd((N, K), ks.dtype, 5, 0.2)
     r = ref_set(ks.dtype)
@@ -94,7 +94,7 @@ def test_linear(ks, M, N, K):
         assert ks.gemm_tc_error() == 0, "a tensor-core block gave up waiting"
 
 
-@pytest.mark.parametrize("M,F,K", [(3, 24, 48), (70, 100, 96), (8, 40, 512), (40, 17, 96), (64, 72, 64), (129, 256, 192), (700, 136, 320)])
+@pytest.mark.parametrize("M,F,K", [(3, 24, 48), (70, 100, 96), (8, 40, 512), (40, 17, 96), (64, 72, 64), (129, 256, 192), (700, 136, 320), (1100, 1000, 128)])
 def test_linear_swiglu(ks, M, F, K):
     x, w = rnd((M, K), ks.dtype, 8), rnd((2 * F, K), ks.dtype, 9, 0.3)
     scale = torch.rand(M) + 0.5
