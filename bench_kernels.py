@@ -197,6 +197,7 @@ def main(argv=None):
         attention_case("attention_prefill", 1, 512 if args.small else 2048, 512 if args.small else 2048, ("full", 0))
         if not args.small:
             attention_case("attention_prefill", 1, 2048, 8192, ("chunk", 8192))
+            attention_case("attention_prefill", 1, 8192, 131072, ("full", 0))     # a late portion of a long prompt
 
     # ---- the small kernels of a decode step
     if want("small"):

@@ -40,7 +40,7 @@ namespace {
 using namespace tc;
 
 constexpr int BM = 128;                 // rows of one row tile
-constexpr int BN = 64;                  // keys per tile
+constexpr int BN = 64;                  // keys per tile (the softmax reads a score tile with one 64-column load)
 constexpr int ST = 3;                   // stages of the K ring and of the V ring
 constexpr int THREADS = 11 * 32;
 constexpr int TMEM_COLS = 512;
@@ -289,15 +289,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                     if (!ok) break;
                     fence_after();
                     float s[BN];
-                    {
-                        float t[32];
-                        ld32(t, lane_base + sb * BN);
-#pragma unroll
-                        for (int e = 0; e < 32; ++e) s[e] = t[e];
-                        ld32(t, lane_base + sb * BN + 32);
-#pragma unroll
-                        for (int e = 0; e < 32; ++e) s[32 + e] = t[e];
-                    }
+                    ld64(s, lane_base + sb * BN);
                     fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(smem_u32(&gb.s_free[sb]));   // the tensor cores may overwrite this score tile
