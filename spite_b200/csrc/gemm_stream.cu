@@ -1,0 +1,376 @@
+// Matrix product for the few tokens of a decode step, weights streamed through shared memory by TMA:
+//   y[M, N] = epilogue( x[M, K] W[N, K]^T ),  at most 16 rows per group, bfloat16 inputs, float32 sums.
+//
+// With few tokens the product is bound by reading W once from HBM, and what decides the speed is how
+// many bytes a multiprocessor keeps in flight and how quickly the stream starts again after the
+// kernel before.  Here a producer warp keeps a ring of shared-memory stages full: per stage one TMA
+// box of 128 weight rows x 64 k (128-byte swizzle; for SwiGLU 64 gate and 64 up rows) and the
+// matching 64 k of the group's tokens (cp.async, same swizzle).  Eight consumer warps own 16 of the
+// 128 rows each and multiply with mma.sync.m16n8k16 (weights as the 16-row operand from ldmatrix,
+// tokens as the 8 columns), so no sums cross warps.  Registers stay few, and two blocks (of this
+// kernel, or the last of this and the first of the next) share a multiprocessor.
+//
+// Work items are (group with tokens, tile of 128 weight rows, k split); blocks are persistent and
+// take items with a stride of the grid, the ring running on across items.  With k splits the
+// partial tiles go through a float32 scratch in global memory; the block that arrives last at the
+// tile's ticket adds them in the order of the splits, so a sum's order does not depend on timing.
+// A one-group product knows its items without the step's earlier kernels: its producer requests the
+// first weights before griddepcontrol.wait.
+#include "gemm.cuh"
+#include "tcgen05.cuh"
+
+namespace {
+using namespace tc;
+
+constexpr int ROWS = 128, BK = 64;
+constexpr int W_BYTES = ROWS * BK * 2;                  // 16 KiB
+constexpr int CONSUMERS = 8;                            // warps; warp CONSUMERS is the producer
+constexpr int THREADS = (CONSUMERS + 1) * 32;
+constexpr int MAX_STAGES = 12;
+constexpr int MAX_GROUPS = 1024;
+
+__device__ int g_stream_error = 0;
+
+struct Tail {
+    unsigned long long full[MAX_STAGES], empty[MAX_STAGES];
+    int abort_flag, n_active, last;
+    int active[MAX_GROUPS];
+};
+
+__device__ __forceinline__ void mma16816(float (&d)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], unsigned addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x2(unsigned& r0, unsigned& r1, unsigned addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];\n" : "=r"(r0), "=r"(r1) : "r"(addr));
+}
+__device__ __forceinline__ void cp_async16(unsigned dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src) : "memory");
+}
+// The mbarrier gets one arrival when this thread's cp.async copies so far have landed.
+__device__ __forceinline__ void cp_async_arrive(unsigned bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;\n" ::"n"(CONSUMERS * 32) : "memory"); }
+
+struct Item {
+    int group, lo, m;             // group, its first row in the sorted order, its tokens
+    int tile, n0;                 // tile id (group slot x row tiles + row tile) and first output column
+    int split, kb0, kb1;          // k split and its range of 64-wide k blocks
+};
+
+// NT: token columns (8 or 16).  `n_splits` k splits per tile; `scratch` holds tiles x n_splits x NT x 128
+// floats, `tickets` one zeroed int per tile (left zeroed).
+template <int NT, int EPI>
+__global__ void __launch_bounds__(THREADS, 3)
+gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const GemmParams p, const int n_stages,
+                   const int n_splits, float* __restrict__ scratch, int* __restrict__ tickets) {
+    constexpr bool DUAL = (EPI == EPI_SWIGLU);
+    constexpr int COLS = DUAL ? ROWS / 2 : ROWS;                 // output columns of a tile
+    constexpr int X_BYTES = NT * BK * 2;                         // 1 or 2 KiB
+    constexpr int STAGE = W_BYTES + (X_BYTES < 1024 ? 1024 : X_BYTES);
+    constexpr int NB = NT / 8;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    Tail* tail = (Tail*)(smem + (size_t)n_stages * STAGE);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const bool grouped = p.group_offsets != nullptr;
+    const int row_tiles = (p.N + COLS - 1) / COLS;
+    const int num_kb = p.K / BK;
+    const int w_rows = DUAL ? 2 * p.N : p.N;
+    volatile int* abort_flag = &tail->abort_flag;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < n_stages; ++s) { mbar_init(smem_u32(&tail->full[s]), 33); mbar_init(smem_u32(&tail->empty[s]), CONSUMERS); }
+        tail->abort_flag = 0;
+        mbar_init_fence();
+    }
+    // A one-group product's first item is known now: request its first weights before waiting for
+    // the kernels before (weights are written by no kernel of the step).
+    int pre = 0;
+    if (!grouped) {
+        __syncthreads();
+        if (warp == CONSUMERS && lane == 0 && (int)blockIdx.x < row_tiles * n_splits) {
+            const int i = blockIdx.x;
+            const int split = i % n_splits, rt = i / n_splits;
+            const int kb0 = (int)((long long)num_kb * split / n_splits), kb1 = (int)((long long)num_kb * (split + 1) / n_splits);
+            pre = min(n_stages, kb1 - kb0);
+            for (int j = 0; j < pre; ++j) {
+                const unsigned bar = smem_u32(&tail->full[j]), dst = smem_u32(smem + j * STAGE);
+                mbar_expect_tx(bar, W_BYTES);
+                if (DUAL) {
+                    tma_load_2d(dst, &map_w, (kb0 + j) * BK, rt * COLS, bar);
+                    tma_load_2d(dst + W_BYTES / 2, &map_w, (kb0 + j) * BK, p.N + rt * COLS, bar);
+                } else {
+                    tma_load_2d(dst, &map_w, (kb0 + j) * BK, rt * COLS, bar);
+                }
+            }
+        }
+    }
+    pdl_wait();
+    pdl_launch_dependents();
+
+    // groups that have tokens, in group order
+    if (warp == 0) {
+        int n = 0;
+        const int groups = grouped ? p.n_groups : 1;
+        for (int e0 = 0; e0 < groups; e0 += 32) {
+            const int e = e0 + lane;
+            const int m = e < groups ? (grouped ? p.group_offsets[e + 1] - p.group_offsets[e] : p.M) : 0;
+            const unsigned has = __ballot_sync(0xffffffffu, m > 0);
+            if (m > 0) tail->active[n + __popc(has & ((1u << lane) - 1u))] = e;
+            n += __popc(has);
+        }
+        if (lane == 0) tail->n_active = n;
+    }
+    __syncthreads();
+    const int total = tail->n_active * row_tiles * n_splits;
+
+    auto item_at = [&](int i) {
+        Item it;
+        it.split = i % n_splits;
+        const int rt = (i / n_splits) % row_tiles, slot = i / (n_splits * row_tiles);
+        it.group = tail->active[slot];
+        it.lo = grouped ? p.group_offsets[it.group] : 0;
+        it.m = min(NT, (grouped ? p.group_offsets[it.group + 1] : p.M) - it.lo);
+        it.tile = slot * row_tiles + rt;
+        it.n0 = rt * COLS;
+        it.kb0 = (int)((long long)num_kb * it.split / n_splits);
+        it.kb1 = (int)((long long)num_kb * (it.split + 1) / n_splits);
+        return it;
+    };
+
+    if (warp == CONSUMERS) {
+        // ---- producer
+        int s = 0;
+        unsigned ph = 0;
+        int skip_tma = __shfl_sync(0xffffffffu, pre, 0);         // stages whose weights are on the way already
+        bool ok = true;
+        const __nv_bfloat16* X = (const __nv_bfloat16*)p.A;
+        for (int i = blockIdx.x; i < total && ok; i += gridDim.x) {
+            const Item it = item_at(i);
+            // this lane's 16-byte chunks of the token tile: chunk q = lane + 32 j, token q / 8, k chunk q % 8
+            const __nv_bfloat16* src[NT / 4];
+            unsigned off[NT / 4];
+#pragma unroll
+            for (int j = 0; j < NT / 4; ++j) {
+                const int q = lane + 32 * j, t = q >> 3, c = q & 7;
+                const int li = it.lo + min(t, it.m - 1);         // rows past the group's tokens repeat its last one; never stored
+                src[j] = X + (size_t)(p.a_rows ? p.a_rows[li] : li) * p.lda + c * 8;
+                off[j] = W_BYTES + t * 128 + ((c ^ (t & 7)) << 4);
+            }
+            const int wy = it.group * w_rows + it.n0;
+            for (int kb = it.kb0; kb < it.kb1; ++kb, s = (s + 1 == n_stages ? 0 : s + 1), ph ^= (s == 0)) {
+                if (lane == 0) ok = mbar_wait(smem_u32(&tail->empty[s]), ph ^ 1, abort_flag, &g_stream_error, 1);
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) break;
+                const unsigned bar = smem_u32(&tail->full[s]), dst = smem_u32(smem + s * STAGE);
+                if (skip_tma > 0) {
+                    --skip_tma;
+                } else if (lane == 0) {
+                    mbar_expect_tx(bar, W_BYTES);
+                    if (DUAL) {
+                        tma_load_2d(dst, &map_w, kb * BK, wy, bar);
+                        tma_load_2d(dst + W_BYTES / 2, &map_w, kb * BK, wy + p.N, bar);
+                    } else {
+                        tma_load_2d(dst, &map_w, kb * BK, wy, bar);
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < NT / 4; ++j) cp_async16(dst + off[j], src[j] + (size_t)kb * BK);
+                cp_async_arrive(bar);
+            }
+        }
+        asm volatile("cp.async.wait_all;\n" ::: "memory");
+    } else {
+        // ---- consumers: warp w owns rows 16 w .. 16 w + 15 of the tile (SwiGLU: gate rows 8 w .. + 7 and
+        //      the up rows of the same output columns as fragment rows 8 .. 15)
+        const int g = lane >> 2, c = lane & 3;
+        const int mrow = (lane & 7) + ((lane >> 3) & 1) * 8;     // fragment row this lane addresses for ldmatrix
+        const int arow = DUAL ? (mrow < 8 ? 8 * warp + mrow : ROWS / 2 + 8 * warp + mrow - 8) : 16 * warp + mrow;
+        const unsigned a_off = arow * 128, a_swz = arow & 7, a_k = lane >> 4;
+        const int brow = lane & 7;
+        const unsigned b_k = (lane >> 3) & 1;
+        int s = 0;
+        unsigned ph = 0;
+        bool ok = true;
+        for (int i = blockIdx.x; i < total; i += gridDim.x) {
+            const Item it = item_at(i);
+            float acc[NB][4];
+#pragma unroll
+            for (int j = 0; j < NB; ++j)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) acc[j][e] = 0.f;
+            for (int kb = it.kb0; kb < it.kb1; ++kb, s = (s + 1 == n_stages ? 0 : s + 1), ph ^= (s == 0)) {
+                ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&tail->full[s]), ph, abort_flag, &g_stream_error, 2));
+                if (!ok) break;
+                const unsigned wbase = smem_u32(smem + s * STAGE), xbase = wbase + W_BYTES;
+#pragma unroll
+                for (int ks = 0; ks < BK / 16; ++ks) {
+                    unsigned a[4];
+                    ldmatrix_x4(a, wbase + a_off + (((2 * ks + a_k) ^ a_swz) << 4));
+#pragma unroll
+                    for (int j = 0; j < NB; ++j) {
+                        const int t = 8 * j + brow;
+                        unsigned b0, b1;
+                        ldmatrix_x2(b0, b1, xbase + t * 128 + (((2 * ks + b_k) ^ (t & 7)) << 4));
+                        mma16816(acc[j], a, b0, b1);
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&tail->empty[s]));
+            }
+            // A warp whose wait ran out leaves at once only if the epilogue has no block-wide steps; else it
+            // goes through this item's barriers with the others (storing nothing) and all leave together.
+            if (!ok && n_splits == 1) break;
+
+            // ---- epilogue.  This lane holds, for token 8 j + 2 c + (e & 1), fragment rows g (e < 2) and g + 8.
+            auto finish = [&](int t, int col, float v, float v2) {      // output column n0 + col of token t
+                const int n = it.n0 + col;
+                if (t >= it.m || n >= p.N) return;
+                const int li = it.lo + t;
+                const int ar = p.a_rows ? p.a_rows[li] : li;
+                const int crow = p.c_rows ? p.c_rows[li] : li;
+                const float sc = p.row_scale ? p.row_scale[p.scale_by_a_row ? ar : li] : 1.f;
+                const size_t o = (size_t)crow * p.ldc + n;
+                if (EPI == EPI_STORE) ((__nv_bfloat16*)p.C)[o] = __float2bfloat16_rn(v * sc);
+                else if (EPI == EPI_STORE_F32) ((float*)p.C)[o] = v * sc;
+                else if (EPI == EPI_ADD_F32) ((float*)p.C)[o] += v * sc;
+                else ((__nv_bfloat16*)p.C)[o] = __float2bfloat16_rn(silu_f32(v * sc) * (v2 * sc));
+            };
+            if (n_splits == 1) {
+#pragma unroll
+                for (int j = 0; j < NB; ++j)
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const int t = 8 * j + 2 * c + e;
+                        if (DUAL) {
+                            finish(t, 8 * warp + g, acc[j][e], acc[j][e + 2]);
+                        } else {
+                            finish(t, 16 * warp + g, acc[j][e], 0.f);
+                            finish(t, 16 * warp + g + 8, acc[j][e + 2], 0.f);
+                        }
+                    }
+                continue;
+            }
+            // partial tile: scratch[tile][split][token][tile row]; tile rows of the SwiGLU form: 0..63 gate, 64..127 up
+            float* part = scratch + ((size_t)it.tile * n_splits + it.split) * NT * ROWS;
+            const int r_lo = DUAL ? 8 * warp + g : 16 * warp + g;
+            const int r_hi = DUAL ? ROWS / 2 + 8 * warp + g : 16 * warp + g + 8;
+#pragma unroll
+            for (int j = 0; j < NB; ++j)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int t = 8 * j + 2 * c + e;
+                    if (t < it.m && ok) {
+                        __stcg(part + t * ROWS + r_lo, acc[j][e]);
+                        __stcg(part + t * ROWS + r_hi, acc[j][e + 2]);
+                    }
+                }
+            __threadfence();
+            consumer_sync();
+            if (threadIdx.x == 0) {
+                const int arrived = atomicAdd(&tickets[it.tile], 1);
+                tail->last = (arrived == n_splits - 1);
+                if (tail->last) tickets[it.tile] = 0;
+            }
+            consumer_sync();
+            if (tail->last) {
+                __threadfence();
+                const float* all = scratch + (size_t)it.tile * n_splits * NT * ROWS;
+                for (int idx = threadIdx.x; idx < COLS * it.m; idx += CONSUMERS * 32) {
+                    const int col = idx % COLS, t = idx / COLS;
+                    float v = 0.f, v2 = 0.f;
+                    for (int sp = 0; sp < n_splits; ++sp) {
+                        v += __ldcg(all + ((size_t)sp * NT + t) * ROWS + col);
+                        if (DUAL) v2 += __ldcg(all + ((size_t)sp * NT + t) * ROWS + ROWS / 2 + col);
+                    }
+                    finish(t, col, v, v2);
+                }
+            }
+            consumer_sync();                                  // `last` is read before the next item writes it
+            if (*abort_flag) break;                           // the same answer in every warp, after the barrier
+            ok = true;
+        }
+    }
+}
+
+template <int NT, int EPI>
+int launch(const GemmParams& p, int n_blocks, int smem_budget, int n_splits, float* scratch, int* tickets, cudaStream_t st) {
+    constexpr bool DUAL = (EPI == EPI_SWIGLU);
+    constexpr int X_BYTES = NT * BK * 2;
+    constexpr int STAGE = W_BYTES + (X_BYTES < 1024 ? 1024 : X_BYTES);
+    const long long w_rows = (long long)(DUAL ? 2 : 1) * p.N * p.n_groups;
+    CUtensorMap mw;
+    cuuint64_t dims[2] = {(cuuint64_t)p.K, (cuuint64_t)w_rows};
+    cuuint64_t strides[1] = {(cuuint64_t)p.K * 2};
+    cuuint32_t box[2] = {BK, (cuuint32_t)(DUAL ? ROWS / 2 : ROWS)};
+    if (!make_map(&mw, p.W, 2, dims, strides, box)) return SPITE_LAUNCH_FAILED;
+    int n_stages = (smem_budget - (int)sizeof(Tail) - 1024) / STAGE;
+    if (n_stages > MAX_STAGES) n_stages = MAX_STAGES;
+    if (n_stages < 2) return SPITE_BAD_ARG;
+    const size_t smem = (size_t)n_stages * STAGE + sizeof(Tail) + 1024;
+    auto k = gemm_stream_kernel<NT, EPI>;
+    if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||
+        cudaFuncSetAttribute(k, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared) != cudaSuccess)
+        return SPITE_LAUNCH_FAILED;
+    const int cols = DUAL ? ROWS / 2 : ROWS;
+    const long long tiles = (long long)((p.N + cols - 1) / cols) * (p.group_offsets ? (p.n_groups < p.M ? p.n_groups : p.M) : 1) * n_splits;
+    const int grid = (int)(tiles < n_blocks ? tiles : n_blocks);
+    SPITE_LAUNCH(k, grid, THREADS, smem, st, mw, p, n_stages, n_splits, scratch, tickets);
+    return spite_launch_status();
+}
+
+}  // namespace
+
+// `max_rows_per_group` <= 16.  `n_blocks`: resident blocks (two per multiprocessor fit when `smem_budget`,
+// the bytes of shared memory a block may take, is at most about 110 KiB).  `n_splits`: k splits per tile
+// (1: no scratch needed).  `scratch`: groups-with-tokens x row tiles x n_splits x 16 x 128 floats;
+// `tickets`: that many tiles' ints, zero before the first call; calls that share them must not overlap.
+SPITE_API int spite_gemm_stream(const GemmParams* p, int max_rows_per_group, int n_blocks, int smem_budget, int n_splits,
+                                float* scratch, long long scratch_floats, int* tickets, int n_tickets, void* stream) {
+    if (!p || !p->A || !p->W || !p->C) return SPITE_BAD_ARG;
+    if (p->M < 0 || p->N <= 0 || p->K <= 0 || p->lda < p->K || p->ldc < p->N || n_blocks < 1 || n_splits < 1) return SPITE_BAD_ARG;
+    if (p->group_offsets ? p->n_groups < 1 : p->n_groups != 1) return SPITE_BAD_ARG;
+    if (p->epilogue < 0 || p->epilogue > EPI_SWIGLU) return SPITE_BAD_ARG;
+    if (p->K % BK || p->lda % 8 || (((uintptr_t)p->A | (uintptr_t)p->W) & 15)) return SPITE_UNSUPPORTED;
+    if (max_rows_per_group < 1 || max_rows_per_group > 16 || p->n_groups > MAX_GROUPS) return SPITE_UNSUPPORTED;
+    if (p->n_groups > 1 && p->w_group_stride != (long long)(p->epilogue == EPI_SWIGLU ? 2 : 1) * p->N * p->K)
+        return SPITE_UNSUPPORTED;                              // groups must be stacked without gaps
+    if (p->M == 0) return SPITE_OK;
+    if (n_splits > p->K / BK) n_splits = p->K / BK;
+    const int nt = max_rows_per_group <= 8 ? 8 : 16;
+    const int cols = p->epilogue == EPI_SWIGLU ? ROWS / 2 : ROWS;
+    const long long tiles = (long long)((p->N + cols - 1) / cols) * (p->group_offsets ? (p->n_groups < p->M ? p->n_groups : p->M) : 1);
+    if (n_splits > 1) {
+        if (!scratch || !tickets || tiles > n_tickets || tiles * n_splits * nt * ROWS > scratch_floats) return SPITE_BAD_ARG;
+    }
+    cudaStream_t st = (cudaStream_t)stream;
+#define SPITE_STREAM_CASE(E)                                                                                     \
+    case E:                                                                                                      \
+        return nt == 8 ? launch<8, E>(*p, n_blocks, smem_budget, n_splits, scratch, tickets, st)                  \
+                       : launch<16, E>(*p, n_blocks, smem_budget, n_splits, scratch, tickets, st);
+    switch (p->epilogue) {
+        SPITE_STREAM_CASE(EPI_STORE)
+        SPITE_STREAM_CASE(EPI_STORE_F32)
+        SPITE_STREAM_CASE(EPI_ADD_F32)
+        default: return nt == 8 ? launch<8, EPI_SWIGLU>(*p, n_blocks, smem_budget, n_splits, scratch, tickets, st)
+                                : launch<16, EPI_SWIGLU>(*p, n_blocks, smem_budget, n_splits, scratch, tickets, st);
+    }
+#undef SPITE_STREAM_CASE
+}
+
+// Error code recorded by a block that gave up waiting (0: none); reading it clears it.
+// 1: the producer waited for a free stage, 2: a consumer waited for a stage.
+SPITE_API int spite_gemm_stream_error() {
+    int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, g_stream_error, sizeof(int)) != cudaSuccess) return -1;
+    if (v) cudaMemcpyToSymbol(g_stream_error, &zero, sizeof(int));
+    return v;
+}

@@ -97,6 +97,12 @@ class CudaKernels(KernelSet):
         # one-group products of at least this many rows run on pairs of multiprocessors (0: never)
         self.tc_pair_min_rows = int(os.environ.get("SPITE_TC_PAIR_MIN_ROWS", "256")) or (1 << 30)
         self.skinny_tall_rows = int(os.environ.get("SPITE_SKINNY_TALL_ROWS", "0"))
+        # the TMA weight-streaming kernel for decode products: k elements per work item, shared memory per block
+        self.use_stream = os.environ.get("SPITE_NO_STREAM_GEMM", "") == ""
+        self.stream_split_k = int(os.environ.get("SPITE_STREAM_SPLIT_K", "2048"))
+        self.stream_smem = int(os.environ.get("SPITE_STREAM_SMEM", str(110 * 1024)))
+        self.stream_blocks = int(float(os.environ.get("SPITE_STREAM_BLOCKS_PER_SM", "2")) * self.sm_count)
+        self._tickets, self._tickets_n = None, 65536     # arrival counters of the k splits, zero between calls
 
     # ------------------------------------------------------------------ helpers
     def _count(self, library, n=1):
@@ -155,6 +161,12 @@ class CudaKernels(KernelSet):
             # tall matrices (output head), where the TMA pipeline of the tcgen05 kernel streams better
             few = p.M <= self.skinny_max_rows and not (not grouped and p.N >= 65536 and p.M > self.skinny_tall_rows)
             tc_ok = self.use_tcgen05 and p.K % 8 == 0 and p.lda % 8 == 0
+            if few and self.use_stream and p.K % 64 == 0 and max_rows_per_group <= 16:
+                st = self._gemm_stream(p, int(max_rows_per_group), grouped)
+                if st != -2:
+                    self._count("gemm_stream", 1)
+                    _check(st, what + " (streaming)")
+                    return
             if few or (not tc_ok and max_rows_per_group <= 64):
                 st = self._lib("gemm_skinny").spite_gemm_skinny(C.byref(p), int(max_rows_per_group), self.skinny_blocks,
                                                                 self._stream())
@@ -198,13 +210,34 @@ class CudaKernels(KernelSet):
         self._count("gemm_simt", 1)
         _check(st, what)
 
+    def _gemm_stream(self, p, max_rows_per_group, grouped):
+        """The TMA weight-streaming kernel for decode steps: picks the k splits so that the work items
+        are many enough to spread evenly, and lends the scratch for their partial sums."""
+        swiglu = p.epilogue == EPI_SWIGLU
+        cols = 64 if swiglu else 128
+        tiles = -(-p.N // cols) * (min(p.n_groups, p.M) if grouped else 1)
+        blocks = self.stream_blocks
+        splits = 1 if tiles >= 6 * blocks else max(1, min(16, p.K // self.stream_split_k))
+        scratch, n_floats = None, 0
+        if splits > 1:
+            if tiles > self._tickets_n:
+                return -2
+            n_floats = tiles * splits * (8 if max_rows_per_group <= 8 else 16) * 128
+            scratch = torch.empty(n_floats, dtype=torch.float32, device=self.device)
+            if self._tickets is None:
+                self._tickets = torch.zeros(self._tickets_n, dtype=torch.int32, device=self.device)
+        return self._lib("gemm_stream").spite_gemm_stream(
+            C.byref(p), max_rows_per_group, blocks, self.stream_smem, splits, C.c_void_p(_ptr(scratch)),
+            C.c_longlong(n_floats), C.c_void_p(_ptr(self._tickets)), self._tickets_n, self._stream())
+
     def attention_tc_error(self) -> int:
         """Error code left by a tcgen05 attention block that gave up waiting (0: none); clears it. Synchronises."""
         return int(self._lib("attention_tc").spite_attention_tc_error())
 
     def gemm_tc_error(self) -> int:
         """Error code left by a tcgen05 block that gave up waiting (0: none); clears it. Synchronises."""
-        return int(self._lib("gemm_tc").spite_gemm_tc_error()) or int(self._lib("gemm_tc_pair").spite_gemm_tc_pair_error())
+        return (int(self._lib("gemm_tc").spite_gemm_tc_error()) or int(self._lib("gemm_tc_pair").spite_gemm_tc_pair_error())
+                or int(self._lib("gemm_stream").spite_gemm_stream_error()))
 
     def linear(self, x, w, out, *, accumulate=False, row_scale=None):
         self._t(x, self.dtype, "x"); self._t(w, self.dtype, "w"); self._t(out, None, "out")

@@ -130,7 +130,7 @@ def test_sizes_of_the_tcgen05_kernels(tmp_path):
     assert eng.n_pages * 64 < sum(H._round64(len(t)) for t in requests.values())
     H.compare_with_plain(H.run_steps(eng, steps), path, requests, TOL["bfloat16"])
     assert model.kernels.attention_tc_error() == 0 and model.kernels.gemm_tc_error() == 0
-    assert all(by_library[lib] > 0 for lib in ("attention_tc", "attention_rows", "attention_mma", "gemm_skinny"))
+    assert all(by_library[lib] > 0 for lib in ("attention_tc", "attention_rows", "attention_mma", "gemm_stream"))
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

@@ -70,12 +70,16 @@ def test_rms_norm(ks, M, d, eps):
 # ---------------------------------------------------------------------------- matrix products
 @pytest.mark.parametrize("M,N,K", [(1, 40, 48), (5, 1000, 96), (130, 72, 200), (64, 64, 64), (67, 129, 33),
                                    (8, 200, 5120), (64, 96, 2048), (33, 50, 64), (17, 33, 128), (2, 31, 32),
-                                   (128, 128, 64), (256, 384, 512), (300, 200, 136), (1000, 520, 1024), (515, 7168, 192), (2048, 264, 320)])
+                                   (128, 128, 64), (256, 384, 512), (300, 200, 136), (1000, 520, 1024), (515, 7168, 192), (2048, 264, 320),
+                                   (3, 129, 8192), (16, 300, 4096), (1, 40, 64), (9, 1000, 2048)])
 def test_linear(ks, M, N, K):
     x, w = rnd((M, K), ks.dtype, 4), rnd((N, K), ks.dtype, 5, 0.2)
     r = ref_set(ks.dtype)
     out = torch.empty((M, N), dtype=ks.dtype, device=DEV)
+    streamed = ks.launches_by_library["gemm_stream"]
     ks.linear(x.to(DEV), w.to(DEV), out)
+    if ks.dtype == torch.bfloat16 and M <= 16 and K % 64 == 0:
+        assert ks.launches_by_library["gemm_stream"] == streamed + 1     # the TMA weight-streaming kernel took it
     ref = torch.empty((M, N), dtype=torch.float64)
     r.linear(x, w, ref)
     close(out, ref, TOL[ks.dtype], "linear")
@@ -94,7 +98,8 @@ def test_linear(ks, M, N, K):
         assert ks.gemm_tc_error() == 0, "a tensor-core block gave up waiting"
 
 
-@pytest.mark.parametrize("M,F,K", [(3, 24, 48), (70, 100, 96), (8, 40, 512), (40, 17, 96), (64, 72, 64), (129, 256, 192), (700, 136, 320), (1100, 1000, 128)])
+@pytest.mark.parametrize("M,F,K", [(3, 24, 48), (70, 100, 96), (8, 40, 512), (40, 17, 96), (64, 72, 64), (129, 256, 192), (700, 136, 320), (1100, 1000, 128),
+                                   (5, 100, 4096), (16, 72, 6144), (12, 200, 128)])
 def test_linear_swiglu(ks, M, F, K):
     x, w = rnd((M, K), ks.dtype, 8), rnd((2 * F, K), ks.dtype, 9, 0.3)
     scale = torch.rand(M) + 0.5
@@ -106,7 +111,8 @@ def test_linear_swiglu(ks, M, F, K):
 
 
 @pytest.mark.parametrize("M,E,F,K", [(1, 3, 24, 48), (9, 5, 40, 96), (150, 7, 72, 64), (64, 16, 48, 128),
-                                     (60, 3, 24, 64), (8, 128, 16, 32), (1500, 16, 160, 256), (300, 4, 128, 72)])
+                                     (60, 3, 24, 64), (8, 128, 16, 32), (1500, 16, 160, 256), (300, 4, 128, 72),
+                                     (7, 5, 40, 4096), (16, 9, 72, 128), (1, 3, 2048, 64), (8, 16, 100, 6144), (4, 3, 4096, 64)])
 def test_grouped_products(ks, M, E, F, K):
     """Tokens sorted by expert, some experts empty; SwiGLU in, scatter-add out."""
     g = torch.Generator().manual_seed(10)
