@@ -236,13 +236,15 @@ def run_ours(args):
     for r in list(engine.cache.requests):
         engine.finish(r)
 
-    prefill = measure_prefill()
-
     points = {}
     if not args.skip_points:
         for nb in (1, 64):
             ms_b, _, _ = timed_decode(nb, max(4, args.steps // 2), 3)
             points[f"decode_b{nb}"] = round(nb * 1000.0 / ms_b, 1)
+        for r in list(engine.cache.requests):
+            engine.finish(r)
+
+    prefill = measure_prefill()
 
     line = {
         "metric": "decode tok/s (Llama-4-Scout-shaped, batch 8, context 8192)",
