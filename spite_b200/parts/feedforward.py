@@ -7,6 +7,8 @@ input, SwiGLU experts, unweighted sum).
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from ..config.specs import ConfigError
@@ -65,6 +67,8 @@ class MoESigmoidPrescaled(FeedForward):
         self.d, self.E, self.top_k = int(hidden_size), int(num_experts), int(top_k)
         self.f, self.fs = int(expert_size), int(shared_size)
         self.router = self.w_gate_up = self.w_down = self.ws_gate_up = self.ws_down = None
+        self._side = None
+        self.router_beside_shared = os.environ.get("SPITE_NO_SIDE_STREAM", "") == ""
 
     def param_specs(self):
         d, E, f, fs = self.d, self.E, self.f, self.fs
@@ -102,14 +106,40 @@ class MoESigmoidPrescaled(FeedForward):
     def forward(self, x, h, batch):
         k = self.k
         M = x.shape[0]
-        routing = k.moe_route(x, self.router, self.top_k)
+        # The shared expert needs only x, the routed experts need the router's answer first.  On a GPU
+        # the router (two short kernels that leave the memory system idle) runs on a side stream beside
+        # the shared expert's products; both streams meet before the routed experts.  The residual
+        # stream gets the shared expert's output first, then the routed experts', on every path.
+        side = self._side_stream(x) if self.fs else None
+        if side is not None:
+            main = torch.cuda.current_stream(x.device)
+            forked = torch.cuda.Event()
+            forked.record(main)
+            with torch.cuda.stream(side):
+                side.wait_event(forked)
+                routing = k.moe_route(x, self.router, self.top_k)
+                routed = torch.cuda.Event()
+                routed.record(side)
+        else:
+            routing = k.moe_route(x, self.router, self.top_k)
         self.last_routing = routing
+        if self.fs:
+            a = torch.empty((M, self.fs), dtype=x.dtype, device=x.device)
+            k.linear_swiglu(x, self.ws_gate_up, a)
+            k.linear(a, self.ws_down, h, accumulate=True)
+        if side is not None:
+            main.wait_event(routed)
+            for t in (routing.expert_ids, routing.weights, routing.offsets, routing.sorted_rows):
+                t.record_stream(main)                        # made on the side stream, read on this one
         for slot in range(self.top_k):
             a = torch.empty((M, self.f), dtype=x.dtype, device=x.device)
             k.grouped_linear_swiglu(x, self.w_gate_up, routing.sorted_rows[slot], routing.offsets[slot],
                                     routing.weights[slot], a)
             k.grouped_linear_accumulate(a, self.w_down, routing.sorted_rows[slot], routing.offsets[slot], h)
-        if self.fs:
-            a = torch.empty((M, self.fs), dtype=x.dtype, device=x.device)
-            k.linear_swiglu(x, self.ws_gate_up, a)
-            k.linear(a, self.ws_down, h, accumulate=True)
+
+    def _side_stream(self, x):
+        if not x.is_cuda or not self.router_beside_shared:
+            return None
+        if self._side is None:
+            self._side = torch.cuda.Stream(device=x.device)
+        return self._side
