@@ -102,7 +102,7 @@ class CudaKernels(KernelSet):
         self.stream_split_k = int(os.environ.get("SPITE_STREAM_SPLIT_K", "2048"))
         self.stream_smem = int(os.environ.get("SPITE_STREAM_SMEM", str(110 * 1024)))
         self.stream_blocks = int(float(os.environ.get("SPITE_STREAM_BLOCKS_PER_SM", "2")) * self.sm_count)
-        self._tickets, self._tickets_n = None, 65536     # arrival counters of the k splits, zero between calls
+        self._tickets, self._tickets_n = {}, 65536       # arrival counters of the k splits (zero between calls), per stream
 
     # ------------------------------------------------------------------ helpers
     def _count(self, library, n=1):
@@ -224,11 +224,14 @@ class CudaKernels(KernelSet):
                 return -2
             n_floats = tiles * splits * (8 if max_rows_per_group <= 8 else 16) * 128
             scratch = torch.empty(n_floats, dtype=torch.float32, device=self.device)
-            if self._tickets is None:
-                self._tickets = torch.zeros(self._tickets_n, dtype=torch.int32, device=self.device)
+        # the k splits' arrival counters: one set per stream, since calls that share a set must not overlap
+        stream = torch.cuda.current_stream().cuda_stream
+        tickets = self._tickets.get(stream)
+        if tickets is None and splits > 1:
+            tickets = self._tickets[stream] = torch.zeros(self._tickets_n, dtype=torch.int32, device=self.device)
         return self._lib("gemm_stream").spite_gemm_stream(
             C.byref(p), max_rows_per_group, blocks, self.stream_smem, splits, C.c_void_p(_ptr(scratch)),
-            C.c_longlong(n_floats), C.c_void_p(_ptr(self._tickets)), self._tickets_n, self._stream())
+            C.c_longlong(n_floats), C.c_void_p(_ptr(tickets)), self._tickets_n, C.c_void_p(stream))
 
     def attention_tc_error(self) -> int:
         """Error code left by a tcgen05 attention block that gave up waiting (0: none); clears it. Synchronises."""
