@@ -16,6 +16,9 @@
 // tile's ticket adds them in the order of the splits, so a sum's order does not depend on timing.
 // A one-group product knows its items without the step's earlier kernels: its producer requests the
 // first weights before griddepcontrol.wait.
+// (Dealing every block one equal run of k blocks across tile borders was measured too: faster alone,
+// 219 against 248 us for 8 tokens over 7 experts, and no faster in the decode step, where blocks that
+// finish early make room for the next kernel's blocks to start and fetch.)
 #include "gemm.cuh"
 #include "tcgen05.cuh"
 
