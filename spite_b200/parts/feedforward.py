@@ -15,6 +15,9 @@ from ..config.specs import ConfigError
 from .base import FeedForward, ParamSpec, register_feed_forward
 
 
+_SIDE_STREAMS: dict = {}      # one side stream per device, shared by the layers
+
+
 @register_feed_forward("dense_swiglu")
 class DenseSwiGLU(FeedForward):
     """h += down( silu(gate x) * (up x) )          (llama4.rs:257-271)"""
@@ -67,7 +70,6 @@ class MoESigmoidPrescaled(FeedForward):
         self.d, self.E, self.top_k = int(hidden_size), int(num_experts), int(top_k)
         self.f, self.fs = int(expert_size), int(shared_size)
         self.router = self.w_gate_up = self.w_down = self.ws_gate_up = self.ws_down = None
-        self._side = None
         self.router_beside_shared = os.environ.get("SPITE_NO_SIDE_STREAM", "") == ""
 
     def param_specs(self):
@@ -140,6 +142,7 @@ class MoESigmoidPrescaled(FeedForward):
     def _side_stream(self, x):
         if not x.is_cuda or not self.router_beside_shared:
             return None
-        if self._side is None:
-            self._side = torch.cuda.Stream(device=x.device)
-        return self._side
+        side = _SIDE_STREAMS.get(x.device)
+        if side is None:
+            side = _SIDE_STREAMS[x.device] = torch.cuda.Stream(device=x.device)
+        return side
