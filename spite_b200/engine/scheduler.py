@@ -276,11 +276,12 @@ class Scheduler:
         if self._in_flight is not None:
             ahead = self._launch_ahead()
             outputs = self._read(self._in_flight)
-            self._in_flight = ahead
             if ahead is not None:
                 ahead.dead = {r.id for r in ahead.requests if r.state is RequestState.DONE}
-                return outputs
-            if not self.active_count():
+                if len(ahead.dead) == len(ahead.requests):
+                    ahead = None                 # every request of the step launched ahead has just ended: nothing to read
+            self._in_flight = ahead
+            if ahead is not None or not self.active_count():
                 return outputs
         plan = self.plan_step()
         outputs += [StepOutput(r.id, None, True, why) for r, why in plan.ended]

@@ -210,3 +210,35 @@ def test_decoding_ahead_produces_the_same_tokens(model, budget, pages, slots):
         assert ahead_run.finished[i].finish_reason is plain_run.finished[i].finish_reason, i
         assert ahead_emitted[i] == plain_emitted[i] == plain_run.finished[i].output, i
     assert plain_run.finished[1].finish_reason is FinishReason.EOS_TOKEN
+
+
+@pytest.mark.parametrize("seed", range(16))
+def test_decoding_ahead_random_scenarios(model, seed):
+    """Random prompts, limits, stop tokens, budgets and pool sizes: reading the ids one step late never
+    changes what a request produces or why it ends, and every page comes back."""
+    import random
+    rng = random.Random(seed)
+    n_req = rng.randint(2, 6)
+    prompts = [H.random_tokens(512, rng.randint(2, 40), 100 * seed + i) for i in range(n_req)]
+    limits = [rng.randint(1, 14) for _ in range(n_req)]
+    probe = plain_greedy(model, prompts[0], limits[0])
+    eos = [probe[rng.randrange(len(probe))]] if rng.random() < 0.7 else []
+    stops = [tuple(rng.sample(range(512), 3)) if rng.random() < 0.5 else () for _ in range(n_req)]
+    budget, slots = rng.choice([3, 16, 64, 2048]), rng.randint(1, 4)
+    pages = rng.choice([96, 160, 512])
+
+    def run(ahead):
+        s = make(model, max_batch_tokens=budget, cache_tokens=pages, max_requests=slots, eos_token_ids=eos,
+                 decode_ahead=ahead)
+        for i in range(n_req):
+            s.submit(Request(i, prompts[i], greedy(limits[i], stop_token_ids=stops[i])))
+        s.run_until_done(max_steps=2000)
+        assert not s.active_count() and s._in_flight is None
+        s.engine.cache.check_invariants()
+        assert s.engine.cache.free_pages() == [s.engine.n_pages] * 2
+        return s
+
+    a, b = run(False), run(True)
+    for i in range(n_req):
+        assert b.finished[i].output == a.finished[i].output, (seed, i)
+        assert b.finished[i].finish_reason is a.finished[i].finish_reason, (seed, i)
