@@ -91,6 +91,7 @@ class CudaKernels(KernelSet):
         self.use_tcgen05_attention = os.environ.get("SPITE_NO_TCGEN05_ATTENTION", "") == ""
         # fewest tokens of a request in a step that go to the tcgen05 attention kernel (0: one full tile of rows)
         self.attention_tc_min_tokens = int(os.environ.get("SPITE_ATTENTION_TC_MIN_TOKENS", "0"))
+        self.attention_max_splits = int(os.environ.get("SPITE_ATTENTION_MAX_SPLITS", "32"))    # most key splits of decode attention (more cost the merge more than they gain)
         # row counts up to which the weight-streaming kernel is preferred over the tcgen05 one
         self.skinny_max_rows = int(os.environ.get("SPITE_SKINNY_MAX_ROWS", "16"))
         self.skinny_blocks = int(float(os.environ.get("SPITE_SKINNY_BLOCKS_PER_SM", "2")) * self.sm_count)
@@ -389,7 +390,7 @@ class CudaKernels(KernelSet):
                 splits = 1
             else:
                 splits = max(range(1, 5), key=lambda s: (base * s / slots) / -(-base * s // slots))
-            splits = max(1, min(splits, tiles // 8, 128))
+            splits = max(1, min(splits, tiles // 8, self.attention_max_splits))
             o_part = ml_part = None
             if splits > 1:
                 o_part = torch.empty((batch.n_tokens, num_heads, splits, c.head_dim), dtype=torch.float32,
