@@ -19,7 +19,10 @@
 // multicasts its arrival to the pair), `acc_empty` lives in the leader and takes the arrivals
 // of both blocks' epilogue warps.  The SwiGLU form gives the leader the gate rows and the
 // other block the up rows of W.
-// One-group products only (a routed product's groups are too small to fill 256 rows).
+// A grouped product cuts every group into row tiles of up to 256 rows of its own (listed in shared
+// memory by both blocks alike); rows of A are contiguous in group order (gathered beforehand), and
+// `a_rows`, if set, only indexes `row_scale`.  A group's last tile is part-filled (128 rows wasted on
+// average), so it pays only where the groups hold many hundreds of rows.
 // Every wait is bounded (tcgen05.cuh); the blocks of a pair leave together through a cluster
 // barrier, after which each frees its tensor memory.  No TMA multicast is used.
 #include "gemm_tc_epilogue.cuh"
@@ -32,6 +35,7 @@ constexpr int A_BYTES = BM * BK * 2;                     // 16 KiB: this block's
 constexpr int RING_BYTES = 192 * 1024;
 constexpr int ACC_COLS = 256, TMEM_COLS = 512;
 constexpr int THREADS = 192;
+constexpr int MAX_LISTED = 1024;                         // row tiles of a grouped product kept as a list in shared memory
 
 __device__ int g_pair_error = 0;
 
@@ -42,6 +46,12 @@ struct SharedTail {
     unsigned long long acc_empty[2];                     // used in the leader
     unsigned tmem_base;
     int abort_flag;
+    int n_row_tiles;                                     // grouped products: row tiles (of up to 256 rows) that hold rows
+    int rt_group[MAX_LISTED], rt_row0[MAX_LISTED], rt_rows[MAX_LISTED];
+};
+
+struct Tile {
+    int group, row0, rows, n0;                           // rows: of the whole 256-row tile
 };
 
 __device__ __forceinline__ unsigned cluster_rank() {
@@ -91,7 +101,7 @@ __device__ __forceinline__ void tmem_free_pair(unsigned base, unsigned cols) {
 template <int EPI>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-                    const GemmParams p, const int bnh, const int row_tiles, const int total_tiles, const int n_stages) {
+                    const GemmParams p, const int bnh, const int dense_row_tiles, const int col_tiles, const int n_stages) {
     constexpr bool DUAL = (EPI == EPI_SWIGLU);
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -113,12 +123,50 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         tail->abort_flag = 0;
         mbar_init_fence();
     }
+    if (warp == 2 && p.group_offsets) {
+        // the row tiles of all groups in group order, up to 256 rows each: 32 groups at a time, places by a warp scan
+        int base = 0;
+        for (int g0 = 0; g0 < p.n_groups; g0 += 32) {
+            const int g = g0 + lane;
+            int lo = 0, hi = 0;
+            if (g < p.n_groups) { lo = p.group_offsets[g]; hi = p.group_offsets[g + 1]; }
+            const int cnt = hi > lo ? (hi - lo + 2 * BM - 1) / (2 * BM) : 0;
+            int incl = cnt;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int v = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += v;
+            }
+            const int at = base + incl - cnt;
+            for (int i = 0; i < cnt && at + i < MAX_LISTED; ++i) {
+                tail->rt_group[at + i] = g;
+                tail->rt_row0[at + i] = lo + i * 2 * BM;
+                tail->rt_rows[at + i] = min(2 * BM, hi - lo - i * 2 * BM);
+            }
+            base += __shfl_sync(0xffffffffu, incl, 31);
+        }
+        if (lane == 0) tail->n_row_tiles = min(base, MAX_LISTED);
+    }
     __syncthreads();
     if (warp == 1) tmem_alloc_pair(&tail->tmem_base, TMEM_COLS);
     fence_before();
     cluster_sync();                                          // both blocks' barriers exist before either is signalled
     fence_after();
     const unsigned tmem = tail->tmem_base;
+    const int row_tiles = p.group_offsets ? tail->n_row_tiles : dense_row_tiles;
+    const int total_tiles = row_tiles * col_tiles;
+    const int w_rows = DUAL ? 2 * p.N : p.N;
+    auto tile_at = [&](int idx) {
+        Tile t;
+        const int rt = idx % row_tiles;
+        t.n0 = (idx / row_tiles) * cols_per_tile;
+        if (p.group_offsets) {
+            t.group = tail->rt_group[rt]; t.row0 = tail->rt_row0[rt]; t.rows = tail->rt_rows[rt];
+        } else {
+            t.group = 0; t.row0 = rt * 2 * BM; t.rows = min(2 * BM, p.M - t.row0);
+        }
+        return t;
+    };
 
     if (warp == 0) {
         if (lane == 0) {
@@ -127,9 +175,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             unsigned ph = 0;
             bool ok = true;
             for (int idx = pair; idx < total_tiles && ok; idx += n_pairs) {
-                const int row0 = (idx % row_tiles) * 2 * BM + (int)rank * BM;
-                const int n0 = (idx / row_tiles) * cols_per_tile;
-                const int wy = DUAL ? (rank ? p.N + n0 : n0) : n0 + (int)rank * bnh;
+                const Tile t = tile_at(idx);
+                const int row0 = t.row0 + (int)rank * BM;
+                const int wy = t.group * w_rows + (DUAL ? (rank ? p.N + t.n0 : t.n0) : t.n0 + (int)rank * bnh);
                 for (int kb = 0; kb < num_kb; ++kb, ++it, s = (s + 1 == n_stages ? 0 : s + 1), ph ^= (s == 0)) {
                     ok = mbar_wait(smem_u32(&tail->empty[s]), ph ^ 1, abort_flag, &g_pair_error, 1);
                     if (!ok) break;
@@ -176,13 +224,12 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         int lt = 0;
         bool ok = true;
         for (int idx = pair; idx < total_tiles && ok; idx += n_pairs) {
-            const int row0 = (idx % row_tiles) * 2 * BM + (int)rank * BM;
-            const int n0 = (idx / row_tiles) * cols_per_tile;
+            const Tile t = tile_at(idx);
             const int buf = lt & 1;
             ok = mbar_wait(smem_u32(&tail->acc_full[buf]), (lt >> 1) & 1, abort_flag, &g_pair_error, 3);
             if (!ok) break;
             fence_after();
-            drain_accumulator_row<EPI>(p, row0 + r, row0 + r < p.M, n0, cols_per_tile, bnh,
+            drain_accumulator_row<EPI>(p, t.row0 + (int)rank * BM + r, (int)rank * BM + r < t.rows, t.n0, cols_per_tile, bnh,
                                        tmem + buf * ACC_COLS + ((unsigned)(quarter * 32) << 16));
             // this warp has read its lanes of the accumulator: tell the leader
             fence_before();
@@ -227,12 +274,15 @@ int choose_bnh(const GemmParams& p, int row_tiles, int n_pairs) {
 
 template <int EPI>
 int launch(const GemmParams& p, int n_pairs, cudaStream_t st) {
-    const int row_tiles = (p.M + 2 * BM - 1) / (2 * BM);
-    const int bnh = choose_bnh(p, row_tiles, n_pairs);
+    // grouped: an upper bound (every group may end in a part-filled tile); the kernel counts the tiles that hold rows
+    const int row_tiles = (p.M + 2 * BM - 1) / (2 * BM) + (p.group_offsets ? p.n_groups : 0);
+    if (p.group_offsets && row_tiles > MAX_LISTED) return SPITE_UNSUPPORTED;
+    const int bnh = choose_bnh(p, p.group_offsets ? (p.M + 2 * BM - 1) / (2 * BM) + p.n_groups / 2 : row_tiles, n_pairs);
     const int cols = (EPI == EPI_SWIGLU) ? bnh : 2 * bnh;
-    const long long total = (long long)((p.N + cols - 1) / cols) * row_tiles;
+    const int col_tiles = (p.N + cols - 1) / cols;
+    const long long total = (long long)col_tiles * row_tiles;
     if (total > 0x7fffffff) return SPITE_UNSUPPORTED;
-    const long long w_rows = (long long)(EPI == EPI_SWIGLU ? 2 : 1) * p.N;
+    const long long w_rows = (long long)(EPI == EPI_SWIGLU ? 2 : 1) * p.N * p.n_groups;
     CUtensorMap ma, mw;
     if (!make_matrix_map(&ma, p.A, p.M, p.K, p.lda, BM) || !make_matrix_map(&mw, p.W, w_rows, p.K, p.K, bnh))
         return SPITE_LAUNCH_FAILED;
@@ -257,17 +307,19 @@ int launch(const GemmParams& p, int n_pairs, cudaStream_t st) {
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = spite_pdl_enabled() ? 2 : 1;
-    (void)cudaLaunchKernelEx(&cfg, k, ma, mw, p, bnh, row_tiles, (int)total, n_stages);
+    (void)cudaLaunchKernelEx(&cfg, k, ma, mw, p, bnh, row_tiles, col_tiles, n_stages);
     return spite_launch_status();
 }
 
 }  // namespace
 
-// One-group products only.  `n_pairs`: half the number of multiprocessors (one persistent pair of blocks each).
+// `n_pairs`: half the number of multiprocessors (one persistent pair of blocks each).
 SPITE_API int spite_gemm_tc_pair(const GemmParams* p, int n_pairs, void* stream) {
     if (!p || !p->A || !p->W || !p->C) return SPITE_BAD_ARG;
     if (p->M < 0 || p->N <= 0 || p->K <= 0 || p->lda < p->K || p->ldc < p->N || n_pairs < 1) return SPITE_BAD_ARG;
-    if (p->group_offsets || p->n_groups != 1 || p->a_rows) return SPITE_UNSUPPORTED;
+    if (p->group_offsets ? p->n_groups < 1 : p->n_groups != 1) return SPITE_BAD_ARG;
+    if (p->n_groups > 1 && p->w_group_stride != (long long)(p->epilogue == EPI_SWIGLU ? 2 : 1) * p->N * p->K)
+        return SPITE_UNSUPPORTED;                              // groups must be stacked without gaps
     if (p->epilogue < 0 || p->epilogue > EPI_SWIGLU) return SPITE_BAD_ARG;
     // TMA: 16-byte aligned bases and row pitches
     if (p->K % 8 || p->lda % 8 || (((uintptr_t)p->A | (uintptr_t)p->W) & 15)) return SPITE_UNSUPPORTED;

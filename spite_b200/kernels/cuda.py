@@ -97,6 +97,10 @@ class CudaKernels(KernelSet):
         self.skinny_blocks = int(float(os.environ.get("SPITE_SKINNY_BLOCKS_PER_SM", "2")) * self.sm_count)
         # one-group products of at least this many rows run on pairs of multiprocessors (0: never)
         self.tc_pair_min_rows = int(os.environ.get("SPITE_TC_PAIR_MIN_ROWS", "256")) or (1 << 30)
+        # grouped products with at least this many rows per group on average do too (0: never).  Measured at
+        # Scout's expert shapes with 512 rows a group: 1324 against 1340 us (gate/up) and 676 against 682 us
+        # (down): what the pair saves in shared-memory traffic, the part-filled last tile of 256 rows gives back.
+        self.tc_pair_min_group_rows = int(os.environ.get("SPITE_TC_PAIR_MIN_GROUP_ROWS", "512")) or (1 << 30)
         self.skinny_tall_rows = int(os.environ.get("SPITE_SKINNY_TALL_ROWS", "0"))
         # the TMA weight-streaming kernel for decode products: k elements per work item, shared memory per block
         self.use_stream = os.environ.get("SPITE_NO_STREAM_GEMM", "") == ""
@@ -189,8 +193,8 @@ class CudaKernels(KernelSet):
                     _check(st, "gather_rows")
                     p = GemmParams.from_buffer_copy(p)
                     p.A = keep.data_ptr()          # rows are in place now; a_rows only indexes the row scale
-                if not grouped and p.M >= self.tc_pair_min_rows:
-                    # a product of many rows on pairs of multiprocessors (tcgen05 cta_group::2)
+                if p.M >= (self.tc_pair_min_group_rows * p.n_groups if grouped else self.tc_pair_min_rows):
+                    # a product of many rows (per group) on pairs of multiprocessors (tcgen05 cta_group::2)
                     st = self._lib("gemm_tc_pair").spite_gemm_tc_pair(C.byref(p), self.sm_count // 2, self._stream())
                     if st != -2:
                         self._count("gemm_tc_pair", 1)

@@ -112,7 +112,8 @@ def test_linear_swiglu(ks, M, F, K):
 
 @pytest.mark.parametrize("M,E,F,K", [(1, 3, 24, 48), (9, 5, 40, 96), (150, 7, 72, 64), (64, 16, 48, 128),
                                      (60, 3, 24, 64), (8, 128, 16, 32), (1500, 16, 160, 256), (300, 4, 128, 72),
-                                     (7, 5, 40, 4096), (16, 9, 72, 128), (1, 3, 2048, 64), (8, 16, 100, 6144), (4, 3, 4096, 64)])
+                                     (7, 5, 40, 4096), (16, 9, 72, 128), (1, 3, 2048, 64), (8, 16, 100, 6144), (4, 3, 4096, 64),
+                                     (1700, 3, 160, 256), (2100, 4, 72, 64), (18000, 35, 48, 64)])
 def test_grouped_products(ks, M, E, F, K):
     """Tokens sorted by expert, some experts empty; SwiGLU in, scatter-add out."""
     g = torch.Generator().manual_seed(10)
