@@ -11,13 +11,17 @@
 //              three stages each;
 //   warps 1-2  warp 1 allocates tensor memory (per row tile two score tiles of 64 columns and
 //              the output tile of head-size columns); one lane of each issues, for its row
-//              tile,  S = Q K^T  (128 x 64 x head size) and  O += P V  (128 x head size x 64; V
-//              is used as it lies in the cache, as an MN-major operand), two score tiles ahead
-//              of the softmax;
+//              tile,  S = Q K^T  (128 x 64 x head size) and  O += P V  (128 x head size x 64; P
+//              is read from tensor memory, V is used as it lies in the cache, as an MN-major
+//              operand), two score tiles ahead of the softmax;
 //   warps 3-10 four warps per row tile, one thread per row: read a score tile with tcgen05.ld,
 //              scale and mask it, keep the running maximum and sum in float32, write P as
-//              bfloat16 into shared memory in the K-major operand layout, and at the end divide
-//              the output by the sum.
+//              bfloat16 pairs over the first 32 columns of the score tile it came from
+//              (tcgen05.st), and at the end divide the output by the sum.
+// P never passes through shared memory: the tensor cores' operand reads from shared memory
+// (q and the K tile for the scores, the V tile for the output) are what bounds the kernel, and P
+// through shared memory would add a third to them.  A score tile's columns are written again
+// (scores of the tile after next) only after the product that read P from them has completed.
 // While one row tile's threads compute a softmax, the tensor cores work on the other tile's
 // products.  (A kernel that allocates tensor memory gets one block per multiprocessor, so the
 // overlap has to come from within the block.)  Blocks are persistent, one per multiprocessor:
@@ -41,7 +45,7 @@ using namespace tc;
 
 constexpr int BM = 128;                 // rows of one row tile
 constexpr int BN = 64;                  // keys per tile (the softmax reads a score tile with one 64-column load)
-constexpr int ST = 3;                   // stages of the K ring and of the V ring
+constexpr int ST = 4;                   // stages of the K ring and of the V ring
 constexpr int THREADS = 11 * 32;
 constexpr int TMEM_COLS = 512;
 constexpr int GROUP_COLS = 256;         // tensor-memory columns of one row tile: S0, S1 (64 each), O
@@ -51,7 +55,7 @@ constexpr float LOG2E = 1.4426950408889634f;
 __device__ int g_attn_tc_error = 0;
 
 struct GroupBarriers {
-    unsigned long long s_full[2], s_free[2], p_ready, pv_done;
+    unsigned long long s_full[2], p_ready, pv_done, exp_done;
 };
 struct Barriers {
     unsigned long long q_full, k_full[ST], k_empty[ST], v_full[ST], v_empty[ST];
@@ -80,8 +84,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     constexpr int HD = 64 * NKB;
     constexpr int Q_BYTES = NKB * BM * 128;              // q of one row tile
     constexpr int KT_BYTES = NKB * BN * 128;             // one K tile, one V tile
-    constexpr int P_BYTES = BM * 128;
-    extern __shared__ __align__(1024) unsigned char smem[];   // [Q0][Q1][K ring][V ring][P0][P1], each 1024-byte aligned
+    extern __shared__ __align__(1024) unsigned char smem[];   // [Q0][Q1][K ring][V ring], each 1024-byte aligned
     __shared__ Barriers bars;
     pdl_wait();
     pdl_launch_dependents();
@@ -93,7 +96,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     unsigned char* q_s = smem;
     unsigned char* k_s = q_s + 2 * Q_BYTES;
     unsigned char* v_s = k_s + ST * KT_BYTES;
-    unsigned char* p_s = v_s + ST * KT_BYTES;
     volatile int* abort_flag = &bars.abort_flag;
 
     auto init_barriers = [&](bool renew) {
@@ -107,9 +109,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             one(&bars.v_full[s], 1); one(&bars.v_empty[s], 2);
         }
         for (int g = 0; g < 2; ++g) {
-            for (int s = 0; s < 2; ++s) { one(&bars.g[g].s_full[s], 1); one(&bars.g[g].s_free[s], 4); }   // one arrival per softmax warp
-            one(&bars.g[g].p_ready, 4);
+            for (int s = 0; s < 2; ++s) one(&bars.g[g].s_full[s], 1);
+            one(&bars.g[g].p_ready, 4);                            // one arrival per softmax warp
             one(&bars.g[g].pv_done, 1);
+            one(&bars.g[g].exp_done, 4);
         }
         mbar_init_fence();
     };
@@ -216,9 +219,17 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 last = (p_last - k_begin) / BN;
             }
             const int n_own = last - first + 1;
+            // own key tiles of the other row tile (the two take turns at the exponentials)
+            int n_other = 0;
+            {
+                const int og = g ^ 1, otg0 = t0 + og * tpt, ontg = max(0, min(tpt, nt - og * tpt));
+                if (ontg > 0) {
+                    const int op_first = b.positions[otg0], op_last = b.positions[otg0 + ontg - 1];
+                    n_other = (op_last - k_begin) / BN - (window_lowest(p.window_kind, p.window_size, op_first) / BN * BN - k_begin) / BN + 1;
+                }
+            }
             const unsigned tmem_g = tmem + g * GROUP_COLS;
             unsigned char* q_g = q_s + g * Q_BYTES;
-            unsigned char* p_g = p_s + g * P_BYTES;
 
             if (warp < 3) {
                 if (lane == 0) {
@@ -236,11 +247,12 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                         mbar_arrive(smem_u32(&bars.v_empty[s]));
                         return true;
                     };
-                    // scores of own tile li (key tile first + li) into score buffer li & 1
+                    // scores of own tile li (key tile first + li) into score buffer li & 1, whose columns held
+                    // P of tile li - 2: the product that read it must have completed
                     auto issue_scores = [&](int li) {
                         const int i = first + li, s = i % ST, sb = li & 1;
                         if (!mbar_wait(smem_u32(&bars.k_full[s]), (i / ST) & 1, abort_flag, &g_attn_tc_error, 2)) return false;
-                        if (!mbar_wait(smem_u32(&gb.s_free[sb]), ((li >> 1) & 1) ^ 1, abort_flag, &g_attn_tc_error, 2)) return false;
+                        if (li >= 2 && !mbar_wait(smem_u32(&gb.pv_done), li & 1, abort_flag, &g_attn_tc_error, 2)) return false;
                         fence_after();
                         const unsigned qa = smem_u32(q_g), ka = smem_u32(k_s + s * KT_BYTES);
 #pragma unroll
@@ -260,11 +272,11 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                              mbar_wait(smem_u32(&bars.v_full[s]), (i / ST) & 1, abort_flag, &g_attn_tc_error, 2);
                         if (!ok) break;
                         fence_after();
-                        const unsigned pa = smem_u32(p_g), va = smem_u32(v_s + s * KT_BYTES);
+                        const unsigned va = smem_u32(v_s + s * KT_BYTES);
 #pragma unroll
                         for (int ks = 0; ks < BN / 16; ++ks)
-                            mma(tmem_g + 2 * BN, smem_desc_k_major(pa + ks * 32), smem_desc(va + ks * 16 * 128, BN * 128, 1024),
-                                idesc_pv, (li > 0 || ks > 0) ? 1u : 0u);
+                            mma_a_tmem(tmem_g + 2 * BN, tmem_g + (li & 1) * BN + ks * 8, smem_desc(va + ks * 16 * 128, BN * 128, 1024),
+                                       idesc_pv, (li > 0 || ks > 0) ? 1u : 0u);
                         commit(smem_u32(&gb.pv_done));
                         commit(smem_u32(&bars.v_empty[s]));
                         if (li + 2 < n_own) ok = issue_scores(li + 2);
@@ -290,9 +302,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                     fence_after();
                     float s[BN];
                     ld64(s, lane_base + sb * BN);
-                    fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(smem_u32(&gb.s_free[sb]));   // the tensor cores may overwrite this score tile
                     const int j0 = k_begin + (first + li) * BN;
                     const bool open = j0 >= lo_last && j0 + BN - 1 <= p_first;   // every key visible to every row with a token
                     // maximum of the raw scores (the scale is positive); four running values shorten the chain
@@ -311,6 +320,17 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                     float corr = 1.f;
                     if (need) { corr = exp2f(m_ref - mx); l *= corr; m_ref = mx; }
                     const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref;
+                    // The two row tiles take turns at the exponentials (tile li of the first, tile li of the
+                    // second, tile li + 1 of the first, ...): the special-function units serve one at full rate
+                    // while the tensor cores work for the other, instead of both halves of the block
+                    // computing and then both waiting.
+                    {
+                        const int oli = g == 0 ? li - 1 : li;             // the other row tile's turn before this one
+                        if (oli >= 0 && oli < n_other) {
+                            ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.g[g ^ 1].exp_done), oli & 1, abort_flag, &g_attn_tc_error, 3));
+                            if (!ok) break;
+                        }
+                    }
                     unsigned packed[BN / 2];
                     float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -319,29 +339,25 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                         sum4[(e >> 1) & 3] += a + bb;
                         packed[e / 2] = pack_bf16(a, bb);
                     }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&gb.exp_done));
                     const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
                     l += sum;
-                    if (li > 0) {
-                        // the product of the tile before must have read P and left O before either changes
+                    if (li > 0 && __any_sync(0xffffffffu, need)) {
+                        // the product of the tile before must have left O before its rows are rescaled
                         ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&gb.pv_done), (li - 1) & 1, abort_flag, &g_attn_tc_error, 3));
                         if (!ok) break;
                         fence_after();
-                        if (__any_sync(0xffffffffu, need)) {
 #pragma unroll 1
-                            for (int c0 = 0; c0 < HD; c0 += 32) {
-                                float o[32];
-                                ld32(o, lane_base + 2 * BN + c0);
+                        for (int c0 = 0; c0 < HD; c0 += 32) {
+                            float o[32];
+                            ld32(o, lane_base + 2 * BN + c0);
 #pragma unroll
-                                for (int e = 0; e < 32; ++e) o[e] *= corr;
-                                st32(lane_base + 2 * BN + c0, o);
-                            }
+                            for (int e = 0; e < 32; ++e) o[e] *= corr;
+                            st32(lane_base + 2 * BN + c0, o);
                         }
                     }
-#pragma unroll
-                    for (int ch = 0; ch < 8; ++ch)
-                        *(uint4*)(p_g + r * 128 + ((ch ^ (r & 7)) << 4)) =
-                            make_uint4(packed[4 * ch], packed[4 * ch + 1], packed[4 * ch + 2], packed[4 * ch + 3]);
-                    fence_proxy_async();
+                    st32(lane_base + sb * BN, packed);              // P over the first half of the score tile just read
                     fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(smem_u32(&gb.p_ready));
@@ -400,7 +416,7 @@ int launch(const AttentionParams& p, const StepTokens& b, const PagedCache& c, c
         if (!make_map(&mk, c.kv, 2, dims, strides, box)) return SPITE_LAUNCH_FAILED;
         if (!make_map(&mv, (const __nv_bfloat16*)c.kv + c.v_offset, 2, dims, strides, box)) return SPITE_LAUNCH_FAILED;
     }
-    const size_t smem = 2 * (size_t)NKB * BM * 128 + 2 * ST * (size_t)NKB * BN * 128 + 2 * (size_t)BM * 128;
+    const size_t smem = 2 * (size_t)NKB * BM * 128 + 2 * ST * (size_t)NKB * BN * 128;
     auto k = attn_tc_kernel<NKB>;
     if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
         return SPITE_LAUNCH_FAILED;

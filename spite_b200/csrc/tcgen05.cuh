@@ -79,6 +79,14 @@ __device__ __forceinline__ void mma(unsigned d_tmem, unsigned long long a_desc, 
                  "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
                  ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
+// The same product with the A operand in tensor memory: row i of A in lane i, two consecutive k
+// elements of 16 bits in one 32-bit column (the even k in the low half), so 16 k take 8 columns.
+__device__ __forceinline__ void mma_a_tmem(unsigned d_tmem, unsigned a_tmem, unsigned long long b_desc,
+                                           unsigned idesc, unsigned accumulate) {
+    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
+                 ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
 // Tensor-memory allocation of `cols` columns (a power of two, 32..512) by one whole warp; the
 // base address lands in *slot (shared memory).
 __device__ __forceinline__ void tmem_alloc(unsigned* slot, unsigned cols) {
@@ -124,6 +132,19 @@ __device__ __forceinline__ void ld64(float (&v)[64], unsigned taddr) {
     asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 #pragma unroll
     for (int i = 0; i < 64; ++i) v[i] = __uint_as_float(r[i]);
+}
+// 32 consecutive 32-bit columns of this thread's lane, written and waited for.
+__device__ __forceinline__ void st32(unsigned taddr, const unsigned (&v)[32]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+                 "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+                 "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n"
+                 ::"r"(taddr),
+                   "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+                   "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]),
+                   "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]),
+                   "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+                 : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
 }
 __device__ __forceinline__ void st32(unsigned taddr, const float (&v)[32]) {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
