@@ -59,7 +59,7 @@ class ClockSampler:
     def __enter__(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.Q}",
-                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                          "--format=csv,noheader,nounits", "-lms", "50"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._pump, daemon=True).start()
         except OSError:
@@ -194,11 +194,17 @@ def run_ours(args):
     clocks = ClockSampler()
     ms_step, launches, _ = timed_decode(B, args.steps, args.warmup, clocks)
     value = B * 1000.0 / ms_step
-    # experts the batch's tokens use, layer by layer, in the last step
-    distinct = []
-    for blk in model.blocks:
-        r = getattr(blk.ffn, "last_routing", None)
-        distinct.append(int(torch.unique(r.expert_ids).numel()) if r is not None else 0)
+    # experts the batch's tokens use, layer by layer: the mean over a few more (untimed) steps of the same kind
+    probe = 8
+    occupy(B, ctx - probe - 1)
+    ptoks = torch.randint(0, vocab, (probe, B), generator=g).tolist()
+    distinct = [0.0] * len(model.blocks)
+    for i in range(probe):
+        engine.step([StepEntry(r, [ptoks[i][r]], [0]) for r in range(B)])
+        for li, blk in enumerate(model.blocks):
+            r = getattr(blk.ffn, "last_routing", None)
+            if r is not None:
+                distinct[li] += torch.unique(r.expert_ids).numel() / probe
     end_ctx = ctx - 1
     nbytes = decode_bytes(model, engine, [end_ctx] * B, distinct)
     achieved = nbytes / (ms_step * 1e-3) / 1e9
@@ -290,7 +296,7 @@ def run_reference(args):
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=16)
+    ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--layers", type=int, default=FULL_LAYERS)

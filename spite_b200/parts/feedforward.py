@@ -97,10 +97,10 @@ class MoESigmoidPrescaled(FeedForward):
             n += self.ws_gate_up.numel() + self.ws_down.numel()
         return n * self.w_down.element_size() + self.router.numel() * 4
 
-    def active_weight_bytes(self, n_distinct_experts: int) -> int:
-        """Bytes a step reads when its tokens use `n_distinct_experts` experts."""
+    def active_weight_bytes(self, n_distinct_experts: float) -> int:
+        """Bytes a step reads when its tokens use `n_distinct_experts` experts (a mean over steps may be fractional)."""
         per = (self.w_gate_up.shape[1] * self.d + self.d * self.f) * self.w_down.element_size()
-        n = per * n_distinct_experts + self.router.numel() * 4
+        n = int(per * n_distinct_experts) + self.router.numel() * 4
         if self.fs:
             n += (self.ws_gate_up.numel() + self.ws_down.numel()) * self.w_down.element_size()
         return n
