@@ -343,18 +343,22 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                     if (lane == 0) mbar_arrive(smem_u32(&gb.exp_done));
                     const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
                     l += sum;
-                    if (li > 0 && __any_sync(0xffffffffu, need)) {
-                        // the product of the tile before must have left O before its rows are rescaled
+                    if (li > 0) {
+                        // The product of the tile before must have left O before its rows are rescaled.  The wait is
+                        // made for every tile, needed or not: a wait by parity is only right while the waiter is
+                        // at most one phase behind the barrier.
                         ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&gb.pv_done), (li - 1) & 1, abort_flag, &g_attn_tc_error, 3));
                         if (!ok) break;
-                        fence_after();
+                        if (__any_sync(0xffffffffu, need)) {
+                            fence_after();
 #pragma unroll 1
-                        for (int c0 = 0; c0 < HD; c0 += 32) {
-                            float o[32];
-                            ld32(o, lane_base + 2 * BN + c0);
+                            for (int c0 = 0; c0 < HD; c0 += 32) {
+                                float o[32];
+                                ld32(o, lane_base + 2 * BN + c0);
 #pragma unroll
-                            for (int e = 0; e < 32; ++e) o[e] *= corr;
-                            st32(lane_base + 2 * BN + c0, o);
+                                for (int e = 0; e < 32; ++e) o[e] *= corr;
+                                st32(lane_base + 2 * BN + c0, o);
+                            }
                         }
                     }
                     st32(lane_base + sb * BN, packed);              // P over the first half of the score tile just read
