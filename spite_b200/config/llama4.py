@@ -40,7 +40,7 @@ def _need(d, key):
     return d[key]
 
 
-@register_architecture("Llama4ForCausalLM", "Llama4ForConditionalGeneration")
+@register_architecture("Llama4ForCausalLM", "Llama4ForConditionalGeneration", model_types=("llama4_text", "llama4"))
 @dataclass(frozen=True)
 class Llama4Config:
     vocab_size: int

@@ -14,13 +14,16 @@ from pathlib import Path
 from .specs import ConfigError
 
 _ARCHITECTURES: dict[str, type] = {}
+_MODEL_TYPES: dict[str, str] = {}       # config.json `model_type` -> architecture name, for files without `architectures`
 
 
-def register_architecture(*names: str):
-    """Class decorator: `@register_architecture("FooForCausalLM")`."""
+def register_architecture(*names: str, model_types: tuple = ()):
+    """Class decorator: `@register_architecture("FooForCausalLM", model_types=("foo",))`."""
     def deco(cls):
         for n in names:
             _ARCHITECTURES[n] = cls
+        for t in model_types:
+            _MODEL_TYPES[t] = names[0]
         return cls
     return deco
 
@@ -39,8 +42,14 @@ def config_class_for(name: str):
 
 def config_from_dict(d: dict):
     archs = d.get("architectures")
+    if isinstance(archs, str):
+        archs = [archs]
     if not archs or not isinstance(archs, (list, tuple)):
-        raise ConfigError("config.json has no `architectures` list")
+        name = _MODEL_TYPES.get(d.get("model_type"))
+        if name is None:
+            raise ConfigError("config.json has no `architectures` list (and no known `model_type`); known architectures: "
+                              + (", ".join(known_architectures()) or "(none)"))
+        return config_class_for(name).from_dict(d)
     return config_class_for(archs[0]).from_dict(d)
 
 

@@ -97,6 +97,13 @@ def test_registry_accepts_another_architecture():
     assert config_from_dict({"architectures": ["ToyForTests"], "n": 3}) == ("toy", 3)
 
 
+def test_model_type_stands_in_for_a_missing_architectures_list():
+    d = {k: v for k, v in H.CONFIG_A.items() if k != "architectures"}
+    assert config_from_dict(dict(d, model_type="llama4_text")) == Llama4Config.from_dict(H.CONFIG_A)
+    with pytest.raises(ConfigError, match="architectures"):
+        config_from_dict(dict(d, model_type="something_else"))
+
+
 def test_plan_validation_of_the_run_order():
     from dataclasses import replace
     from spite_b200.config import LayerCall
