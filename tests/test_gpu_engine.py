@@ -178,3 +178,45 @@ def test_trace_run_program(folder, dtype, tmp_path):
                 row += 1
             pos[e["id"]] = pos.get(e["id"], 0) + len(e["tokens"])
     H.compare_with_plain(results, path, reqs, TOL[dtype])
+
+
+def test_trace_run_step_by_step(folder, tmp_path):
+    """`bin/trace_run` driven as a caller that waits for every `done`: a request with an integer id, steps in
+    which nothing is wanted, a request that sits a step out, a step that only ends a request, the end of an
+    unknown request, wanted places out of order, step numbers with gaps."""
+    path, name = folder
+    vocab = json.loads((Path(path) / "config.json").read_text())["vocab_size"]
+    a, b, c = H.random_tokens(vocab, 70, 1), H.random_tokens(vocab, 40, 2), H.random_tokens(vocab, 9, 3)
+    steps = [
+        {"step": 0, "entries": [{"id": 1, "tokens": a[:33], "want": []}], "end": []},
+        {"step": 1, "entries": [{"id": 1, "tokens": a[33:35], "want": [1]},
+                                {"id": "b", "tokens": b[:2], "want": [0, 1]}], "end": []},
+        {"step": 2, "entries": [{"id": "b", "tokens": b[2:40], "want": [37]}], "end": []},
+        {"step": 3, "entries": [], "end": ["b"]},
+        {"step": 4, "entries": [{"id": 1, "tokens": a[35:36], "want": [0]},
+                                {"id": "c", "tokens": c, "want": [8, 0]}], "end": ["c", "nobody"]},
+        {"step": 7, "entries": [{"id": 1, "tokens": a[36:70], "want": [33]}], "end": [1]},
+    ]
+    out = tmp_path / "out"
+    proc = subprocess.Popen(
+        [sys.executable, str(ROOT / "bin" / "trace_run"), "--model", str(path), "--dtype", "float32",
+         "--out", str(out), "--max-tokens", "192"],
+        stdin=subprocess.PIPE, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
+    try:
+        for s in steps:
+            proc.stdin.write(json.dumps(s) + "\n")
+            proc.stdin.flush()
+            assert proc.stdout.readline().strip() == f"done {s['step']}"
+        proc.stdin.close()
+        assert proc.wait(timeout=120) == 0
+    finally:
+        if proc.poll() is None:
+            proc.kill()
+    assert sorted(p.name for p in out.iterdir()) == ["1.f32", "2.f32", "4.f32", "7.f32"]
+    refs = {"a": H.plain_logits(path, a), "b": H.plain_logits(path, b), "c": H.plain_logits(path, c)}
+    wanted = {1: [("a", 34), ("b", 0), ("b", 1)], 2: [("b", 39)], 4: [("a", 35), ("c", 8), ("c", 0)], 7: [("a", 69)]}
+    for step, rows in wanted.items():
+        data = np.fromfile(out / f"{step}.f32", dtype="<f4").reshape(len(rows), vocab)
+        for i, (r, p) in enumerate(rows):
+            err = float((torch.from_numpy(data[i].copy()) - refs[r][p]).abs().max()) / float(refs[r].abs().max())
+            assert err <= TOL["float32"], f"step {step}, row {i}: error {err:.3e}"
