@@ -219,13 +219,15 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 last = (p_last - k_begin) / BN;
             }
             const int n_own = last - first + 1;
-            // own key tiles of the other row tile (the two take turns at the exponentials)
-            int n_other = 0;
+            // the key tiles that both row tiles own, [shared_lo, shared_hi] among the block's: there the two take
+            // turns at the exponentials
+            int shared_lo = 0, shared_hi = -1;
             {
                 const int og = g ^ 1, otg0 = t0 + og * tpt, ontg = max(0, min(tpt, nt - og * tpt));
-                if (ontg > 0) {
+                if (ontg > 0 && ntg > 0) {
                     const int op_first = b.positions[otg0], op_last = b.positions[otg0 + ontg - 1];
-                    n_other = (op_last - k_begin) / BN - (window_lowest(p.window_kind, p.window_size, op_first) / BN * BN - k_begin) / BN + 1;
+                    shared_lo = max(first, (window_lowest(p.window_kind, p.window_size, op_first) / BN * BN - k_begin) / BN);
+                    shared_hi = min(last, (op_last - k_begin) / BN);
                 }
             }
             const unsigned tmem_g = tmem + g * GROUP_COLS;
@@ -320,16 +322,17 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                     float corr = 1.f;
                     if (need) { corr = exp2f(m_ref - mx); l *= corr; m_ref = mx; }
                     const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref;
-                    // The two row tiles take turns at the exponentials (tile li of the first, tile li of the
-                    // second, tile li + 1 of the first, ...): the special-function units serve one at full rate
-                    // while the tensor cores work for the other, instead of both halves of the block
-                    // computing and then both waiting.
-                    {
-                        const int oli = g == 0 ? li - 1 : li;             // the other row tile's turn before this one
-                        if (oli >= 0 && oli < n_other) {
-                            ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.g[g ^ 1].exp_done), oli & 1, abort_flag, &g_attn_tc_error, 3));
-                            if (!ok) break;
-                        }
+                    // Over the key tiles that both own, the two row tiles take turns at the exponentials (key tile i
+                    // of the first row tile, key tile i of the second, key tile i + 1 of the first, ...): the
+                    // special-function units serve one at full rate while the tensor cores work for the other,
+                    // instead of both halves of the block computing and then both waiting.  Both count their
+                    // turns from the first shared key tile, so each is at most one phase behind the other's barrier.
+                    const int turn = first + li - shared_lo;
+                    const bool takes_turns = turn >= 0 && first + li <= shared_hi;
+                    if (takes_turns && (g == 1 || turn > 0)) {
+                        const int before = g == 0 ? turn - 1 : turn;      // the other row tile's turn before this one
+                        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.g[g ^ 1].exp_done), before & 1, abort_flag, &g_attn_tc_error, 3));
+                        if (!ok) break;
                     }
                     unsigned packed[BN / 2];
                     float sum4[4] = {0.f, 0.f, 0.f, 0.f};
@@ -340,7 +343,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                         packed[e / 2] = pack_bf16(a, bb);
                     }
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(smem_u32(&gb.exp_done));
+                    if (takes_turns && lane == 0) mbar_arrive(smem_u32(&gb.exp_done));
                     const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
                     l += sum;
                     if (li > 0) {

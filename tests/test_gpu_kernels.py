@@ -255,16 +255,17 @@ def dense_attention_reference(q, k_all, v_all, specs, nq, nkv, win, scale):
 @pytest.mark.parametrize("nq,nkv,hd,window,P", [
     (10, 2, 128, ("full", 0), 64), (8, 8, 128, ("chunk", 128), 64), (6, 1, 64, ("chunk", 96), 64),
     (16, 1, 128, ("sliding", 100), 128), (40, 8, 128, ("chunk", 256), 64), (3, 3, 64, ("full", 0), 128),
-    (9, 3, 64, ("chunk", 300), 64), (48, 3, 64, ("chunk", 300), 64)])
+    (9, 3, 64, ("chunk", 300), 64), (48, 3, 64, ("chunk", 300), 64), (40, 8, 128, ("chunk", 425), 64)])
 def test_paged_attention_tcgen05(nq, nkv, hd, window, P):
     """Prompt portions that go to the tcgen05 kernel: several 128-row tiles per request, portions that
     start deep in a context, windows that end inside a 64-key tile, pages behind the window given back,
-    and a window's edge several key tiles into a row tile's keys (some of its rows then start late and
-    the output is rescaled in the middle of the walk)."""
+    a window's edge several key tiles into a row tile's keys (some of its rows then start late and the
+    output is rescaled in the middle of the walk), and a block whose second row tile starts at a window's
+    edge more key tiles on than the ring holds (tokens 400-424 and 425-449 with chunks of 425)."""
     from spite_b200.kernels.cuda import CudaKernels
     ks = CudaKernels(torch.bfloat16, DEV)
     win = Window(*window)
-    specs = [(0, 650 if window[1] == 300 else 300), (200, 130), (1000, 64), (0, 1), (517, 40)]
+    specs = [(0, 650 if window[1] in (300, 425) else 300), (200, 130), (1000, 64), (0, 1), (517, 40)]
     n_pages = sum(-(-(s + n) // P) for s, n in specs) + 5
     batch, tables = make_batch(specs, P, n_pages, 40, DEV)
     M = batch.n_tokens
