@@ -36,8 +36,14 @@ __device__ __forceinline__ void ldmatrix_x4_trans(unsigned (&r)[4], unsigned add
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
 }
-__device__ __forceinline__ void cp_async16(unsigned dst, const void* src) {
-    asm volatile("cp.async.cg.shared.global.L2::256B [%0], [%1], 16;\n" ::"r"(dst), "l"(src));
+// 16 bytes of the cache: read once a step, so marked to leave L2 first
+__device__ __forceinline__ void cp_async16(unsigned dst, const void* src, unsigned long long policy) {
+    asm volatile("cp.async.cg.shared.global.L2::cache_hint.L2::256B [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "l"(policy));
+}
+__device__ __forceinline__ unsigned long long l2_evict_first() {
+    unsigned long long policy;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;\n" : "=l"(policy));
+    return policy;
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
@@ -114,6 +120,7 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_kernel(const AttentionPar
     const __nv_bfloat16* kbase = (const __nv_bfloat16*)c.kv;
     const __nv_bfloat16* vbase = kbase + c.v_offset;
 
+    const unsigned long long kv_policy = l2_evict_first();
     auto issue = [&](int stage, int ti) {
         const int j0 = ti * TILE;
         const int page = table[j0 / c.page_size];
@@ -124,8 +131,8 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_kernel(const AttentionPar
             const int e = lane + 32 * i;
             const int r = e / CH, ch = e % CH;
             const unsigned d = r * (HD * 2) + ((ch ^ (r & SWZ)) << 4);
-            cp_async16(kdst + d, kbase + off + (size_t)r * HD + ch * 8);
-            cp_async16(vdst + d, vbase + off + (size_t)r * HD + ch * 8);
+            cp_async16(kdst + d, kbase + off + (size_t)r * HD + ch * 8, kv_policy);
+            cp_async16(vdst + d, vbase + off + (size_t)r * HD + ch * 8, kv_policy);
         }
     };
 

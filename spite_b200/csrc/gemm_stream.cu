@@ -94,6 +94,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const GemmParams p
         tail->abort_flag = 0;
         mbar_init_fence();
     }
+    const unsigned long long w_policy = l2_evict_first();   // weights are read once a step: they should not push the tokens and the cache out of L2
     // A one-group product's first item is known now: request its first weights before waiting for
     // the kernels before (weights are written by no kernel of the step).
     int pre = 0;
@@ -108,10 +109,10 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const GemmParams p
                 const unsigned bar = smem_u32(&tail->full[j]), dst = smem_u32(smem + j * STAGE);
                 mbar_expect_tx(bar, W_BYTES);
                 if (DUAL) {
-                    tma_load_2d(dst, &map_w, (kb0 + j) * BK, rt * COLS, bar);
-                    tma_load_2d(dst + W_BYTES / 2, &map_w, (kb0 + j) * BK, p.N + rt * COLS, bar);
+                    tma_load_2d_hint(dst, &map_w, (kb0 + j) * BK, rt * COLS, bar, w_policy);
+                    tma_load_2d_hint(dst + W_BYTES / 2, &map_w, (kb0 + j) * BK, p.N + rt * COLS, bar, w_policy);
                 } else {
-                    tma_load_2d(dst, &map_w, (kb0 + j) * BK, rt * COLS, bar);
+                    tma_load_2d_hint(dst, &map_w, (kb0 + j) * BK, rt * COLS, bar, w_policy);
                 }
             }
         }
@@ -179,10 +180,10 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const GemmParams p
                 } else if (lane == 0) {
                     mbar_expect_tx(bar, W_BYTES);
                     if (DUAL) {
-                        tma_load_2d(dst, &map_w, kb * BK, wy, bar);
-                        tma_load_2d(dst + W_BYTES / 2, &map_w, kb * BK, wy + p.N, bar);
+                        tma_load_2d_hint(dst, &map_w, kb * BK, wy, bar, w_policy);
+                        tma_load_2d_hint(dst + W_BYTES / 2, &map_w, kb * BK, wy + p.N, bar, w_policy);
                     } else {
-                        tma_load_2d(dst, &map_w, kb * BK, wy, bar);
+                        tma_load_2d_hint(dst, &map_w, kb * BK, wy, bar, w_policy);
                     }
                 }
 #pragma unroll

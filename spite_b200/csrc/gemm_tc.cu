@@ -137,6 +137,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (warp == 0) {
         if (lane == 0) {
             // ---- loader
+            // weights that one row tile alone uses are read once: they should leave L2 first
+            const bool dense_once = !p.group_offsets && p.M <= BM;
+            const unsigned long long w_policy = l2_evict_first();
             int it = 0;                                       // k blocks issued so far, over all tiles
             int s = 0;                                        // it % n_stages and the ring's phase, kept by counting
             unsigned ph = 0;
@@ -144,6 +147,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             for (int idx = blockIdx.x; idx < total_tiles && ok; idx += gridDim.x) {
                 const Tile t = tile_at(p, tail, listed, idx, row_tiles, cols_per_tile);
                 if (!t.ok) continue;
+                const bool w_once = p.group_offsets ? p.group_offsets[t.group + 1] - p.group_offsets[t.group] <= BM : dense_once;
                 const int wy0 = t.group * w_rows + t.n0;
                 const int wy1 = DUAL ? t.group * w_rows + p.N + t.n0 : wy0 + bnh;
                 for (int kb = 0; kb < num_kb; ++kb, ++it, s = (s + 1 == n_stages ? 0 : s + 1), ph ^= (s == 0)) {
@@ -153,8 +157,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     const unsigned dst = smem_u32(smem + s * stage_tx);
                     mbar_expect_tx(bar, stage_tx);
                     tma_load_2d(dst, &map_a, kb * BK, t.row0, bar);
-                    tma_load_2d(dst + A_BYTES, &map_w, kb * BK, wy0, bar);
-                    tma_load_2d(dst + A_BYTES + bnh * BK * 2, &map_w, kb * BK, wy1, bar);
+                    if (w_once) {
+                        tma_load_2d_hint(dst + A_BYTES, &map_w, kb * BK, wy0, bar, w_policy);
+                        tma_load_2d_hint(dst + A_BYTES + bnh * BK * 2, &map_w, kb * BK, wy1, bar, w_policy);
+                    } else {
+                        tma_load_2d(dst + A_BYTES, &map_w, kb * BK, wy0, bar);
+                        tma_load_2d(dst + A_BYTES + bnh * BK * 2, &map_w, kb * BK, wy1, bar);
+                    }
                 }
             }
             if (*abort_flag) {

@@ -61,6 +61,17 @@ __device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap* map
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
                  ::"r"(dst), "l"((unsigned long long)map), "r"(x), "r"(y), "r"(bar) : "memory");
 }
+// The same with an L2 eviction policy (see l2_evict_first) for data that is read once.
+__device__ __forceinline__ void tma_load_2d_hint(unsigned dst, const CUtensorMap* map, int x, int y, unsigned bar,
+                                                 unsigned long long policy) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3}], [%4], %5;\n"
+                 ::"r"(dst), "l"((unsigned long long)map), "r"(x), "r"(y), "r"(bar), "l"(policy) : "memory");
+}
+__device__ __forceinline__ unsigned long long l2_evict_first() {
+    unsigned long long policy;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;\n" : "=l"(policy));
+    return policy;
+}
 __device__ __forceinline__ void tma_load_3d(unsigned dst, const CUtensorMap* map, int x, int y, int z, unsigned bar) {
     asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];\n"
                  ::"r"(dst), "l"((unsigned long long)map), "r"(x), "r"(y), "r"(z), "r"(bar) : "memory");
