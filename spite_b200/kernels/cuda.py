@@ -157,9 +157,9 @@ class CudaKernels(KernelSet):
     def _gemm(self, p: GemmParams, what, max_rows_per_group, gather_src=None):
         """Pick the kernel.  bfloat16: up to 16 rows (a decode step) go to the TMA weight-streaming
         kernel when K is a multiple of 64, else to the register-ring streaming kernel; more rows to
-        the tcgen05 kernels (TMA-fed, accumulators in TMEM): one group of 256 rows and more on pairs
-        of multiprocessors, the rest on one block a tile; a very tall matrix (output head) goes there
-        even with few rows.  float32, and shapes those refuse, go to the CUDA-core kernel.
+        the tcgen05 kernels (TMA-fed, accumulators in TMEM): one group of 256 rows and more, or groups
+        of 512 rows on average, on pairs of multiprocessors, the rest on one block a tile; a very
+        tall matrix (output head) goes there even with few rows.  float32, and shapes those refuse, go to the CUDA-core kernel.
         `gather_src` is the tensor whose rows `p.a_rows` gathers: the tcgen05 kernel wants contiguous
         rows, so they are gathered first."""
         if self.dtype == torch.bfloat16:
