@@ -8,7 +8,7 @@
 //   warp 0     one lane loads the rows of q of both tiles once (three-dimensional TMA boxes: 64
 //              elements x the group's heads x the tokens, which land row by row in the
 //              128-byte-swizzled K-major layout) and then the K and V tiles into two rings of
-//              three stages each;
+//              four stages each;
 //   warps 1-2  warp 1 allocates tensor memory (per row tile two score tiles of 64 columns and
 //              the output tile of head-size columns); one lane of each issues, for its row
 //              tile,  S = Q K^T  (128 x 64 x head size) and  O += P V  (128 x head size x 64; P
