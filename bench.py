@@ -185,6 +185,8 @@ def run_ours(args):
             pre_ms.append(e0.elapsed_time(e1))
         pms = sorted(pre_ms[1:])[2]                       # the median of five runs after one warm-up
         pflops = prefill_flops(cfgd, T)
+        if os.environ.get("SPITE_BENCH_VERBOSE"):
+            print("prefill runs (ms):", [round(x, 2) for x in pre_ms], file=sys.stderr)
         return {"value": round(T * 1000.0 / pms, 1), "tokens": T, "ms": round(pms, 3),
                 "frac": round(pflops / (pms * 1e-3) / (pk["bf16_tflops_sustained"] * 1e12), 4)}
 

@@ -334,7 +334,7 @@ int launch(const GemmParams& p, int n_blocks, int smem_budget, int n_splits, flo
 }  // namespace
 
 // `max_rows_per_group` <= 16.  `n_blocks`: resident blocks (two per multiprocessor fit when `smem_budget`,
-// the bytes of shared memory a block may take, is at most about 110 KiB).  `n_splits`: k splits per tile
+// the bytes of shared memory a block may take, is at most about 110 KiB, three at 74 KiB).  `n_splits`: k splits per tile
 // (1: no scratch needed).  `scratch`: groups-with-tokens x row tiles x n_splits x 16 x 128 floats;
 // `tickets`: that many tiles' ints, zero before the first call; calls that share them must not overlap.
 SPITE_API int spite_gemm_stream(const GemmParams* p, int max_rows_per_group, int n_blocks, int smem_budget, int n_splits,

@@ -105,8 +105,13 @@ class CudaKernels(KernelSet):
         # the TMA weight-streaming kernel for decode products: k elements per work item, shared memory per block
         self.use_stream = os.environ.get("SPITE_NO_STREAM_GEMM", "") == ""
         self.stream_split_k = int(os.environ.get("SPITE_STREAM_SPLIT_K", "2048"))
-        self.stream_smem = int(os.environ.get("SPITE_STREAM_SMEM", str(110 * 1024)))
-        self.stream_blocks = int(float(os.environ.get("SPITE_STREAM_BLOCKS_PER_SM", "2")) * self.sm_count)
+        # (shared memory per block, blocks per multiprocessor) for up to 3 tokens and for more: measured in the decode
+        # step at Scout shapes, one token 2.90 ms with (110 KiB, 2) against 3.01 with (74 KiB, 3), eight tokens 7.10
+        # against 7.02, sixty-four alike.  SPITE_STREAM_SMEM / SPITE_STREAM_BLOCKS_PER_SM set both alike.
+        smem, per_sm = os.environ.get("SPITE_STREAM_SMEM"), os.environ.get("SPITE_STREAM_BLOCKS_PER_SM")
+        few = (int(smem or 110 * 1024), float(per_sm or 2))
+        more = (int(smem or 74 * 1024), float(per_sm or 3))
+        self.stream_shape = [(sm, int(b * self.sm_count)) for sm, b in (few, more)]
         self._tickets, self._tickets_n = {}, 65536       # arrival counters of the k splits (zero between calls), per stream
 
     # ------------------------------------------------------------------ helpers
@@ -223,7 +228,7 @@ class CudaKernels(KernelSet):
         swiglu = p.epilogue == EPI_SWIGLU
         cols = 64 if swiglu else 128
         tiles = -(-p.N // cols) * (min(p.n_groups, p.M) if grouped else 1)
-        blocks = self.stream_blocks
+        smem, blocks = self.stream_shape[p.M > 3]
         splits = 1 if tiles >= 6 * blocks else max(1, min(16, p.K // self.stream_split_k))
         scratch, n_floats = None, 0
         if splits > 1:
@@ -237,7 +242,7 @@ class CudaKernels(KernelSet):
         if tickets is None and splits > 1:
             tickets = self._tickets[stream] = torch.zeros(self._tickets_n, dtype=torch.int32, device=self.device)
         return self._lib("gemm_stream").spite_gemm_stream(
-            C.byref(p), max_rows_per_group, blocks, self.stream_smem, splits, C.c_void_p(_ptr(scratch)),
+            C.byref(p), max_rows_per_group, blocks, smem, splits, C.c_void_p(_ptr(scratch)),
             C.c_longlong(n_floats), C.c_void_p(_ptr(tickets)), self._tickets_n, C.c_void_p(stream))
 
     def attention_tc_error(self) -> int:
