@@ -316,6 +316,9 @@ def main(argv=None):
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    if args.steps < 1 or args.steps + args.warmup + 16 > args.context:
+        print(f"bench.py: --steps {args.steps} with --warmup {args.warmup} does not fit the context of {args.context}")
+        return 2
     run_ours(args)
     return 0
 
