@@ -231,6 +231,8 @@ class CacheManager:
     def rollback(self, req_id):
         """Undo an uncommitted reserve (the step did not run)."""
         rc = self.get(req_id)
+        if not rc.reserved:
+            raise CacheError(f"request {req_id!r} has nothing reserved")
         for g, lps in enumerate(rc.pending):
             for lp in lps:
                 self.pools[g].free(rc.tables[g][lp])
@@ -250,6 +252,7 @@ class CacheManager:
         freed = []
         for g, key in enumerate(self.groups):
             rc.pending[g] = []
+            rc.len_before[g] = len(rc.tables[g])
             first_live = key.window.first_needed(rc.n_tokens) // self.page_size
             out = []
             table = rc.tables[g]

@@ -5,12 +5,15 @@ Every step is planned like this:
   1. every generating request contributes its one next token;
   2. the rest of the token budget goes to prompt portions: first the requests
      already admitted (oldest first), then waiting ones in arrival order, each
-     `min(rest of its prompt, rest of the budget, max_portion)` tokens, as long
-     as a slot is free and the pages for the portion can be supplied;
+     `min(rest of its prompt, rest of the budget, max_portion)` tokens, or as
+     many of them as the free pages hold; a waiting request is admitted while a
+     slot is free and the groups that keep every key have room for its whole
+     prompt beside what the running requests still need;
   3. a request whose prompt ends in this step samples its first token from
      this step's logits.
-When pages run out for the decoding requests, the most recently admitted
-request is preempted: its pages and slot are freed and it goes back to the head
+When pages run out for the decoding requests, or no admitted request can run
+at all (prompts in progress hold the pages each of them needs next), the most
+recently admitted request is preempted: its pages and slot are freed and it goes back to the head
 of the waiting queue with prompt := prompt + tokens generated so far (its
 generator state is kept, so it samples what it would have sampled).  A request
 that is alone and still cannot get a page ends with reason `cache_full`.  The
@@ -186,7 +189,7 @@ class Scheduler:
         if self.waiting:
             head = self.waiting[0]
             n = min(len(head.all_tokens()), self.max_batch_tokens - len(go_on), self.max_portion)
-            if n >= 1 and self.engine.can_run({**wants, head.id: n}):
+            if n >= 1 and self._room_for_whole_prompt(head) and self._fit(head, n, wants):
                 return None                  # the head of the queue can be admitted now
         import torch
         ids = cur.device_tokens
@@ -202,47 +205,87 @@ class Scheduler:
         return self._leave_in_flight(go_on, logits)
 
     # ------------------------------------------------------------------ planning
+    def _fit(self, r: Request, n: int, wants: dict) -> int:
+        """Most tokens, up to `n`, of request `r` that the pools can supply beside `wants` (0: none)."""
+        if n < 1 or not self.engine.can_run({**wants, r.id: 1}):
+            return 0
+        if self.engine.can_run({**wants, r.id: n}):
+            return n
+        lo, hi = 1, n                        # lo fits, hi does not; more tokens never need fewer pages
+        while hi - lo > 1:
+            mid = (lo + hi) // 2
+            if self.engine.can_run({**wants, r.id: mid}):
+                lo = mid
+            else:
+                hi = mid
+        return lo
+
+    def _room_for_whole_prompt(self, head: Request) -> bool:
+        """Admission rule: beside what the running requests still need to finish their prompts and
+        take one decoded token, the groups that keep every key have the pages for the whole prompt
+        of `head` and its first token.  Two prompts admitted into a pool that holds neither of them
+        to the end would only take pages from each other.  With nothing running the head is always
+        admitted: it then gets the pool to itself."""
+        if not self.running:
+            return True
+        cache = self.engine.cache
+        need = [0] * len(cache.groups)
+        for r in self.running + [head]:
+            rest = len(r.all_tokens()) - r.n_fed + (0 if r.state is RequestState.GENERATING else 1)
+            for g, k in enumerate(cache.pages_needed(r.id, max(rest, 1))):
+                need[g] += k
+        return all(n <= pool.n_free for n, pool, key in zip(need, cache.pools, cache.groups)
+                   if key.window.kind == "full")
+
     def plan_step(self) -> StepPlan:
         cache = self.engine.cache
         preempted, ended = [], []
         while True:
-            decodes = [r for r in self.running if r.state is RequestState.GENERATING]
-            wants = {r.id: 1 for r in decodes}
-            if not decodes or cache.can_reserve(wants):
+            while True:
+                decodes = [r for r in self.running if r.state is RequestState.GENERATING]
+                wants = {r.id: 1 for r in decodes}
+                if not decodes or cache.can_reserve(wants):
+                    break
+                victim = self.running[-1]
+                if len(self.running) == 1:
+                    ended.append((victim, FinishReason.CACHE_FULL))
+                    self._finish(victim, FinishReason.CACHE_FULL)
+                    continue
+                self._preempt(victim)
+                preempted.append(victim)
+
+            entries = [(r, [r.all_tokens()[r.n_fed]], True) for r in decodes]
+            budget = self.max_batch_tokens - len(entries)
+
+            def try_portion(r) -> bool:
+                nonlocal budget
+                toks = r.all_tokens()
+                n = self._fit(r, min(len(toks) - r.n_fed, budget, self.max_portion), wants)
+                if n < 1:
+                    return False
+                wants[r.id] = n
+                budget -= n
+                entries.append((r, toks[r.n_fed:r.n_fed + n], r.n_fed + n == len(toks)))
+                return True
+
+            for r in self.running:
+                if r.state is RequestState.PREFILLING and budget > 0:
+                    try_portion(r)
+            if entries or not self.running:
                 break
+            # Nothing can run although requests are admitted: prompts in progress hold the pages that
+            # each of them needs next.  The most recently admitted one gives way (it is recomputed
+            # later); a request that is alone and still gets no page cannot be served by this pool.
             victim = self.running[-1]
             if len(self.running) == 1:
                 ended.append((victim, FinishReason.CACHE_FULL))
                 self._finish(victim, FinishReason.CACHE_FULL)
-                continue
+                break
             self._preempt(victim)
             preempted.append(victim)
-
-        entries = [(r, [r.all_tokens()[r.n_fed]], True) for r in decodes]
-        budget = self.max_batch_tokens - len(entries)
-        wants = {r.id: 1 for r in decodes}
-
-        def try_portion(r) -> bool:
-            nonlocal budget
-            toks = r.all_tokens()
-            n = min(len(toks) - r.n_fed, budget, self.max_portion)
-            if n < 1:
-                return False
-            trial = dict(wants)
-            trial[r.id] = n
-            if not self.engine.can_run(trial):
-                return False
-            wants[r.id] = n
-            budget -= n
-            entries.append((r, toks[r.n_fed:r.n_fed + n], r.n_fed + n == len(toks)))
-            return True
-
-        for r in self.running:
-            if r.state is RequestState.PREFILLING and budget > 0:
-                try_portion(r)
         while self.waiting and budget > 0 and not preempted:
             r = self.waiting[0]
-            if not try_portion(r):
+            if not self._room_for_whole_prompt(r) or not try_portion(r):
                 break                       # arrival order is kept: nobody overtakes the head
             self.waiting.popleft()
             r.state = RequestState.PREFILLING

@@ -114,6 +114,25 @@ def test_reserve_is_all_or_nothing_and_rollback_restores():
     m.check_invariants()
 
 
+def test_rollback_after_a_commit_changes_nothing():
+    """A rollback with nothing reserved must not cut the pages of the reserve committed before it."""
+    m = manager(pages=8, page_size=4)
+    m.admit("a")
+    m.reserve("a", 5)
+    m.commit("a")
+    m.reserve("a", 6)
+    m.commit("a")
+    before = ([list(t) for t in m.get("a").tables], m.free_pages())
+    with pytest.raises(CacheError, match="nothing reserved"):
+        m.rollback("a")
+    assert ([list(t) for t in m.get("a").tables], m.free_pages()) == before
+    m.check_invariants()
+    m.reserve("a", 3)
+    m.rollback("a")
+    assert ([list(t) for t in m.get("a").tables], m.free_pages()) == before
+    m.check_invariants()
+
+
 @pytest.mark.parametrize("seed", range(6))
 def test_random_orders_of_requests_keep_the_invariants(seed):
     rng = random.Random(seed)

@@ -242,3 +242,75 @@ def test_decoding_ahead_random_scenarios(model, seed):
     for i in range(n_req):
         assert b.finished[i].output == a.finished[i].output, (seed, i)
         assert b.finished[i].finish_reason is a.finished[i].finish_reason, (seed, i)
+
+
+def test_two_prompts_in_a_tight_pool_do_not_block_each_other(model):
+    """Two 120-token prompts that each fit a pool of 160 tokens alone, portions of 32 under a budget of 64:
+    whatever is admitted, every step runs something and both requests end with the right tokens."""
+    a, b = H.random_tokens(512, 120, 70), H.random_tokens(512, 120, 71)
+    s = make(model, cache_tokens=160, page_size=16, max_batch_tokens=64, max_portion=32)
+    s.submit(Request("a", a, greedy(4)))
+    s.submit(Request("b", b, greedy(4)))
+    while s.active_count():
+        before = s.counters["steps"]
+        s.step()
+        assert s.counters["steps"] == before + 1
+        s.engine.cache.check_invariants()
+    assert s.finished["a"].output == plain_greedy(model, a, 4)
+    assert s.finished["b"].output == plain_greedy(model, b, 4)
+    assert all(r.finish_reason is FinishReason.MAX_TOKENS for r in s.finished.values())
+    assert s.counters["preemptions"] == 0                 # b waited for a instead of taking its pages
+    assert s.engine.cache.free_pages() == [s.engine.n_pages] * 2
+
+
+def test_prompts_in_progress_give_way_when_none_can_go_on(model):
+    """The state that greedy admission could reach: two requests in the middle of their prompts hold all the
+    pages between them.  The later one is preempted, the earlier one goes on."""
+    a, b = H.random_tokens(512, 120, 70), H.random_tokens(512, 120, 71)
+    s = make(model, cache_tokens=160, page_size=16, max_batch_tokens=64, max_portion=32)
+    s.submit(Request("a", a, greedy(3)))
+    s.submit(Request("b", b, greedy(3)))
+    ra, rb = s.waiting.popleft(), s.waiting.popleft()
+    for r, n in ((ra, 96), (rb, 64)):                       # 6 + 4 pages of 10: nothing is free
+        s.engine.step([(r.id, r.prompt[:n], [])])
+        r.n_fed, r.state = n, RequestState.PREFILLING
+        s.running.append(r)
+    assert s.engine.cache.free_pages() == [10, 0]           # (chunked, full): the chunked group let the passed chunks go
+    s.step()
+    assert [r.id for r in s.waiting] == ["b"] and rb.preemptions == 1 and rb.n_fed == 0
+    assert ra.n_fed == 120 and len(ra.output) == 1          # a ran the rest of its prompt in that step
+    done = s.run_until_done()
+    assert done["a"].output == plain_greedy(model, a, 3) and done["b"].output == plain_greedy(model, b, 3)
+    assert done["b"].preemptions == 1
+    assert s.engine.cache.free_pages() == [s.engine.n_pages] * 2
+
+
+@pytest.mark.parametrize("seed", range(12))
+def test_random_pools_and_budgets_always_make_progress(model, seed):
+    """Random prompts, portions, budgets and pools down to the size of the longest request: every step runs
+    something, nobody ends for want of pages that the pool has, the tokens are the plain implementation's."""
+    import random
+    rng = random.Random(1000 + seed)
+    n_req = rng.randint(2, 5)
+    prompts = [H.random_tokens(512, rng.randint(2, 90), 50 * seed + i) for i in range(n_req)]
+    limits = [rng.randint(1, 6) for _ in range(n_req)]
+    longest = max(len(p) + n for p, n in zip(prompts, limits))
+    pages = -(-longest // 16) * 16 + 16 * rng.choice([0, 0, 1, 3, 8])
+    budget = rng.choice([2, 5, 16, 40, 64, 2048])
+    portion = rng.choice([None, 3, 16, 32])
+    s = make(model, cache_tokens=pages, page_size=16, max_batch_tokens=budget, max_portion=portion,
+             max_requests=rng.randint(2, 4))
+    for i in range(n_req):
+        s.submit(Request(i, prompts[i], greedy(limits[i])))
+    steps = 0
+    while s.active_count():
+        before = (s.counters["steps"], len(s.finished))
+        s.step()
+        assert (s.counters["steps"], len(s.finished)) != before
+        s.engine.cache.check_invariants()
+        steps += 1
+        assert steps < 3000
+    for i in range(n_req):
+        assert s.finished[i].finish_reason is FinishReason.MAX_TOKENS, (seed, i)
+        assert s.finished[i].output == plain_greedy(model, prompts[i], limits[i]), (seed, i)
+    assert s.engine.cache.free_pages() == [s.engine.n_pages] * 2
