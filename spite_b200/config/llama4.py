@@ -21,7 +21,7 @@ class WeightBinding:
     target: str                 # e.g. "layers.3.ffn.experts_down"
     source: str                 # checkpoint tensor name
     source_shape: tuple         # exact shape expected in the file
-    transform: Optional[str] = None   # None | "transpose_last2"
+    transform: Optional[str] = None   # a registered weight transform (spite_b200.weights.register_weight_transform)
     init: str = "normal"        # how the random-weights mode fills it: "normal" | "ones"
 
 
@@ -240,7 +240,7 @@ class Llama4Config:
             else:
                 ffn = PartSpec("dense_swiglu", {
                     "hidden_size": c.hidden_size, "intermediate_size": c.intermediate_size_mlp})
-            blocks.append(BlockSpec("prenorm_residual", norm, mixer, norm, ffn))
+            blocks.append(BlockSpec("prenorm_residual", {"mixer_norm": norm, "mixer": mixer, "ffn_norm": norm, "ffn": ffn}))
         order = tuple(LayerCall(L, L, True) for L in range(c.num_hidden_layers))
         return ModelPlan(hidden_size=c.hidden_size, vocab_size=c.vocab_size, blocks=tuple(blocks),
                          order=order, final_norm=norm, tie_word_embeddings=c.tie_word_embeddings,

@@ -27,12 +27,22 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class BlockSpec:
-    """A layer: how its parts are arranged (`arrangement` is a registered block kind)."""
+    """A layer: how its parts are arranged (`arrangement` is a registered block kind) and the
+    parts themselves by the names the arrangement gives its places (`prenorm_residual`:
+    mixer_norm, mixer, ffn_norm, ffn).  Another arrangement has other places: more norms, no
+    feed-forward, two mixers."""
     arrangement: str
-    mixer_norm: PartSpec
-    mixer: PartSpec
-    ffn_norm: PartSpec
-    ffn: PartSpec
+    parts: dict[str, PartSpec] = field(default_factory=dict)
+
+    def __hash__(self):
+        return hash((self.arrangement, tuple(sorted((k, hash(v)) for k, v in self.parts.items()))))
+
+    def __getattr__(self, place):
+        """`spec.mixer` reads the part at the place `mixer`."""
+        parts = self.__dict__.get("parts", {})
+        if place in parts:
+            return parts[place]
+        raise AttributeError(f"block {self.__dict__.get('arrangement')!r} has no place {place!r}; it has {sorted(parts)}")
 
 
 @dataclass(frozen=True)
@@ -58,12 +68,17 @@ class ModelPlan:
     final_norm: PartSpec
     tie_word_embeddings: bool
     max_positions: int
+    embedding_scale: float = 1.0          # the embedding row is multiplied by this as it enters the residual stream
+    logit_scale: float = 1.0              # logits are multiplied by this,
+    logit_softcap: float | None = None    # then squashed to cap * tanh(logit / cap)
 
     def validate(self):
         if self.hidden_size <= 0 or self.vocab_size <= 0:
             raise ConfigError("hidden_size and vocab_size must be positive")
         if not self.blocks:
             raise ConfigError("a model needs at least one layer")
+        if self.logit_softcap is not None and not self.logit_softcap > 0:
+            raise ConfigError("logit_softcap must be positive")
         writers = {}
         for call in self.order:
             if not 0 <= call.layer < len(self.blocks):

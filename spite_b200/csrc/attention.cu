@@ -1,8 +1,9 @@
 // Attention over the paged cache, general kernels (any head size that is a
 // multiple of 2 up to 256, any number of heads and groups, both element types).
 //
-//  * qk_prepare: position encoding of q and k, weightless per-head norm, the
-//    temperature factor of layers without rotation, and the append of k and v to
+//  * qk_prepare: position encoding of q and k (neighbouring elements or the two halves of
+//    the rotating part pair up), per-head RMS norm after or before it with or without gains,
+//    the temperature factor of layers without rotation, and the append of k and v to
 //    their pages, in one pass over the projection's output (one warp per head).
 //  * paged_attention: one warp per (token, query head) walks the visible keys in
 //    tiles of 32, keeps a running maximum and sum (all in float32) and gathers the
@@ -43,14 +44,24 @@ __global__ void __launch_bounds__(256) qk_prepare_kernel(const QkPrepareParams p
     float temp = 1.f;
     if (p.temperature_floor > 0) temp = logf((float)((pos + 1) / p.temperature_floor) + 1.0f) * p.temperature_scale + 1.0f;
 
-    // the rotation of pair i is the same for every head: cos and sin of pos * inv_freq[i], once per warp
+    // Pair i of a head is the elements (e0, e1): the neighbours (2i, 2i+1), or, among the first
+    // `rot` elements when halves pair up, (i, i + rot/2); pairs beyond the rotating part are the
+    // neighbours that remain.  Lane l holds the pairs l, l + 32, ...; the rotation of a pair is the
+    // same for every head: cos and sin of pos * inv_freq[i], once per warp.
     constexpr int MAXP = 4;                                  // pairs per lane: head_dim <= 256
+    const int rot = p.inv_freq ? p.rotary_dim : 0;
+    const bool halves = p.pairing == SPITE_PAIR_HALVES;
     float cs[MAXP], sn[MAXP];
+    int e0[MAXP], e1[MAXP];
 #pragma unroll
     for (int r = 0; r < MAXP; ++r) {
         const int i = lane + 32 * r;
         cs[r] = 1.f; sn[r] = 0.f;
-        if (p.inv_freq && 2 * i < hd) sincosf((float)pos * p.inv_freq[i], &sn[r], &cs[r]);
+        e0[r] = 2 * i; e1[r] = 2 * i + 1;
+        if (2 * i < rot) {
+            sincosf((float)pos * p.inv_freq[i], &sn[r], &cs[r]);
+            if (halves) { e0[r] = i; e1[r] = i + rot / 2; }
+        }
     }
 
     for (int head = blockIdx.y * heads_per_block + warp; head < head_end; head += n_warps) {
@@ -73,35 +84,54 @@ __global__ void __launch_bounds__(256) qk_prepare_kernel(const QkPrepareParams p
             }
             continue;
         }
-        // q or k: rotate neighbouring pairs (2i, 2i+1) by pos * inv_freq[i]
-        // (rotation: crates/spite-rope/src/lib.rs:83-91; norm after it: llama4.rs:161-176)
+        // q or k (rotation: crates/spite-rope/src/lib.rs:83-91; norm after it: llama4.rs:161-176)
+        const float* gain = is_q ? p.q_gain : p.k_gain;
+        const bool norm = p.qk_norm_eps > 0.f;
+        const bool norm_first = norm && p.norm_before_rotation;
         float x0[MAXP], x1[MAXP];
+#pragma unroll
+        for (int r = 0; r < MAXP; ++r) {
+            x0[r] = x1[r] = 0.f;
+            if (2 * (lane + 32 * r) < hd) {
+                if (halves) { x0[r] = to_f32(in[e0[r]]); x1[r] = to_f32(in[e1[r]]); }
+                else load_pair(in + e0[r], x0[r], x1[r]);
+            }
+        }
+        if (norm_first) {
+            float ss = 0.f;
+#pragma unroll
+            for (int r = 0; r < MAXP; ++r) ss += x0[r] * x0[r] + x1[r] * x1[r];
+            ss = warp_sum(ss);
+            const float mul = 1.0f / sqrtf(ss / (float)hd + p.qk_norm_eps);
+#pragma unroll
+            for (int r = 0; r < MAXP; ++r) {
+                if (2 * (lane + 32 * r) >= hd) continue;
+                x0[r] *= mul; x1[r] *= mul;
+                if (gain) { x0[r] *= gain[e0[r]]; x1[r] *= gain[e1[r]]; }
+            }
+        }
         float ss = 0.f;
 #pragma unroll
         for (int r = 0; r < MAXP; ++r) {
-            const int i = lane + 32 * r;
-            x0[r] = x1[r] = 0.f;
-            if (2 * i < hd) {
-                float a, bb;
-                load_pair(in + 2 * i, a, bb);
-                if (p.inv_freq) {
-                    const float ra = a * cs[r] - bb * sn[r], rb = a * sn[r] + bb * cs[r];
-                    a = ra; bb = rb;
-                }
-                x0[r] = a; x1[r] = bb;
-                ss += a * a + bb * bb;
+            if (2 * (lane + 32 * r) < rot) {
+                const float ra = x0[r] * cs[r] - x1[r] * sn[r], rb = x0[r] * sn[r] + x1[r] * cs[r];
+                x0[r] = ra; x1[r] = rb;
             }
+            ss += x0[r] * x0[r] + x1[r] * x1[r];
         }
         float mul = 1.f;
-        if (p.qk_norm_eps > 0.f) {
+        if (norm && !norm_first) {
             ss = warp_sum(ss);
             mul = 1.0f / sqrtf(ss / (float)hd + p.qk_norm_eps);
         }
         if (is_q) mul *= temp;
 #pragma unroll
         for (int r = 0; r < MAXP; ++r) {
-            const int i = lane + 32 * r;
-            if (2 * i < hd) store_pair(dst + 2 * i, x0[r] * mul, x1[r] * mul);
+            if (2 * (lane + 32 * r) >= hd) continue;
+            float a = x0[r] * mul, bb = x1[r] * mul;
+            if (gain && norm && !norm_first) { a *= gain[e0[r]]; bb *= gain[e1[r]]; }
+            if (halves) { dst[e0[r]] = from_f32<T>(a); dst[e1[r]] = from_f32<T>(bb); }
+            else store_pair(dst + e0[r], a, bb);
         }
     }
 }
@@ -196,6 +226,9 @@ SPITE_API int spite_qk_prepare(int dtype, const QkPrepareParams* p, const StepTo
     const int chk = check_common(b, c, p->num_heads);
     if (chk != SPITE_OK) return chk;
     if (b->n_tokens == 0) return SPITE_OK;
+    if (p->pairing != SPITE_PAIR_NEIGHBOURS && p->pairing != SPITE_PAIR_HALVES) return SPITE_BAD_ARG;
+    if (p->inv_freq && (p->rotary_dim < 2 || p->rotary_dim % 2 || p->rotary_dim > c->head_dim)) return SPITE_BAD_ARG;
+    if (p->pairing == SPITE_PAIR_HALVES && p->inv_freq && p->rotary_dim % 4) return SPITE_UNSUPPORTED;  // pairs beyond the rotating part start at an even pair index
     const int heads = p->num_heads + 2 * c->num_kv_heads;
     // few tokens: four heads a block, so that the step still fills the device; many: a block per token
     const bool many = b->n_tokens >= 1024;

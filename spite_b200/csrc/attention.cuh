@@ -28,11 +28,19 @@ struct PagedCache {
     int head_dim;
 };
 
+#define SPITE_PAIR_NEIGHBOURS 0   // pair i of a head is elements (2i, 2i+1)
+#define SPITE_PAIR_HALVES 1       // pair i is elements (i, i + rotary_dim/2)
+
 struct QkPrepareParams {
     const void* qkv;            // [tokens, (nq + 2 nkv) * head_dim]: q heads, k heads, v heads
     void* q_out;                // [tokens, nq * head_dim]
-    const float* inv_freq;      // [head_dim / 2] rotation frequencies, or null: no rotation
-    float qk_norm_eps;          // > 0: weightless RMS norm of every q and k head after the rotation
+    const float* inv_freq;      // [rotary_dim / 2] rotation frequencies, or null: no rotation
+    const float* q_gain;        // [head_dim] gain of the norm of q heads, or null (weightless)
+    const float* k_gain;        // [head_dim] the same for k heads
+    float qk_norm_eps;          // > 0: RMS norm of every q and k head
+    int norm_before_rotation;   // the norm runs before the rotation instead of after it
+    int pairing;                // SPITE_PAIR_*
+    int rotary_dim;             // the first rotary_dim elements of a head rotate (even, <= head_dim)
     int temperature_floor;      // > 0: q *= ln(floor((pos+1)/floor) + 1) * temperature_scale + 1
     float temperature_scale;
     int num_heads;

@@ -267,30 +267,44 @@ __global__ void __launch_bounds__(WARPS * 32) attn_mma_kernel(const AttentionPar
         if (x.n_splits == 1) {
             ((__nv_bfloat16*)p.out)[((size_t)tok * nq + head) * HD + d] = __float2bfloat16_rn(acc / fmaxf(l, 1e-30f));
         } else {
-            const size_t slot = ((size_t)tok * nq + head) * x.n_splits + split;
+            // partial results are indexed by the block's place among this kernel's blocks, not by the
+            // token's place in the step: a long prompt portion beside one decoded token costs no scratch
+            const size_t slot = (((size_t)blockIdx.x * x.tokens_per_block + r / G) * nq + head) * x.n_splits + split;
             x.o_part[slot * HD + d] = acc;
             if (d == 0) { x.ml_part[slot * 2] = m; x.ml_part[slot * 2 + 1] = l; }
         }
     }
 }
 
-// grid tokens * heads, block 128: merge the splits of one (token, head).  Thread s takes split s's
-// maximum and sum (at most MERGE_THREADS splits); the weights 2^.. of the splits go through shared
-// memory, then every thread sums its output elements over the splits in ascending order.
+// grid (blocks of the kernel above) * tokens_per_block * heads, block 128: merge the splits of one
+// (token, head).  Thread s takes split s's maximum and sum (at most MERGE_THREADS splits); the weights
+// 2^.. of the splits go through shared memory, then every thread sums its output elements over the
+// splits in ascending order.
 constexpr int MERGE_THREADS = 128;
 __global__ void __launch_bounds__(MERGE_THREADS) attn_merge_kernel(const float* __restrict__ o_part,
                                                                    const float* __restrict__ ml_part,
                                                                    __nv_bfloat16* __restrict__ out, int n_splits, int hd,
-                                                                   int num_heads, const int* __restrict__ seg_of_token,
-                                                                   const int* __restrict__ cu_seqlens, int seg_min, int seg_max) {
+                                                                   int num_heads, const AttnMmaExtra x) {
     __shared__ float w_s[MERGE_THREADS];
     __shared__ float scratch[33];
     pdl_wait();
     pdl_launch_dependents();
     const size_t row = blockIdx.x;
-    const int seg = seg_of_token[row / num_heads];
-    const int seg_n = cu_seqlens[seg + 1] - cu_seqlens[seg];
-    if (seg_n < seg_min || seg_n > seg_max) return;
+    const int head = (int)(row % num_heads);
+    const int local = (int)((row / num_heads) % x.tokens_per_block);
+    int idx = (int)(row / num_heads / x.tokens_per_block), tok = -1;
+    for (int s = 0; s < x.n_segments; ++s) {                // the same walk as the kernel above
+        const int lo = x.cu_seqlens[s], n = x.cu_seqlens[s + 1] - lo;
+        if (n < x.seg_min_tokens || n > x.seg_max_tokens) continue;
+        const int blocks = (n + x.tokens_per_block - 1) / x.tokens_per_block;
+        if (idx < blocks) {
+            const int t = lo + idx * x.tokens_per_block + local;
+            if (t < lo + n) tok = t;
+            break;
+        }
+        idx -= blocks;
+    }
+    if (tok < 0) return;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     float ms = -INFINITY, ls = 0.f;
     if (tid < n_splits) {
@@ -306,11 +320,12 @@ __global__ void __launch_bounds__(MERGE_THREADS) attn_merge_kernel(const float* 
     const float l = block_sum(ls * w, scratch);             // syncs: w_s is visible afterwards
     const float inv = 1.0f / fmaxf(l, 1e-30f);
     const float* o = o_part + row * n_splits * hd;
+    __nv_bfloat16* dst = out + ((size_t)tok * num_heads + head) * hd;
     for (int d = tid; d < hd; d += MERGE_THREADS) {
         float acc = 0.f;
 #pragma unroll 4
         for (int s = 0; s < n_splits; ++s) acc = fmaf(o[(size_t)s * hd + d], w_s[s], acc);
-        out[row * hd + d] = __float2bfloat16_rn(acc * inv);
+        dst[d] = __float2bfloat16_rn(acc * inv);
     }
 }
 
@@ -331,7 +346,9 @@ int launch(const AttentionParams& p, const StepTokens& b, const PagedCache& c, c
 
 }  // namespace
 
-// `n_blocks` = sum over segments of ceil(tokens / tokens_per_block), computed by the caller.
+// `n_blocks` = sum over the segments this kernel serves of ceil(tokens / tokens_per_block), computed by the
+// caller.  With splits, `o_part` holds n_blocks * tokens_per_block * heads * splits * head_dim floats and
+// `ml_part` two floats per (row, head, split).
 SPITE_API int spite_paged_attention_mma(const AttentionParams* p, const StepTokens* b, const PagedCache* c,
                                         const AttnMmaExtra* x, int n_blocks, void* stream) {
     if (!p || !b || !c || !x || !p->q || !p->out || !x->cu_seqlens || !c->kv) return SPITE_BAD_ARG;
@@ -360,8 +377,8 @@ SPITE_API int spite_paged_attention_mma(const AttentionParams* p, const StepToke
         default: rc = launch<8>(*p, *b, *c, *x, n_blocks, st); break;
     }
     if (rc != SPITE_OK || x->n_splits == 1) return rc;
-    SPITE_LAUNCH(attn_merge_kernel, b->n_tokens * p->num_heads, MERGE_THREADS, 0, st, (const float*)x->o_part,
-                 (const float*)x->ml_part, (__nv_bfloat16*)p->out, x->n_splits, c->head_dim, p->num_heads,
-                 b->seg_of_token, x->cu_seqlens, x->seg_min_tokens, x->seg_max_tokens);
+    SPITE_LAUNCH(attn_merge_kernel, n_blocks * x->tokens_per_block * p->num_heads, MERGE_THREADS, 0, st,
+                 (const float*)x->o_part, (const float*)x->ml_part, (__nv_bfloat16*)p->out, x->n_splits,
+                 c->head_dim, p->num_heads, *x);
     return spite_launch_status();
 }

@@ -53,6 +53,11 @@ constexpr float RESCALE_STEP = 8.f;     // log2 units
 constexpr float LOG2E = 1.4426950408889634f;
 
 __device__ int g_attn_tc_error = 0;
+}  // namespace
+// 1: the loader waited for a free stage, 2: the tensor-core issuer waited, 3: a softmax warp waited.
+// (`extra_tx` is not used here.)
+SPITE_WAIT_CONTROLS(attention_tc, g_attn_tc_error)
+namespace {
 
 struct GroupBarriers {
     unsigned long long s_full[2], p_ready, pv_done, exp_done;
@@ -80,7 +85,8 @@ template <int NKB>
 __global__ void __launch_bounds__(THREADS, 1)
 attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                const __grid_constant__ CUtensorMap map_v, const AttentionParams p, const StepTokens b,
-               const PagedCache c, const AttnMmaExtra x, const int q_box_tokens, const int n_tile_pairs) {
+               const PagedCache c, const AttnMmaExtra x, const int q_box_tokens, const int n_tile_pairs,
+               const WaitControl waits) {
     constexpr int HD = 64 * NKB;
     constexpr int Q_BYTES = NKB * BM * 128;              // q of one row tile
     constexpr int KT_BYTES = NKB * BN * 128;             // one K tile, one V tile
@@ -97,6 +103,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     unsigned char* k_s = q_s + 2 * Q_BYTES;
     unsigned char* v_s = k_s + ST * KT_BYTES;
     volatile int* abort_flag = &bars.abort_flag;
+    int* const err_word = waits.error_word ? waits.error_word : &g_attn_tc_error;
+    const long long wait_limit = waits.limit_cycles;
 
     auto init_barriers = [&](bool renew) {
         auto one = [&](unsigned long long* bar, unsigned count) {
@@ -178,13 +186,13 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                     int page = table[j0 / c.page_size];
                     if (page < 0 || page >= c.n_pages) page = 0;   // a page behind every row's window: its keys are masked
                     const int y = (page * nkv + kvh) * c.page_size + j0 % c.page_size;
-                    if (!mbar_wait(smem_u32(&bars.k_empty[s]), ph ^ 1, abort_flag, &g_attn_tc_error, 1)) break;
+                    if (!mbar_wait(smem_u32(&bars.k_empty[s]), ph ^ 1, abort_flag, err_word, 1, wait_limit)) break;
                     mbar_expect_tx(smem_u32(&bars.k_full[s]), KT_BYTES);
 #pragma unroll
                     for (int kb = 0; kb < NKB; ++kb)
                         tma_load_2d(smem_u32(k_s + s * KT_BYTES + kb * BN * 128), &map_k, kb * 64, y, smem_u32(&bars.k_full[s]));
                     ++issued_k;
-                    if (!mbar_wait(smem_u32(&bars.v_empty[s]), ph ^ 1, abort_flag, &g_attn_tc_error, 1)) break;
+                    if (!mbar_wait(smem_u32(&bars.v_empty[s]), ph ^ 1, abort_flag, err_word, 1, wait_limit)) break;
                     mbar_expect_tx(smem_u32(&bars.v_full[s]), KT_BYTES);
 #pragma unroll
                     for (int kb = 0; kb < NKB; ++kb)
@@ -193,14 +201,14 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 }
                 // the last releases of the stages must have arrived before the barriers are renewed for the next item
                 for (int j = max(0, n_tiles - ST); j < n_tiles && !*abort_flag; ++j) {
-                    if (!mbar_wait(smem_u32(&bars.k_empty[j % ST]), (j / ST) & 1, abort_flag, &g_attn_tc_error, 1)) break;
-                    if (!mbar_wait(smem_u32(&bars.v_empty[j % ST]), (j / ST) & 1, abort_flag, &g_attn_tc_error, 1)) break;
+                    if (!mbar_wait(smem_u32(&bars.k_empty[j % ST]), (j / ST) & 1, abort_flag, err_word, 1, wait_limit)) break;
+                    if (!mbar_wait(smem_u32(&bars.v_empty[j % ST]), (j / ST) & 1, abort_flag, err_word, 1, wait_limit)) break;
                 }
                 if (*abort_flag) {
                     // copies in flight must land before the block gives its shared memory back
-                    mbar_drain(q_bar, 0);
-                    for (int j = max(0, issued_k - ST); j < issued_k; ++j) mbar_drain(smem_u32(&bars.k_full[j % ST]), (j / ST) & 1);
-                    for (int j = max(0, issued_v - ST); j < issued_v; ++j) mbar_drain(smem_u32(&bars.v_full[j % ST]), (j / ST) & 1);
+                    mbar_drain(q_bar, 0, wait_limit);
+                    for (int j = max(0, issued_k - ST); j < issued_k; ++j) mbar_drain(smem_u32(&bars.k_full[j % ST]), (j / ST) & 1, wait_limit);
+                    for (int j = max(0, issued_v - ST); j < issued_v; ++j) mbar_drain(smem_u32(&bars.v_full[j % ST]), (j / ST) & 1, wait_limit);
                 }
             }
         } else {
@@ -237,15 +245,15 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 if (lane == 0) {
                     // ---- tensor-core issue for this row tile
                     const unsigned idesc_s = make_idesc(BM, BN), idesc_pv = make_idesc(BM, HD, true);
-                    bool ok = mbar_wait(smem_u32(&bars.q_full), 0, abort_flag, &g_attn_tc_error, 2);
+                    bool ok = mbar_wait(smem_u32(&bars.q_full), 0, abort_flag, err_word, 2, wait_limit);
                     // a key tile that this row tile does not need: wait until it has landed (so that the two
                     // row tiles never drift apart by more than the ring) and hand the stage back unread
                     auto pass_tile = [&](int i) {
                         const int s = i % ST;
                         const unsigned ph = (i / ST) & 1;
-                        if (!mbar_wait(smem_u32(&bars.k_full[s]), ph, abort_flag, &g_attn_tc_error, 2)) return false;
+                        if (!mbar_wait(smem_u32(&bars.k_full[s]), ph, abort_flag, err_word, 2, wait_limit)) return false;
                         mbar_arrive(smem_u32(&bars.k_empty[s]));
-                        if (!mbar_wait(smem_u32(&bars.v_full[s]), ph, abort_flag, &g_attn_tc_error, 2)) return false;
+                        if (!mbar_wait(smem_u32(&bars.v_full[s]), ph, abort_flag, err_word, 2, wait_limit)) return false;
                         mbar_arrive(smem_u32(&bars.v_empty[s]));
                         return true;
                     };
@@ -253,8 +261,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                     // P of tile li - 2: the product that read it must have completed
                     auto issue_scores = [&](int li) {
                         const int i = first + li, s = i % ST, sb = li & 1;
-                        if (!mbar_wait(smem_u32(&bars.k_full[s]), (i / ST) & 1, abort_flag, &g_attn_tc_error, 2)) return false;
-                        if (li >= 2 && !mbar_wait(smem_u32(&gb.pv_done), li & 1, abort_flag, &g_attn_tc_error, 2)) return false;
+                        if (!mbar_wait(smem_u32(&bars.k_full[s]), (i / ST) & 1, abort_flag, err_word, 2, wait_limit)) return false;
+                        if (li >= 2 && !mbar_wait(smem_u32(&gb.pv_done), li & 1, abort_flag, err_word, 2, wait_limit)) return false;
                         fence_after();
                         const unsigned qa = smem_u32(q_g), ka = smem_u32(k_s + s * KT_BYTES);
 #pragma unroll
@@ -270,8 +278,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                     if (ok && n_own > 1) ok = issue_scores(1);
                     for (int li = 0; li < n_own && ok; ++li) {
                         const int i = first + li, s = i % ST;
-                        ok = mbar_wait(smem_u32(&gb.p_ready), li & 1, abort_flag, &g_attn_tc_error, 2) &&
-                             mbar_wait(smem_u32(&bars.v_full[s]), (i / ST) & 1, abort_flag, &g_attn_tc_error, 2);
+                        ok = mbar_wait(smem_u32(&gb.p_ready), li & 1, abort_flag, err_word, 2, wait_limit) &&
+                             mbar_wait(smem_u32(&bars.v_full[s]), (i / ST) & 1, abort_flag, err_word, 2, wait_limit);
                         if (!ok) break;
                         fence_after();
                         const unsigned va = smem_u32(v_s + s * KT_BYTES);
@@ -299,7 +307,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 bool ok = true;
                 for (int li = 0; li < n_own; ++li) {
                     const int sb = li & 1;
-                    ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&gb.s_full[sb]), (li >> 1) & 1, abort_flag, &g_attn_tc_error, 3));
+                    ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&gb.s_full[sb]), (li >> 1) & 1, abort_flag, err_word, 3, wait_limit));
                     if (!ok) break;
                     fence_after();
                     float s[BN];
@@ -331,7 +339,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                     const bool takes_turns = turn >= 0 && first + li <= shared_hi;
                     if (takes_turns && (g == 1 || turn > 0)) {
                         const int before = g == 0 ? turn - 1 : turn;      // the other row tile's turn before this one
-                        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.g[g ^ 1].exp_done), before & 1, abort_flag, &g_attn_tc_error, 3));
+                        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars.g[g ^ 1].exp_done), before & 1, abort_flag, err_word, 3, wait_limit));
                         if (!ok) break;
                     }
                     unsigned packed[BN / 2];
@@ -350,7 +358,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                         // The product of the tile before must have left O before its rows are rescaled.  The wait is
                         // made for every tile, needed or not: a wait by parity is only right while the waiter is
                         // at most one phase behind the barrier.
-                        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&gb.pv_done), (li - 1) & 1, abort_flag, &g_attn_tc_error, 3));
+                        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&gb.pv_done), (li - 1) & 1, abort_flag, err_word, 3, wait_limit));
                         if (!ok) break;
                         if (__any_sync(0xffffffffu, need)) {
                             fence_after();
@@ -370,7 +378,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                     if (lane == 0) mbar_arrive(smem_u32(&gb.p_ready));
                 }
                 if (ok && n_own > 0)
-                    ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&gb.pv_done), (n_own - 1) & 1, abort_flag, &g_attn_tc_error, 3));
+                    ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&gb.pv_done), (n_own - 1) & 1, abort_flag, err_word, 3, wait_limit));
                 if (ok && n_own > 0) {
                     fence_after();
                     const float inv = 1.0f / fmaxf(l, 1e-30f);
@@ -429,7 +437,7 @@ int launch(const AttentionParams& p, const StepTokens& b, const PagedCache& c, c
         return SPITE_LAUNCH_FAILED;
     const long long items = (long long)n_blocks * nkv;
     const int grid = (int)(items < n_sm ? items : n_sm);
-    SPITE_LAUNCH(k, grid, THREADS, smem, st, mq, mk, mv, p, b, c, x, box_tokens, n_blocks);
+    SPITE_LAUNCH(k, grid, THREADS, smem, st, mq, mk, mv, p, b, c, x, box_tokens, n_blocks, s_waits);
     return spite_launch_status();
 }
 
@@ -456,12 +464,4 @@ SPITE_API int spite_paged_attention_tc(const AttentionParams* p, const StepToken
     if (b->n_tokens == 0 || n_blocks == 0) return SPITE_OK;
     cudaStream_t st = (cudaStream_t)stream;
     return c->head_dim == 64 ? launch<1>(*p, *b, *c, *x, n_blocks, n_sm, st) : launch<2>(*p, *b, *c, *x, n_blocks, n_sm, st);
-}
-
-// Error code recorded by a block that gave up waiting (0: none); reading it clears it.
-SPITE_API int spite_attention_tc_error() {
-    int v = 0, zero = 0;
-    if (cudaMemcpyFromSymbol(&v, g_attn_tc_error, sizeof(int)) != cudaSuccess) return -1;
-    if (v) cudaMemcpyToSymbol(g_attn_tc_error, &zero, sizeof(int));
-    return v;
 }

@@ -3,10 +3,10 @@
 // model's activation type.
 #include "common.cuh"
 
-// h[m, :] = table[token[m], :]            (crates/spite-models/src/llama/llama4.rs:118-119)
+// h[m, :] = table[token[m], :] * scale    (crates/spite-models/src/llama/llama4.rs:118-119; scale 1 there)
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ tokens,
-                             float* __restrict__ h, int d, int vocab) {
+                             float* __restrict__ h, int d, int vocab, float scale) {
     pdl_wait();
     pdl_launch_dependents();
     const int m = blockIdx.x;
@@ -17,7 +17,7 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
         return;
     }
     const T* row = table + (size_t)tok * d;
-    for (int i = threadIdx.x; i < d; i += blockDim.x) out[i] = to_f32(row[i]);
+    for (int i = threadIdx.x; i < d; i += blockDim.x) out[i] = to_f32(row[i]) * scale;
 }
 
 // y[i, :] = x[r, :] * rsqrt(mean(x[r]^2) + eps) * gain      r = rows ? rows[i] : i
@@ -80,6 +80,17 @@ __global__ void rms_norm_kernel(const float* __restrict__ x, const float* __rest
     for (int c = threadIdx.x; c < d; c += blockDim.x) out[c] = from_f32<T>(in[c] * scale * gain[c]);
 }
 
+// logits = cap * tanh(logits * scale / cap), or logits * scale without a cap (cap <= 0)
+__global__ void transform_logits_kernel(float* __restrict__ logits, long long n, float scale, float cap) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const float inv_cap = cap > 0.f ? 1.0f / cap : 0.f;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const float v = logits[i] * scale;
+        logits[i] = cap > 0.f ? cap * tanhf(v * inv_cap) : v;
+    }
+}
+
 // dst[i, :] = src[idx[i], :]   (rows of activations brought into expert order), 16 bytes per thread and step
 __global__ void gather_rows_kernel(const uint4* __restrict__ src, const int* __restrict__ idx,
                                    uint4* __restrict__ dst, int row_vecs) {
@@ -101,16 +112,25 @@ SPITE_API int spite_gather_rows(const void* src, const int* idx, void* dst, int 
     return spite_launch_status();
 }
 
+SPITE_API int spite_transform_logits(float* logits, long long n, float scale, float softcap, void* stream) {
+    if (!logits || n < 0 || !(scale == scale) || !(softcap == softcap)) return SPITE_BAD_ARG;
+    if (n == 0) return SPITE_OK;
+    const long long blocks = (n + 255) / 256;
+    SPITE_LAUNCH(transform_logits_kernel, (int)(blocks < 4096 ? blocks : 4096), 256, 0, (cudaStream_t)stream, logits, n,
+                 scale, softcap);
+    return spite_launch_status();
+}
+
 SPITE_API int spite_embed(int dtype, const void* table, const int* tokens, float* h,
-                          int n_tokens, int d, int vocab, void* stream) {
-    if (!table || !tokens || !h || n_tokens < 0 || d <= 0 || vocab <= 0) return SPITE_BAD_ARG;
+                          int n_tokens, int d, int vocab, float scale, void* stream) {
+    if (!table || !tokens || !h || n_tokens < 0 || d <= 0 || vocab <= 0 || !(scale == scale)) return SPITE_BAD_ARG;
     if (n_tokens == 0) return SPITE_OK;
     cudaStream_t st = (cudaStream_t)stream;
     const int threads = d >= 1024 ? 256 : 128;
     if (dtype == SPITE_DT_F32)
-        SPITE_LAUNCH(embed_kernel<float>, n_tokens, threads, 0, st, (const float*)table, tokens, h, d, vocab);
+        SPITE_LAUNCH(embed_kernel<float>, n_tokens, threads, 0, st, (const float*)table, tokens, h, d, vocab, scale);
     else if (dtype == SPITE_DT_BF16)
-        SPITE_LAUNCH(embed_kernel<__nv_bfloat16>, n_tokens, threads, 0, st, (const __nv_bfloat16*)table, tokens, h, d, vocab);
+        SPITE_LAUNCH(embed_kernel<__nv_bfloat16>, n_tokens, threads, 0, st, (const __nv_bfloat16*)table, tokens, h, d, vocab, scale);
     else
         return SPITE_BAD_ARG;
     return spite_launch_status();

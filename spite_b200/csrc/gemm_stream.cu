@@ -33,6 +33,10 @@ constexpr int MAX_STAGES = 12;
 constexpr int MAX_GROUPS = 1024;
 
 __device__ int g_stream_error = 0;
+}  // namespace
+// 1: the producer waited for a free stage, 2: a consumer waited for a stage.  (`extra_tx` is not used here.)
+SPITE_WAIT_CONTROLS(gemm_stream, g_stream_error)
+namespace {
 
 struct Tail {
     unsigned long long full[MAX_STAGES], empty[MAX_STAGES];
@@ -72,7 +76,7 @@ struct Item {
 template <int NT, int EPI>
 __global__ void __launch_bounds__(THREADS, 3)
 gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const GemmParams p, const int n_stages,
-                   const int n_splits, float* __restrict__ scratch, int* __restrict__ tickets) {
+                   const int n_splits, float* __restrict__ scratch, int* __restrict__ tickets, const WaitControl waits) {
     constexpr bool DUAL = (EPI == EPI_SWIGLU);
     constexpr int COLS = DUAL ? ROWS / 2 : ROWS;                 // output columns of a tile
     constexpr int X_BYTES = NT * BK * 2;                         // 1 or 2 KiB
@@ -88,6 +92,8 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const GemmParams p
     const int num_kb = p.K / BK;
     const int w_rows = DUAL ? 2 * p.N : p.N;
     volatile int* abort_flag = &tail->abort_flag;
+    int* const err_word = waits.error_word ? waits.error_word : &g_stream_error;
+    const long long wait_limit = waits.limit_cycles;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < n_stages; ++s) { mbar_init(smem_u32(&tail->full[s]), 33); mbar_init(smem_u32(&tail->empty[s]), CONSUMERS); }
@@ -171,7 +177,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const GemmParams p
             }
             const int wy = it.group * w_rows + it.n0;
             for (int kb = it.kb0; kb < it.kb1; ++kb, s = (s + 1 == n_stages ? 0 : s + 1), ph ^= (s == 0)) {
-                if (lane == 0) ok = mbar_wait(smem_u32(&tail->empty[s]), ph ^ 1, abort_flag, &g_stream_error, 1);
+                if (lane == 0) ok = mbar_wait(smem_u32(&tail->empty[s]), ph ^ 1, abort_flag, err_word, 1, wait_limit);
                 ok = __shfl_sync(0xffffffffu, ok, 0);
                 if (!ok) break;
                 const unsigned bar = smem_u32(&tail->full[s]), dst = smem_u32(smem + s * STAGE);
@@ -212,7 +218,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const GemmParams p
 #pragma unroll
                 for (int e = 0; e < 4; ++e) acc[j][e] = 0.f;
             for (int kb = it.kb0; kb < it.kb1; ++kb, s = (s + 1 == n_stages ? 0 : s + 1), ph ^= (s == 0)) {
-                ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&tail->full[s]), ph, abort_flag, &g_stream_error, 2));
+                ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&tail->full[s]), ph, abort_flag, err_word, 2, wait_limit));
                 if (!ok) break;
                 const unsigned wbase = smem_u32(smem + s * STAGE), xbase = wbase + W_BYTES;
 #pragma unroll
@@ -327,7 +333,7 @@ int launch(const GemmParams& p, int n_blocks, int smem_budget, int n_splits, flo
     const int cols = DUAL ? ROWS / 2 : ROWS;
     const long long tiles = (long long)((p.N + cols - 1) / cols) * (p.group_offsets ? (p.n_groups < p.M ? p.n_groups : p.M) : 1) * n_splits;
     const int grid = (int)(tiles < n_blocks ? tiles : n_blocks);
-    SPITE_LAUNCH(k, grid, THREADS, smem, st, mw, p, n_stages, n_splits, scratch, tickets);
+    SPITE_LAUNCH(k, grid, THREADS, smem, st, mw, p, n_stages, n_splits, scratch, tickets, s_waits);
     return spite_launch_status();
 }
 
@@ -368,13 +374,4 @@ SPITE_API int spite_gemm_stream(const GemmParams* p, int max_rows_per_group, int
                                 : launch<16, EPI_SWIGLU>(*p, n_blocks, smem_budget, n_splits, scratch, tickets, st);
     }
 #undef SPITE_STREAM_CASE
-}
-
-// Error code recorded by a block that gave up waiting (0: none); reading it clears it.
-// 1: the producer waited for a free stage, 2: a consumer waited for a stage.
-SPITE_API int spite_gemm_stream_error() {
-    int v = 0, zero = 0;
-    if (cudaMemcpyFromSymbol(&v, g_stream_error, sizeof(int)) != cudaSuccess) return -1;
-    if (v) cudaMemcpyToSymbol(g_stream_error, &zero, sizeof(int));
-    return v;
 }

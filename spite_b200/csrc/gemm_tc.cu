@@ -18,8 +18,9 @@
 // scattered through c_rows), SwiGLU with a per-row scale.
 //
 // Stages, accumulators and roles hand over through mbarriers.  Every wait is bounded:
-// after about two seconds a waiter raises an abort flag that all roles poll, records an
-// error code that the host reads with spite_gemm_tc_error(), waits for its own copies in
+// after its limit (about two seconds unless spite_gemm_tc_configure_waits says otherwise) a waiter
+// raises an abort flag that all roles poll, records an error code (read by spite_gemm_tc_error(),
+// or from the word the caller named), waits for its own copies in
 // flight, and the block leaves through the common exit, where TMEM is freed.
 //
 // Rows of A are contiguous (a grouped product gets its rows gathered into expert order
@@ -39,6 +40,11 @@ constexpr int THREADS = 192;
 constexpr int MAX_LISTED = 1024;                         // row tiles of a grouped product kept as a list in shared memory
 
 __device__ int g_tc_error = 0;
+}  // namespace
+// 1: loader waited for a free stage, 2: tensor-core issue waited for a tile, 3: epilogue waited
+// for an accumulator, 4: tensor-core issue waited for a free accumulator.
+SPITE_WAIT_CONTROLS(gemm_tc, g_tc_error)
+namespace {
 
 struct SharedTail {
     unsigned long long full[MAX_STAGES];
@@ -78,7 +84,8 @@ __device__ __forceinline__ Tile tile_at(const GemmParams& p, const SharedTail* t
 template <int EPI>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-               const GemmParams p, const int bnh, const int max_row_tiles, const int col_tiles, const int n_stages) {
+               const GemmParams p, const int bnh, const int max_row_tiles, const int col_tiles, const int n_stages,
+               const WaitControl waits) {
     constexpr bool DUAL = (EPI == EPI_SWIGLU);
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -92,6 +99,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int cols_per_tile = DUAL ? bnh : 2 * bnh;          // output columns of one tile
     const unsigned stage_tx = A_BYTES + 2 * bnh * BK * 2;   // bytes of one stage, also its stride in the ring
     volatile int* abort_flag = &tail->abort_flag;
+    int* const err_word = waits.error_word ? waits.error_word : &g_tc_error;
+    const long long wait_limit = waits.limit_cycles;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < n_stages; ++s) { mbar_init(smem_u32(&tail->full[s]), 1); mbar_init(smem_u32(&tail->empty[s]), 1); }
@@ -151,11 +160,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 const int wy0 = t.group * w_rows + t.n0;
                 const int wy1 = DUAL ? t.group * w_rows + p.N + t.n0 : wy0 + bnh;
                 for (int kb = 0; kb < num_kb; ++kb, ++it, s = (s + 1 == n_stages ? 0 : s + 1), ph ^= (s == 0)) {
-                    ok = mbar_wait(smem_u32(&tail->empty[s]), ph ^ 1, abort_flag, &g_tc_error, 1);
+                    ok = mbar_wait(smem_u32(&tail->empty[s]), ph ^ 1, abort_flag, err_word, 1, wait_limit);
                     if (!ok) break;
                     const unsigned bar = smem_u32(&tail->full[s]);
                     const unsigned dst = smem_u32(smem + s * stage_tx);
-                    mbar_expect_tx(bar, stage_tx);
+                    mbar_expect_tx(bar, stage_tx + (it == 0 ? waits.extra_tx : 0));
                     tma_load_2d(dst, &map_a, kb * BK, t.row0, bar);
                     if (w_once) {
                         tma_load_2d_hint(dst + A_BYTES, &map_w, kb * BK, wy0, bar, w_policy);
@@ -169,7 +178,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             if (*abort_flag) {
                 // copies in flight must land before the block gives its shared memory back
                 for (int j = max(0, it - n_stages); j < it; ++j)
-                    mbar_drain(smem_u32(&tail->full[j % n_stages]), (j / n_stages) & 1);
+                    mbar_drain(smem_u32(&tail->full[j % n_stages]), (j / n_stages) & 1, wait_limit);
             }
         }
     } else if (warp == 1) {
@@ -183,12 +192,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 const Tile t = tile_at(p, tail, listed, idx, row_tiles, cols_per_tile);
                 if (!t.ok) continue;
                 const int buf = lt & 1;
-                ok = mbar_wait(smem_u32(&tail->acc_empty[buf]), ((lt >> 1) & 1) ^ 1, abort_flag, &g_tc_error, 4);
+                ok = mbar_wait(smem_u32(&tail->acc_empty[buf]), ((lt >> 1) & 1) ^ 1, abort_flag, err_word, 4, wait_limit);
                 if (!ok) break;
                 fence_after();
                 const unsigned d_tmem = tmem + buf * ACC_COLS;
                 for (int kb = 0; kb < num_kb; ++kb, s = (s + 1 == n_stages ? 0 : s + 1), ph ^= (s == 0)) {
-                    ok = mbar_wait(smem_u32(&tail->full[s]), ph, abort_flag, &g_tc_error, 2);
+                    ok = mbar_wait(smem_u32(&tail->full[s]), ph, abort_flag, err_word, 2, wait_limit);
                     if (!ok) break;
                     fence_after();
                     const unsigned a_addr = smem_u32(smem + s * stage_tx);
@@ -212,7 +221,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const Tile t = tile_at(p, tail, listed, idx, row_tiles, cols_per_tile);
             if (!t.ok) continue;
             const int buf = lt & 1;
-            ok = mbar_wait(smem_u32(&tail->acc_full[buf]), (lt >> 1) & 1, abort_flag, &g_tc_error, 3);
+            ok = mbar_wait(smem_u32(&tail->acc_full[buf]), (lt >> 1) & 1, abort_flag, err_word, 3, wait_limit);
             if (!ok) break;
             fence_after();
             drain_accumulator_row<EPI>(p, t.row0 + r, r < t.rows, t.n0, cols_per_tile, bnh,
@@ -276,7 +285,7 @@ int launch(const GemmParams& p, int n_blocks, cudaStream_t st) {
     if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
         return SPITE_LAUNCH_FAILED;
     const int grid = (int)(total < n_blocks ? total : n_blocks);
-    SPITE_LAUNCH(k, grid, THREADS, smem, st, ma, mw, p, bnh, row_tiles, (int)(total / row_tiles), n_stages);
+    SPITE_LAUNCH(k, grid, THREADS, smem, st, ma, mw, p, bnh, row_tiles, (int)(total / row_tiles), n_stages, s_waits);
     return spite_launch_status();
 }
 
@@ -300,14 +309,4 @@ SPITE_API int spite_gemm_tc(const GemmParams* p, int n_blocks, void* stream) {
         case EPI_ADD_F32: return launch<EPI_ADD_F32>(*p, n_blocks, st);
         default: return launch<EPI_SWIGLU>(*p, n_blocks, st);
     }
-}
-
-// Error code recorded by a block that gave up waiting (0: none); reading it clears it.
-// 1: loader waited for a free stage, 2: tensor-core issue waited for a tile, 3: epilogue waited
-// for an accumulator, 4: tensor-core issue waited for a free accumulator.
-SPITE_API int spite_gemm_tc_error() {
-    int v = 0, zero = 0;
-    if (cudaMemcpyFromSymbol(&v, g_tc_error, sizeof(int)) != cudaSuccess) return -3;
-    if (v) cudaMemcpyToSymbol(g_tc_error, &zero, sizeof(int));
-    return v;
 }

@@ -38,6 +38,11 @@ constexpr int THREADS = 192;
 constexpr int MAX_LISTED = 1024;                         // row tiles of a grouped product kept as a list in shared memory
 
 __device__ int g_pair_error = 0;
+}  // namespace
+// 1: loader waited for a free stage, 2: tensor-core issue waited for a stage, 3: epilogue waited
+// for an accumulator, 4: tensor-core issue waited for a free accumulator.  (`extra_tx` is not used here.)
+SPITE_WAIT_CONTROLS(gemm_tc_pair, g_pair_error)
+namespace {
 
 struct SharedTail {
     unsigned long long full[MAX_STAGES];                 // used in the leader
@@ -101,7 +106,8 @@ __device__ __forceinline__ void tmem_free_pair(unsigned base, unsigned cols) {
 template <int EPI>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-                    const GemmParams p, const int bnh, const int dense_row_tiles, const int col_tiles, const int n_stages) {
+                    const GemmParams p, const int bnh, const int dense_row_tiles, const int col_tiles, const int n_stages,
+                    const WaitControl waits) {
     constexpr bool DUAL = (EPI == EPI_SWIGLU);
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -116,6 +122,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const int cols_per_tile = DUAL ? bnh : 2 * bnh;          // output columns of one tile
     const unsigned stage_bytes = A_BYTES + bnh * BK * 2;    // what this block loads per stage, also the ring's stride
     volatile int* abort_flag = &tail->abort_flag;
+    int* const err_word = waits.error_word ? waits.error_word : &g_pair_error;
+    const long long wait_limit = waits.limit_cycles;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < n_stages; ++s) { mbar_init(smem_u32(&tail->full[s]), 1); mbar_init(smem_u32(&tail->empty[s]), 1); }
@@ -179,7 +187,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 const int row0 = t.row0 + (int)rank * BM;
                 const int wy = t.group * w_rows + (DUAL ? (rank ? p.N + t.n0 : t.n0) : t.n0 + (int)rank * bnh);
                 for (int kb = 0; kb < num_kb; ++kb, ++it, s = (s + 1 == n_stages ? 0 : s + 1), ph ^= (s == 0)) {
-                    ok = mbar_wait(smem_u32(&tail->empty[s]), ph ^ 1, abort_flag, &g_pair_error, 1);
+                    ok = mbar_wait(smem_u32(&tail->empty[s]), ph ^ 1, abort_flag, err_word, 1, wait_limit);
                     if (!ok) break;
                     const unsigned bar = in_block(smem_u32(&tail->full[s]), 0);
                     const unsigned dst = smem_u32(smem + s * stage_bytes);
@@ -198,12 +206,12 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             bool ok = true;
             for (int idx = pair; idx < total_tiles && ok; idx += n_pairs) {
                 const int buf = lt & 1;
-                ok = mbar_wait(smem_u32(&tail->acc_empty[buf]), ((lt >> 1) & 1) ^ 1, abort_flag, &g_pair_error, 4);
+                ok = mbar_wait(smem_u32(&tail->acc_empty[buf]), ((lt >> 1) & 1) ^ 1, abort_flag, err_word, 4, wait_limit);
                 if (!ok) break;
                 fence_after();
                 const unsigned d_tmem = tmem + buf * ACC_COLS;
                 for (int kb = 0; kb < num_kb; ++kb, s = (s + 1 == n_stages ? 0 : s + 1), ph ^= (s == 0)) {
-                    ok = mbar_wait(smem_u32(&tail->full[s]), ph, abort_flag, &g_pair_error, 2);
+                    ok = mbar_wait(smem_u32(&tail->full[s]), ph, abort_flag, err_word, 2, wait_limit);
                     if (!ok) break;
                     fence_after();
                     const unsigned a_addr = smem_u32(smem + s * stage_bytes);
@@ -226,7 +234,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         for (int idx = pair; idx < total_tiles && ok; idx += n_pairs) {
             const Tile t = tile_at(idx);
             const int buf = lt & 1;
-            ok = mbar_wait(smem_u32(&tail->acc_full[buf]), (lt >> 1) & 1, abort_flag, &g_pair_error, 3);
+            ok = mbar_wait(smem_u32(&tail->acc_full[buf]), (lt >> 1) & 1, abort_flag, err_word, 3, wait_limit);
             if (!ok) break;
             fence_after();
             drain_accumulator_row<EPI>(p, t.row0 + (int)rank * BM + r, (int)rank * BM + r < t.rows, t.n0, cols_per_tile, bnh,
@@ -307,7 +315,7 @@ int launch(const GemmParams& p, int n_pairs, cudaStream_t st) {
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = spite_pdl_enabled() ? 2 : 1;
-    (void)cudaLaunchKernelEx(&cfg, k, ma, mw, p, bnh, row_tiles, col_tiles, n_stages);
+    (void)cudaLaunchKernelEx(&cfg, k, ma, mw, p, bnh, row_tiles, col_tiles, n_stages, s_waits);
     return spite_launch_status();
 }
 
@@ -331,14 +339,4 @@ SPITE_API int spite_gemm_tc_pair(const GemmParams* p, int n_pairs, void* stream)
         case EPI_ADD_F32: return launch<EPI_ADD_F32>(*p, n_pairs, st);
         default: return launch<EPI_SWIGLU>(*p, n_pairs, st);
     }
-}
-
-// Error code recorded by a block that gave up waiting (0: none); reading it clears it.
-// 1: loader waited for a free stage, 2: tensor-core issue waited for a stage, 3: epilogue waited
-// for an accumulator, 4: tensor-core issue waited for a free accumulator.
-SPITE_API int spite_gemm_tc_pair_error() {
-    int v = 0, zero = 0;
-    if (cudaMemcpyFromSymbol(&v, g_pair_error, sizeof(int)) != cudaSuccess) return -1;
-    if (v) cudaMemcpyToSymbol(g_pair_error, &zero, sizeof(int));
-    return v;
 }

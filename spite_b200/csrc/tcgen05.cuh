@@ -3,15 +3,26 @@
 // instruction descriptors of kind::f16 products with bfloat16 inputs.
 //
 // Every wait on an mbarrier is bounded: a waiter that runs out of time raises the block's abort
-// flag (which all waiters poll) and records a code in the library's error word, so that a kernel
-// always reaches its common exit, where it frees its tensor memory.
+// flag (which all waiters poll) and records a code in an error word, so that a kernel always
+// reaches its common exit, where it frees its tensor memory.  The limit and the error word are
+// launch arguments (`WaitControl`), kept per library and set with its `..._configure_waits`.
 #pragma once
 #include "common.cuh"
 #include <cuda.h>
 
 namespace tc {
 
-constexpr long long WAIT_CYCLES = 4000000000ll;          // about two seconds
+constexpr long long WAIT_CYCLES = 4000000000ll;          // the default limit of a wait: about two seconds
+
+// How the waits of one launch behave.
+struct WaitControl {
+    long long limit_cycles;     // a wait gives up after this many clock cycles
+    int* error_word;            // where the first give-up of a launch records its code (device memory, or host
+                                // memory that the device can write); null: the library's own word
+    int extra_tx;               // bytes added to what a loader announces for its first stage.  Always 0 in
+                                // use; a test sets it so that one barrier never completes and the waits on
+                                // it run out, which is the one way to reach the give-up path on purpose.
+};
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
 
@@ -36,7 +47,7 @@ __device__ __forceinline__ bool mbar_try(unsigned bar, unsigned parity) {
 // flag and the clock are looked at once in 32 polls, so that a waiting warp takes few issue slots
 // from the warps that compute (mbarrier.try_wait itself suspends the thread for a while).
 __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatile int* abort_flag, int* error_word,
-                                          int code) {
+                                          int code, long long limit_cycles) {
     if (mbar_try(bar, parity)) return true;
     const long long t0 = clock64();
     while (true) {
@@ -44,17 +55,20 @@ __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatil
         for (int i = 0; i < 32; ++i)
             if (mbar_try(bar, parity)) return true;
         if (*abort_flag) return false;
-        if (clock64() - t0 > WAIT_CYCLES) {
+        if (clock64() - t0 > limit_cycles) {
             *abort_flag = 1;
-            atomicCAS(error_word, 0, code);
+            // the first code stays; a plain store, because the word may lie in host memory
+            volatile int* w = error_word;
+            if (*w == 0) *w = code;
+            __threadfence_system();
             return false;
         }
     }
 }
 // Waits, without an abort flag, until a copy that is already in flight has landed (or time runs out).
-__device__ __forceinline__ void mbar_drain(unsigned bar, unsigned parity) {
+__device__ __forceinline__ void mbar_drain(unsigned bar, unsigned parity, long long limit_cycles) {
     const long long t0 = clock64();
-    while (!mbar_try(bar, parity) && clock64() - t0 < WAIT_CYCLES) {}
+    while (!mbar_try(bar, parity) && clock64() - t0 < limit_cycles) {}
 }
 
 __device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap* map, int x, int y, unsigned bar) {
@@ -237,3 +251,30 @@ static inline bool make_map(CUtensorMap* map, const void* base, int rank, const 
 }
 
 }  // namespace tc
+
+// The exported controls of a library whose kernels wait on mbarriers: `name` is the library's stem,
+// `own_word` its `__device__ int` error word.
+//   spite_<name>_configure_waits(limit_cycles, error_word, extra_tx)   later launches take these (<= 0 / null: defaults)
+//   spite_<name>_error()   waits for the device, returns the code a give-up left (0: none) and clears it
+#define SPITE_WAIT_CONTROLS(name, own_word)                                                              \
+    namespace { tc::WaitControl s_waits = {tc::WAIT_CYCLES, nullptr, 0}; }                                \
+    SPITE_API int spite_##name##_configure_waits(long long limit_cycles, int* error_word, int extra_tx) { \
+        if (extra_tx < 0 || extra_tx % 16) return SPITE_BAD_ARG;                                          \
+        s_waits.limit_cycles = limit_cycles > 0 ? limit_cycles : tc::WAIT_CYCLES;                         \
+        s_waits.error_word = error_word;                                                                  \
+        s_waits.extra_tx = extra_tx;                                                                      \
+        return SPITE_OK;                                                                                  \
+    }                                                                                                     \
+    SPITE_API int spite_##name##_error() {                                                                \
+        int v = 0, zero = 0;                                                                              \
+        if (cudaDeviceSynchronize() != cudaSuccess) return SPITE_LAUNCH_FAILED;                           \
+        if (s_waits.error_word) {                                                                         \
+            if (cudaMemcpy(&v, s_waits.error_word, sizeof(int), cudaMemcpyDefault) != cudaSuccess)        \
+                return SPITE_LAUNCH_FAILED;                                                               \
+            if (v) cudaMemcpy(s_waits.error_word, &zero, sizeof(int), cudaMemcpyDefault);                 \
+            return v;                                                                                     \
+        }                                                                                                 \
+        if (cudaMemcpyFromSymbol(&v, own_word, sizeof(int)) != cudaSuccess) return SPITE_LAUNCH_FAILED;   \
+        if (v) cudaMemcpyToSymbol(own_word, &zero, sizeof(int));                                          \
+        return v;                                                                                         \
+    }

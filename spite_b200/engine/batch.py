@@ -94,7 +94,12 @@ def build_step_batch(segments, tokens_per_segment, wants, tables_per_group, devi
 class StaticDecodeBatch:
     """The inputs of a decode step (one token per request) at fixed device addresses,
     so that the step's kernels can be captured once in a CUDA graph and replayed:
-    only the contents of these buffers change from step to step."""
+    only the contents of these buffers change from step to step.
+
+    The batch has room for `n_requests` rows; a step of fewer requests fills the
+    rest with copies of its first row.  A copy computes what the first row
+    computes and writes the same keys and values to the same place, so it changes
+    nothing and reads no weight or page that the step would not read anyway."""
 
     def __init__(self, n_requests: int, table_widths: list, device, context_bucket: int):
         S = self.S = n_requests
@@ -129,16 +134,24 @@ class StaticDecodeBatch:
         """Write this step's tokens, positions, slots and block tables and start the copy."""
         if self._copied is not None:
             self._copied.synchronize()          # the last step's copy has read the host buffer
+        n = len(segments)
+        if not 1 <= n <= self.S:
+            raise ValueError(f"a static batch of {self.S} rows cannot hold {n} requests")
+        pad = self.S - n
         buf = self.host.numpy()
-        buf[self._tok] = tokens
-        buf[self._pos] = [s.start_pos for s in segments]
-        buf[self._slots] = [s.slot for s in segments]
+        buf[self._tok] = list(tokens) + [tokens[0]] * pad
+        buf[self._pos] = [s.start_pos for s in segments] + [segments[0].start_pos] * pad
+        buf[self._slots] = [s.slot for s in segments] + [segments[0].slot] * pad
         for sl, w, tabs in zip(self._bt, self.widths, tables_per_group):
             bt = buf[sl].reshape(self.S, w)
             bt[:] = -1
             for i, t in enumerate(tabs):
                 bt[i, :len(t)] = t
-        self.batch.segments = list(segments)
+            if pad:
+                bt[n:] = bt[0]
+        first = segments[0]
+        self.batch.segments = list(segments) + [
+            Segment(first.req_id, first.slot, first.start_pos, 1, n + i, first.fresh) for i in range(pad)]
         self.dev.copy_(self.host, non_blocking=True)
         if self.dev.is_cuda:
             self._copied = torch.cuda.Event()

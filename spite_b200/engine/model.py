@@ -15,7 +15,7 @@ from ..config import ConfigError, ModelPlan, load_config
 from ..kernels import build as kernel_build
 from ..parts import BuildContext, ParamSpec, build_part
 from ..parts.base import _REGISTRIES
-from ..weights import load_bound_tensors
+from ..weights import bind_tensors, load_bound_tensors
 from ..weights.random_init import tensor_seed
 
 DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
@@ -87,7 +87,7 @@ class Model:
     def _check_caches(self):
         self._cache_specs = {}
         for call in self.plan.order:
-            req = self.blocks[call.layer].mixer.cache_request()
+            req = self.blocks[call.layer].cache_request()
             have = self._cache_specs.get(call.cache)
             if have is None:
                 self._cache_specs[call.cache] = req
@@ -158,6 +158,16 @@ class Model:
         tensors = load_bound_tensors(folder, config, device=model.device)
         return model.load_params(tensors)
 
+    @classmethod
+    def from_tensors(cls, config, checkpoint_tensors: dict, *, dtype="bfloat16", device="cuda:0", kernels=None,
+                     build=True) -> "Model":
+        """The same from checkpoint tensors in memory ({checkpoint tensor name: tensor}, the names and
+        layouts a model.safetensors of this architecture would have)."""
+        model = cls.from_config(config, dtype=dtype, device=device, kernels=kernels)
+        if build and kernels is None:
+            kernel_build.ensure_built(model.kernel_libraries())
+        return model.load_params(bind_tensors(config, checkpoint_tensors, device=model.device))
+
     # ------------------------------------------------------------------ running
     def forward(self, batch, storage) -> torch.Tensor:
         """Run the step's tokens through every layer of the run order; returns the
@@ -165,7 +175,7 @@ class Model:
         k = self.kernels
         p = self.plan
         h = torch.empty((batch.n_tokens, p.hidden_size), dtype=torch.float32, device=self.device)
-        k.embed(self.embed_table, batch.token_ids, h)
+        k.embed(self.embed_table, batch.token_ids, h, scale=p.embedding_scale)
         for call in p.order:
             self.blocks[call.layer].forward(h, batch, storage.layer_cache(call.cache, call.write_cache))
         R = batch.logit_rows.numel()
@@ -174,4 +184,6 @@ class Model:
             x = torch.empty((R, p.hidden_size), dtype=self.dtype, device=self.device)
             self.final_norm.forward(h, x, rows=batch.logit_rows)
             k.linear(x, self.head_weight, logits)
+            if p.logit_scale != 1.0 or p.logit_softcap is not None:
+                k.transform_logits(logits, scale=p.logit_scale, softcap=p.logit_softcap)
         return logits

@@ -41,6 +41,7 @@ import enum
 from collections import deque
 from dataclasses import dataclass, field
 
+from ..kernels.api import KernelTimeout
 from ..sampling.sampler import SampleRow, SamplingParams, is_plain_greedy
 from .executor import ContextOverflow, StepEntry
 
@@ -173,6 +174,7 @@ class Scheduler:
         """Wait for the ids of a step in flight and take them in."""
         if step.copied is not None:
             step.copied.synchronize()
+        self._check_kernels()
         tokens = step.host_tokens[:len(step.requests)].tolist()
         return [self._accept(r, int(tok)) for r, tok in zip(step.requests, tokens) if r.id not in step.dead]
 
@@ -292,6 +294,10 @@ class Scheduler:
             self.running.append(r)
         return StepPlan(entries, preempted, ended)
 
+    def _check_kernels(self):
+        """Called when the host has just waited for a step's ids, before it takes them in."""
+        self.engine.check()
+
     def _preempt(self, r: Request):
         if self.engine.is_live(r.id):
             self.engine.finish(r.id)
@@ -314,7 +320,21 @@ class Scheduler:
     # ------------------------------------------------------------------ running
     def step(self) -> list:
         """Plan and run one step; returns what each request produced (with decoding ahead: what was
-        read in this call, which is the step before the one launched)."""
+        read in this call, which is the step before the one launched).
+
+        If a kernel gave up a bounded wait (`KernelTimeout`, noticed when the host has a step's ids or
+        starts the next step), nothing of the steps in flight is kept: every running request gives its
+        pages back and returns to the queue with the tokens it had, to be recomputed when it runs again,
+        and the error goes to the caller, who may go on calling `step`."""
+        try:
+            return self._step()
+        except KernelTimeout:
+            self._in_flight = None
+            for r in list(reversed(self.running)):
+                self._preempt(r)
+            raise
+
+    def _step(self) -> list:
         outputs = []
         if self._in_flight is not None:
             ahead = self._launch_ahead()
@@ -347,6 +367,7 @@ class Scheduler:
             return outputs
         tokens, states = self.sampler.sample(
             logits, [SampleRow(r.params, r.all_tokens(), r.rng_state) for r in sampled])
+        self._check_kernels()                # the ids are on the host: the step has ended
         for r, tok, st in zip(sampled, tokens, states):
             r.rng_state = st
             outputs.append(self._accept(r, int(tok)))

@@ -37,6 +37,7 @@ def replay(engine: Engine, lines, out_dir: Path, log=sys.stdout):
             logits = engine.step(entries)
             if logits.shape[0]:
                 data = logits.detach().to("cpu").contiguous().numpy().astype("<f4", copy=False)
+                engine.check()                 # the logits are here: did every kernel of the step finish its work?
                 data.tofile(out_dir / f"{step}.f32")
         for req in rec.get("end", []):
             if engine.is_live(req):

@@ -1,3 +1,3 @@
-from .api import KernelError, KernelSet, Routing
+from .api import KernelError, KernelSet, KernelTimeout, Routing
 
-__all__ = ["KernelError", "KernelSet", "Routing"]
+__all__ = ["KernelError", "KernelSet", "KernelTimeout", "Routing"]

@@ -20,6 +20,12 @@ class KernelError(RuntimeError):
     """A kernel refused its arguments or could not be launched."""
 
 
+class KernelTimeout(KernelError):
+    """A kernel gave up a bounded wait and left its output incomplete: the results of the steps
+    since the last check cannot be trusted (ExecutorError in crates/spite-executor/src/lib.rs:88-100
+    is the counterpart: a typed error instead of wrong logits)."""
+
+
 @dataclass
 class Routing:
     """Result of `moe_route` for M tokens, E experts and k choices per token."""
@@ -36,9 +42,19 @@ class KernelSet:
     dtype: torch.dtype
     device: torch.device
 
+    def errors(self) -> dict:
+        """{kernel library: code} for every library one of whose kernels gave up a bounded wait since
+        the last call; reading clears.  Does not wait for the device: call it after a point at
+        which the host has waited for the step's results."""
+        return {}
+
     # ---- elementwise
-    def embed(self, table, token_ids, out_h):
-        """out_h[m, :] (float32) = table[token_ids[m], :] (T)."""
+    def embed(self, table, token_ids, out_h, *, scale=1.0):
+        """out_h[m, :] (float32) = table[token_ids[m], :] (T) * scale."""
+        raise NotImplementedError
+
+    def transform_logits(self, logits, *, scale=1.0, softcap=None):
+        """In place: logits *= scale; then, with a cap, logits = cap * tanh(logits / cap)."""
         raise NotImplementedError
 
     def rms_norm(self, h, gain, eps, out, rows=None):
@@ -67,9 +83,12 @@ class KernelSet:
         raise NotImplementedError
 
     # ---- attention
-    def qk_prepare(self, qkv, q_out, batch, cache, *, num_heads, inv_freq, qk_norm_eps, temperature):
+    def qk_prepare(self, qkv, q_out, batch, cache, *, num_heads, rotation, qk_norm, temperature):
         """Encode positions of q and k, normalise, scale q, append k and v to the cache.
-        qkv [M, (nq + 2 nkv) hd] T -> q_out [M, nq hd] T; `cache` is a `LayerCache`."""
+        qkv [M, (nq + 2 nkv) hd] T -> q_out [M, nq hd] T; `cache` is a `LayerCache`.
+        `rotation`: a `parts.Rotation` or None; `qk_norm`: a `parts.QkNorm` or None (RMS norm of
+        every q and k head, after the rotation unless it says before); `temperature`:
+        (floor, scale) or None: q *= ln(floor((pos + 1) / floor) + 1) * scale + 1."""
         raise NotImplementedError
 
     def paged_attention(self, q, out, batch, cache, *, num_heads, window, softmax_scale):

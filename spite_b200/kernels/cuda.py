@@ -12,7 +12,7 @@ import os
 import torch
 
 from . import build
-from .api import KernelError, KernelSet, Routing
+from .api import KernelError, KernelSet, KernelTimeout, Routing
 
 _DT = {torch.float32: 0, torch.bfloat16: 1}
 _STATUS = {-1: "malformed argument", -2: "size not supported by this kernel", -3: "launch failed"}
@@ -42,7 +42,9 @@ class PagedCache(C.Structure):
 
 class QkPrepareParams(C.Structure):
     _fields_ = [("qkv", C.c_void_p), ("q_out", C.c_void_p), ("inv_freq", C.c_void_p),
-                ("qk_norm_eps", C.c_float), ("temperature_floor", C.c_int),
+                ("q_gain", C.c_void_p), ("k_gain", C.c_void_p),
+                ("qk_norm_eps", C.c_float), ("norm_before_rotation", C.c_int), ("pairing", C.c_int),
+                ("rotary_dim", C.c_int), ("temperature_floor", C.c_int),
                 ("temperature_scale", C.c_float), ("num_heads", C.c_int), ("write_cache", C.c_int)]
 
 
@@ -65,6 +67,21 @@ class SampleParams(C.Structure):
                 ("out_tokens", C.c_void_p), ("vocab", C.c_int)]
 
 
+# Libraries whose kernels wait on mbarriers with a limit.  A kernel that gives up records a code in its
+# library's word of one small buffer in pinned host memory, which the device writes directly: the host
+# reads it after any point at which it has waited for a step's results, without another copy or wait.
+_WAITING_LIBRARIES = ("gemm_tc", "gemm_tc_pair", "gemm_stream", "attention_tc")
+_error_words = None          # pinned int32 [len(_WAITING_LIBRARIES)], one per process
+_configured: set = set()
+
+
+def _error_buffer():
+    global _error_words
+    if _error_words is None:
+        _error_words = torch.zeros(len(_WAITING_LIBRARIES), dtype=torch.int32).pin_memory()
+    return _error_words
+
+
 def _ptr(t):
     return None if t is None else t.data_ptr()
 
@@ -85,6 +102,7 @@ class CudaKernels(KernelSet):
         self._dt = _DT[dtype]
         self._libs = {}
         self.launches = 0          # kernels launched so far (for measurement reports)
+        self.attention_scratch_bytes = 0   # partial results of the last split-key attention call
         self.launches_by_library = collections.Counter()   # the same, by kernel library
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.use_tcgen05 = os.environ.get("SPITE_NO_TCGEN05", "") == ""
@@ -123,7 +141,34 @@ class CudaKernels(KernelSet):
         lib = self._libs.get(name)
         if lib is None:
             lib = self._libs[name] = build.load(name)
+            if name in _WAITING_LIBRARIES and name not in _configured:
+                word = _error_buffer().data_ptr() + 4 * _WAITING_LIBRARIES.index(name)
+                _check(self._configure_waits(lib, name, 0, word, 0), f"{name}: configure_waits")
+                _configured.add(name)
         return lib
+
+    @staticmethod
+    def _configure_waits(lib, name, limit_cycles, error_word, extra_tx):
+        return getattr(lib, f"spite_{name}_configure_waits")(C.c_longlong(limit_cycles), C.c_void_p(error_word),
+                                                             C.c_int(extra_tx))
+
+    def configure_waits(self, library: str, *, limit_cycles: int = 0, extra_tx: int = 0):
+        """Set the limit (clock cycles; 0: the default of about two seconds) of the bounded waits in
+        `library`'s kernels for later launches.  `extra_tx` exists for one test: it makes the first
+        barrier of every block of `gemm_tc` incomplete, so that the waits on it run out."""
+        lib = self._lib(library)
+        word = _error_buffer().data_ptr() + 4 * _WAITING_LIBRARIES.index(library)
+        _check(self._configure_waits(lib, library, limit_cycles, word, extra_tx), f"{library}: configure_waits")
+
+    def errors(self) -> dict:
+        words = _error_buffer()
+        out = {}
+        for i, name in enumerate(_WAITING_LIBRARIES):
+            code = int(words[i])
+            if code:
+                out[name] = code
+                words[i] = 0
+        return out
 
     @staticmethod
     def _stream():
@@ -137,15 +182,23 @@ class CudaKernels(KernelSet):
         return t
 
     # ------------------------------------------------------------------ elementwise
-    def embed(self, table, token_ids, out_h):
+    def embed(self, table, token_ids, out_h, *, scale=1.0):
         self._t(table, self.dtype, "table"); self._t(token_ids, torch.int32, "token_ids")
         self._t(out_h, torch.float32, "out_h")
         V, d = table.shape
         st = self._lib("elementwise").spite_embed(
             self._dt, C.c_void_p(table.data_ptr()), C.c_void_p(token_ids.data_ptr()),
-            C.c_void_p(out_h.data_ptr()), token_ids.numel(), d, V, self._stream())
+            C.c_void_p(out_h.data_ptr()), token_ids.numel(), d, V, C.c_float(scale), self._stream())
         self._count("elementwise", 1)
         _check(st, "embed")
+
+    def transform_logits(self, logits, *, scale=1.0, softcap=None):
+        self._t(logits, torch.float32, "logits")
+        st = self._lib("elementwise").spite_transform_logits(
+            C.c_void_p(logits.data_ptr()), C.c_longlong(logits.numel()), C.c_float(scale),
+            C.c_float(softcap or 0.0), self._stream())
+        self._count("elementwise", 1)
+        _check(st, "transform_logits")
 
     def rms_norm(self, h, gain, eps, out, rows=None):
         self._t(h, torch.float32, "h"); self._t(gain, torch.float32, "gain"); self._t(out, None, "out")
@@ -247,12 +300,18 @@ class CudaKernels(KernelSet):
 
     def attention_tc_error(self) -> int:
         """Error code left by a tcgen05 attention block that gave up waiting (0: none); clears it. Synchronises."""
-        return int(self._lib("attention_tc").spite_attention_tc_error())
+        torch.cuda.synchronize(self.device)
+        words = _error_buffer()
+        code, words[3] = int(words[3]), 0
+        return code
 
     def gemm_tc_error(self) -> int:
-        """Error code left by a tcgen05 block that gave up waiting (0: none); clears it. Synchronises."""
-        return (int(self._lib("gemm_tc").spite_gemm_tc_error()) or int(self._lib("gemm_tc_pair").spite_gemm_tc_pair_error())
-                or int(self._lib("gemm_stream").spite_gemm_stream_error()))
+        """Error code left by a product kernel's block that gave up waiting (0: none); clears it. Synchronises."""
+        torch.cuda.synchronize(self.device)
+        words = _error_buffer()
+        code = int(words[0]) or int(words[1]) or int(words[2])
+        words[:3] = 0
+        return code
 
     def linear(self, x, w, out, *, accumulate=False, row_scale=None):
         self._t(x, self.dtype, "x"); self._t(w, self.dtype, "w"); self._t(out, None, "out")
@@ -324,14 +383,29 @@ class CudaKernels(KernelSet):
         return PagedCache(kv=kv.data_ptr(), v_offset=kv.stride(0), n_pages=kv.shape[1],
                           page_size=kv.shape[3], num_kv_heads=kv.shape[2], head_dim=kv.shape[4])
 
-    def qk_prepare(self, qkv, q_out, batch, cache, *, num_heads, inv_freq, qk_norm_eps, temperature):
+    def qk_prepare(self, qkv, q_out, batch, cache, *, num_heads, rotation, qk_norm, temperature):
         self._t(qkv, self.dtype, "qkv"); self._t(q_out, self.dtype, "q_out")
-        if inv_freq is not None:
-            self._t(inv_freq, torch.float32, "inv_freq")
+        head_dim = cache.kv.shape[4]
+        inv_freq, pairing, rotary_dim = None, 0, head_dim
+        if rotation is not None:
+            inv_freq = self._t(rotation.inv_freq, torch.float32, "inv_freq")
+            pairing = {"neighbours": 0, "halves": 1}[rotation.pairing]
+            rotary_dim = int(rotation.rotary_dim or head_dim)
+            if inv_freq.numel() != rotary_dim // 2:
+                raise KernelError(f"qk_prepare: {inv_freq.numel()} frequencies for {rotary_dim} rotating elements")
+        eps, before, q_gain, k_gain = 0.0, 0, None, None
+        if qk_norm is not None:
+            eps, before = float(qk_norm.eps), int(qk_norm.before_rotation)
+            for g in (qk_norm.q_gain, qk_norm.k_gain):
+                if g is not None and (self._t(g, torch.float32, "gain").numel() != head_dim):
+                    raise KernelError("qk_prepare: a gain vector must have head_dim elements")
+            q_gain, k_gain = qk_norm.q_gain, qk_norm.k_gain
         floor, scale = (int(temperature[0]), float(temperature[1])) if temperature else (0, 0.0)
         p = QkPrepareParams(qkv=qkv.data_ptr(), q_out=q_out.data_ptr(), inv_freq=_ptr(inv_freq),
-                            qk_norm_eps=float(qk_norm_eps or 0.0), temperature_floor=floor,
-                            temperature_scale=scale, num_heads=num_heads, write_cache=int(cache.write))
+                            q_gain=_ptr(q_gain), k_gain=_ptr(k_gain), qk_norm_eps=eps,
+                            norm_before_rotation=before, pairing=pairing, rotary_dim=rotary_dim,
+                            temperature_floor=floor, temperature_scale=scale, num_heads=num_heads,
+                            write_cache=int(cache.write))
         b, c = self._step_tokens(batch, cache.group), self._paged(cache)
         st = self._lib("attention").spite_qk_prepare(self._dt, C.byref(p), C.byref(b), C.byref(c), self._stream())
         self._count("attention", 1)
@@ -402,9 +476,11 @@ class CudaKernels(KernelSet):
             splits = max(1, min(splits, tiles // 8, self.attention_max_splits))
             o_part = ml_part = None
             if splits > 1:
-                o_part = torch.empty((batch.n_tokens, num_heads, splits, c.head_dim), dtype=torch.float32,
+                # one row per token place of this kernel's blocks: tokens of longer segments take none
+                o_part = torch.empty((n_small * tpb, num_heads, splits, c.head_dim), dtype=torch.float32,
                                      device=q.device)
-                ml_part = torch.empty((batch.n_tokens, num_heads, splits, 2), dtype=torch.float32, device=q.device)
+                ml_part = torch.empty((n_small * tpb, num_heads, splits, 2), dtype=torch.float32, device=q.device)
+                self.attention_scratch_bytes = (o_part.numel() + ml_part.numel()) * 4
             x = AttnMmaExtra(cu_seqlens=batch.cu_seqlens.data_ptr(), o_part=_ptr(o_part), ml_part=_ptr(ml_part),
                              n_segments=len(batch.segments), tokens_per_block=tpb, n_splits=splits,
                              seg_min_tokens=0, seg_max_tokens=big_from - 1)

@@ -8,10 +8,12 @@ constants arrive as constructor parameters.
 Kinds of parts and what each must provide:
 
   norm           `forward(h, out, rows=None)`: out = norm(h[rows]) (h float32)
-  position       `frequencies(device)`: rotation frequencies or None
+  position       `rotation()`: a `Rotation` (frequencies, which elements pair up, how many
+                 leading elements of a head rotate) or None
   mixer          `cache_request()`, `forward(x, h, batch, cache)`: adds its output into h
   feed_forward   `forward(x, h, batch)`: adds its output into h
-  block          `forward(h, batch, cache)`: one layer on the residual stream h
+  block          `places` (name -> family of each part it is made of),
+                 `forward(h, batch, cache)`: one layer on the residual stream h
 
 `h` is the float32 residual stream [M, hidden]; `x` is a normalised copy in the
 activation type.
@@ -114,9 +116,34 @@ class Norm(Part):
         raise NotImplementedError
 
 
+@dataclass(frozen=True)
+class Rotation:
+    """How a position part wants q and k encoded; the mixer's prepare kernel does it.
+    Pair i of a head is rotated by position * inv_freq[i].  `pairing` says which two elements
+    pair i is: "neighbours" (2i, 2i+1) or "halves" (i, i + rotary_dim/2).  Only the first
+    `rotary_dim` elements of a head rotate (None: all of them)."""
+    inv_freq: torch.Tensor              # float32 [rotary_dim / 2] on the device
+    pairing: str = "neighbours"
+    rotary_dim: Optional[int] = None
+
+    def __post_init__(self):
+        if self.pairing not in ("neighbours", "halves"):
+            raise ConfigError(f"unknown pairing {self.pairing!r}; use 'neighbours' or 'halves'")
+
+
+@dataclass(frozen=True)
+class QkNorm:
+    """RMS norm of every q and k head inside the prepare kernel: after the rotation or before
+    it, with gain vectors [head_dim] (float32) or without."""
+    eps: float
+    before_rotation: bool = False
+    q_gain: Optional[torch.Tensor] = None
+    k_gain: Optional[torch.Tensor] = None
+
+
 class PositionEncoding(Part):
-    def frequencies(self) -> Optional[torch.Tensor]:
-        """float32 [head_dim / 2] rotation frequencies on the device, or None for no rotation."""
+    def rotation(self) -> Optional[Rotation]:
+        """How q and k are rotated, or None for no rotation."""
         raise NotImplementedError
 
 
@@ -135,5 +162,38 @@ class FeedForward(Part):
 
 
 class Block(Part):
+    """One layer.  An arrangement names its places and the family of the part that fills each
+    (`places`); places listed in `optional` may be left out of a `BlockSpec`.  The parts are
+    built here and become attributes of the block under their place names."""
+    places: dict = {}
+    optional: tuple = ()
+
+    def __init__(self, ctx: BuildContext, spec):
+        super().__init__(ctx)
+        unknown = sorted(set(spec.parts) - set(self.places))
+        missing = sorted(n for n in self.places if n not in spec.parts and n not in self.optional)
+        if unknown or missing:
+            raise ConfigError(f"block {self.kind!r} has the places {sorted(self.places)}: "
+                              f"missing {missing}, unknown {unknown}")
+        self._children = {}
+        for name, family in self.places.items():
+            part = build_part(family, spec.parts[name], ctx) if name in spec.parts else None
+            setattr(self, name, part)
+            if part is not None:
+                self._children[name] = part
+
+    def children(self) -> dict:
+        """{place: part} of the parts this layer is made of."""
+        return dict(self._children)
+
+    def cache_request(self):
+        """What one cache of this layer holds: its mixer's request (a layer has at most one
+        part that keeps a cache; two such mixers are two layers of the run order)."""
+        wants = [c.cache_request() for c in self._children.values() if isinstance(c, Mixer)]
+        wants = [w for w in wants if w != (None, None)]
+        if len(wants) > 1:
+            raise ConfigError(f"block {self.kind!r}: more than one part asks for a cache")
+        return wants[0] if wants else (None, None)
+
     def forward(self, h, batch, cache):
         raise NotImplementedError

@@ -9,22 +9,13 @@ from __future__ import annotations
 
 import torch
 
-from .base import Block, build_part, register_block
+from .base import Block, register_block
 
 
 @register_block("prenorm_residual")
 class PreNormResidual(Block):
     graph_safe = True
-    def __init__(self, ctx, spec):
-        super().__init__(ctx)
-        self.mixer_norm = build_part("norm", spec.mixer_norm, ctx)
-        self.mixer = build_part("mixer", spec.mixer, ctx)
-        self.ffn_norm = build_part("norm", spec.ffn_norm, ctx)
-        self.ffn = build_part("feed_forward", spec.ffn, ctx)
-
-    def children(self):
-        return {"mixer_norm": self.mixer_norm, "mixer": self.mixer,
-                "ffn_norm": self.ffn_norm, "ffn": self.ffn}
+    places = {"mixer_norm": "norm", "mixer": "mixer", "ffn_norm": "norm", "ffn": "feed_forward"}
 
     def forward(self, h, batch, cache):
         x = torch.empty(h.shape, dtype=self.ctx.dtype, device=h.device)

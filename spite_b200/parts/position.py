@@ -1,4 +1,5 @@
-"""Position encodings.  A position part only supplies rotation frequencies; the
+"""Position encodings.  A position part says how q and k are to be rotated (the
+frequencies, which elements of a head pair up, how many of them rotate); the
 rotation itself runs inside the mixer's prepare kernel, and keys are cached after
 it (crates/spite-models/src/llama/llama4.rs:155-186), so the cache and the
 attention kernel are the same for every encoding of this kind.
@@ -10,7 +11,7 @@ import math
 import torch
 
 from ..config.specs import ConfigError
-from .base import PositionEncoding, register_position
+from .base import PositionEncoding, Rotation, register_position
 
 
 def rotary_frequencies(head_dim: int, theta: float, scaling: dict | None) -> list[float]:
@@ -49,10 +50,10 @@ class RotaryInterleaved(PositionEncoding):
         if head_dim % 2:
             raise ConfigError("rotary encoding needs an even head_dim")
         f = rotary_frequencies(int(head_dim), float(theta), scaling)
-        self._freq = torch.tensor(f, dtype=torch.float64).to(torch.float32).to(ctx.device)
+        self._rotation = Rotation(torch.tensor(f, dtype=torch.float64).to(torch.float32).to(ctx.device), "neighbours")
 
-    def frequencies(self):
-        return self._freq
+    def rotation(self):
+        return self._rotation
 
 
 @register_position("no_position")
@@ -61,5 +62,5 @@ class NoPosition(PositionEncoding):
     def __init__(self, ctx):
         super().__init__(ctx)
 
-    def frequencies(self):
+    def rotation(self):
         return None

@@ -8,6 +8,11 @@ as matvec errors (dense.rs:226-233); the eager check here is deliberate.
 
 Storage rule: floating tensors are kept in bfloat16 (float16 is converted), a
 tensor the file stores in 32-bit floats stays 32-bit, integer tables become int32.
+
+A binding may name a layout transform that turns the checkpoint's tensor into the
+parameter (the stacked experts are stored input-major and are transposed, for
+instance).  Transforms are registered by name; another architecture adds its own
+with `register_weight_transform` (a permutation of rows, a slice of a fused tensor).
 """
 from __future__ import annotations
 
@@ -35,6 +40,55 @@ class WeightError(ValueError):
         for o in self.other:
             lines.append(f"  {o}")
         super().__init__("\n".join(lines))
+
+
+_TRANSFORMS: dict = {}
+
+
+def register_weight_transform(name: str):
+    """Decorator: `fn(tensor) -> tensor` becomes the transform `name` of a `WeightBinding`.  The function
+    gets the checkpoint tensor (already in its storage type, on the target device)."""
+    def deco(fn):
+        _TRANSFORMS[name] = fn
+        return fn
+    return deco
+
+
+def weight_transforms() -> list[str]:
+    return sorted(_TRANSFORMS)
+
+
+@register_weight_transform("transpose_last2")
+def _transpose_last2(t):
+    """[..., in, out] -> [..., out, in]"""
+    return t.transpose(-1, -2).contiguous()
+
+
+def apply_binding(binding, tensor, device="cpu"):
+    """The parameter that `binding` makes of the checkpoint tensor `tensor`."""
+    t = tensor.to(storage_dtype(tensor.dtype)).to(device)
+    if binding.transform is None:
+        return t
+    try:
+        fn = _TRANSFORMS[binding.transform]
+    except KeyError:
+        raise ValueError(f"unknown weight transform {binding.transform!r} for {binding.source}; "
+                         f"registered: {', '.join(weight_transforms())}") from None
+    return fn(t)
+
+
+def bind_tensors(config, source: dict, device="cpu", folder="(tensors in memory)") -> dict[str, torch.Tensor]:
+    """The same binding for checkpoint tensors that are already in memory: `source` maps checkpoint
+    tensor names (without prefix) to tensors.  One `WeightError` lists what does not fit."""
+    bindings = config.weight_bindings()
+    missing = [(b.source, b.source_shape) for b in bindings if b.source not in source]
+    wrong = [(b.source, tuple(source[b.source].shape), b.source_shape) for b in bindings
+             if b.source in source and tuple(source[b.source].shape) != tuple(b.source_shape)]
+    used = {b.source for b in bindings}
+    unexpected = sorted(n for n in source if n not in used)
+    if missing or wrong or unexpected:
+        raise WeightError(folder, missing, wrong, unexpected)
+    return {b.target: apply_binding(b, source[b.source], device) for b in bindings}
 
 
 def storage_dtype(file_dtype: torch.dtype) -> torch.dtype:
@@ -77,14 +131,7 @@ def load_bound_tensors(folder, config, device="cpu") -> dict[str, torch.Tensor]:
         out = {}
         for b in bindings:
             name = prefix + b.source
-            t = where[name].tensor(name)
-            t = t.to(storage_dtype(t.dtype))
-            t = t.to(device)
-            if b.transform == "transpose_last2":
-                t = t.transpose(-1, -2).contiguous()
-            elif b.transform is not None:
-                raise ValueError(f"unknown weight transform {b.transform!r}")
-            out[b.target] = t
+            out[b.target] = apply_binding(b, where[name].tensor(name), device)
         return out
     finally:
         for f in files:

@@ -32,13 +32,19 @@ def random_tensor(seed, name, shape, init, std, dtype, device="cpu"):
     return t.to(dtype)
 
 
+def random_checkpoint_tensors(config, seed: int = 0, std: float = 0.02, dtype=torch.bfloat16, device="cpu") -> dict:
+    """{checkpoint tensor name: tensor} for `config`, as `write_random_model` would store them (the same
+    values on the CPU; another device has its own generator).  For models that are too large to be worth
+    writing: `Model.from_tensors` binds them like a checkpoint read from disk."""
+    return {b.source: random_tensor(seed, b.source, b.source_shape, b.init, std, dtype, device)
+            for b in config.weight_bindings()}
+
+
 def write_random_model(folder, config, seed: int = 0, std: float = 0.02, dtype=torch.bfloat16):
     """Create `folder` with config.json and model.safetensors for `config`."""
     folder = Path(folder)
     folder.mkdir(parents=True, exist_ok=True)
-    tensors = {}
-    for b in config.weight_bindings():
-        tensors[b.source] = random_tensor(seed, b.source, b.source_shape, b.init, std, dtype)
+    tensors = random_checkpoint_tensors(config, seed, std, dtype)
     (folder / "config.json").write_text(json.dumps(config.to_dict(), indent=1))
     save_file(tensors, folder / "model.safetensors", metadata={"format": "pt", "seed": seed, "std": std})
     return folder

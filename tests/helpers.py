@@ -247,3 +247,24 @@ def compare_with_plain(results: dict, folder, requests: dict, tol: float):
             assert err <= tol, (f"request {r!r}, position {p} (first wrong one): error {err:.3e} of the "
                                 f"logit scale exceeds {tol:.1e}")
     return worst
+
+
+def assert_cuts_identical(results_by_cut: dict):
+    """float32 only: the logits of a (request, position) are the same bits whichever way the requests were
+    cut into steps, whatever else was in the batch and whichever pages held the keys (every kernel's order
+    of additions for one output element depends on that element's own data alone).  Names the first
+    position that differs and by how much."""
+    names = list(results_by_cut)
+    base = results_by_cut[names[0]]
+    compared = 0
+    for other in names[1:]:
+        res = results_by_cut[other]
+        for key in sorted(base.keys() & res.keys(), key=lambda k: (str(k[0]), k[1])):
+            compared += 1
+            if not torch.equal(base[key], res[key]):
+                diff = (base[key] - res[key]).abs()
+                raise AssertionError(
+                    f"request {key[0]!r}, position {key[1]} (first one that differs): {names[0]!r} and {other!r} "
+                    f"disagree in {int((diff > 0).sum())} of {diff.numel()} logits, by up to {float(diff.max()):.3e}")
+    assert compared > 0, "the cuts share no (request, position)"
+    return compared

@@ -24,8 +24,13 @@ class TorchReferenceKernels(KernelSet):
         self.acc = acc
 
     # ---- elementwise
-    def embed(self, table, token_ids, out_h):
-        out_h.copy_(table[token_ids.long()].float())
+    def embed(self, table, token_ids, out_h, *, scale=1.0):
+        out_h.copy_(table[token_ids.long()].float() * scale)
+
+    def transform_logits(self, logits, *, scale=1.0, softcap=None):
+        logits.mul_(scale)
+        if softcap:
+            logits.copy_(softcap * torch.tanh(logits / softcap))
 
     def rms_norm(self, h, gain, eps, out, rows=None):
         x = h if rows is None else h[rows.long()]
@@ -83,7 +88,7 @@ class TorchReferenceKernels(KernelSet):
             h[rows[lo:hi]] += self._mm(a[lo:hi], w_down[e]).to(h.dtype)
 
     # ---- attention
-    def qk_prepare(self, qkv, q_out, batch, cache, *, num_heads, inv_freq, qk_norm_eps, temperature):
+    def qk_prepare(self, qkv, q_out, batch, cache, *, num_heads, rotation, qk_norm, temperature):
         kv = cache.kv
         nkv, P, hd = kv.shape[2], kv.shape[3], kv.shape[4]
         nq = num_heads
@@ -91,20 +96,33 @@ class TorchReferenceKernels(KernelSet):
         x = qkv.to(self.acc).view(M, nq + 2 * nkv, hd)
         q, k, v = x[:, :nq], x[:, nq:nq + nkv], x[:, nq + nkv:]
         pos = batch.positions.long()
-        if inv_freq is not None:
+
+        def norm(t, gain):
+            t = t * (1.0 / torch.sqrt(t.pow(2).mean(-1, keepdim=True) + qk_norm.eps))
+            return t if gain is None else t * gain.to(t.device, self.acc)
+
+        if qk_norm is not None and qk_norm.before_rotation:
+            q, k = norm(q, qk_norm.q_gain), norm(k, qk_norm.k_gain)
+        if rotation is not None:
+            inv_freq = rotation.inv_freq.to(q.device)
+            rd = rotation.rotary_dim or hd
             ang = (pos.to(torch.float32)[:, None] * inv_freq[None, :].to(torch.float32)).to(self.acc)
             cos, sin = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
 
             def rot(t):
-                a, b = t[..., 0::2], t[..., 1::2]
-                o = torch.empty_like(t)
-                o[..., 0::2] = a * cos - b * sin
-                o[..., 1::2] = a * sin + b * cos
+                o = t.clone()
+                if rotation.pairing == "neighbours":
+                    a, b = t[..., 0:rd:2], t[..., 1:rd:2]
+                    o[..., 0:rd:2] = a * cos - b * sin
+                    o[..., 1:rd:2] = a * sin + b * cos
+                else:
+                    a, b = t[..., :rd // 2], t[..., rd // 2:rd]
+                    o[..., :rd // 2] = a * cos - b * sin
+                    o[..., rd // 2:rd] = a * sin + b * cos
                 return o
             q, k = rot(q), rot(k)
-        if qk_norm_eps:
-            q = q * (1.0 / torch.sqrt(q.pow(2).mean(-1, keepdim=True) + qk_norm_eps))
-            k = k * (1.0 / torch.sqrt(k.pow(2).mean(-1, keepdim=True) + qk_norm_eps))
+        if qk_norm is not None and not qk_norm.before_rotation:
+            q, k = norm(q, qk_norm.q_gain), norm(k, qk_norm.k_gain)
         if temperature:
             floor, scale = temperature
             fl = torch.div(pos + 1, int(floor), rounding_mode="floor").to(self.acc)

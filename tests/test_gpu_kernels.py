@@ -165,33 +165,73 @@ def fill_cache(kv, tables, seg_specs, k_all, v_all, page_size):
 
 
 @pytest.mark.parametrize("nq,nkv,hd,rope,norm,temp", [
-    (4, 2, 16, True, True, False), (6, 1, 32, True, False, False), (5, 5, 48, False, False, True),
-    (40, 8, 128, True, True, False), (3, 1, 256, False, False, False)])
+    (4, 2, 16, "neighbours", "after", False), (6, 1, 32, "neighbours", None, False), (5, 5, 48, None, None, True),
+    (40, 8, 128, "neighbours", "after", False), (3, 1, 256, None, None, False),
+    # what other encodings need of the same kernel: the two halves of a head pair up, only the first
+    # elements of a head rotate, the norm runs before the rotation, the norm has gains
+    (4, 2, 16, "halves", "after", False), (6, 2, 64, "halves", "before+gain", False),
+    (8, 2, 128, "halves:64", "after+gain", False), (5, 1, 48, "neighbours:24", "before", True),
+    (3, 3, 256, "halves", None, False), (2, 1, 80, "neighbours:40", "after+gain", False)])
 def test_qk_prepare(ks, nq, nkv, hd, rope, norm, temp):
+    from spite_b200.parts import QkNorm, Rotation
     P, n_pages = 16, 12
     specs = [(0, 19), (30, 1), (15, 3)]
     batch, tables = make_batch(specs, P, n_pages, 20, DEV)
     cpu_batch, _ = make_batch(specs, P, n_pages, 20, "cpu")
     M = batch.n_tokens
     qkv = rnd((M, (nq + 2 * nkv) * hd), ks.dtype, 21)
-    inv_freq = torch.tensor([10000.0 ** (-2.0 * i / hd) for i in range(hd // 2)], dtype=torch.float32) if rope else None
-    args = dict(num_heads=nq, inv_freq=None, qk_norm_eps=1e-5 if norm else None,
-                temperature=(8, 0.25) if temp else None)
+
+    def pieces(device):
+        rotation = qk_norm = None
+        if rope:
+            pairing, _, rd = rope.partition(":")
+            rd = int(rd) if rd else hd
+            inv_freq = torch.tensor([10000.0 ** (-2.0 * i / rd) for i in range(rd // 2)], dtype=torch.float32)
+            rotation = Rotation(inv_freq.to(device), pairing, rd if rd != hd else None)
+        if norm:
+            gains = [(rnd((hd,), torch.float32, 30 + i) + 1.5).to(device) if "gain" in norm else None for i in range(2)]
+            qk_norm = QkNorm(1e-5, norm.startswith("before"), gains[0], gains[1])
+        return dict(num_heads=nq, rotation=rotation, qk_norm=qk_norm, temperature=(8, 0.25) if temp else None)
     kv = torch.zeros((2, n_pages, nkv, P, hd), dtype=ks.dtype, device=DEV)
     q = torch.empty((M, nq * hd), dtype=ks.dtype, device=DEV)
-    ks.qk_prepare(qkv.to(DEV), q, batch, LayerCache(0, kv, None, P, True),
-                  **dict(args, inv_freq=None if inv_freq is None else inv_freq.to(DEV)))
+    ks.qk_prepare(qkv.to(DEV), q, batch, LayerCache(0, kv, None, P, True), **pieces(DEV))
     kv_ref = torch.zeros((2, n_pages, nkv, P, hd), dtype=torch.float64)
     q_ref = torch.empty((M, nq * hd), dtype=torch.float64)
-    ref_set(ks.dtype).qk_prepare(qkv, q_ref, cpu_batch, LayerCache(0, kv_ref, None, P, True),
-                                 **dict(args, inv_freq=inv_freq))
+    ref_set(ks.dtype).qk_prepare(qkv, q_ref, cpu_batch, LayerCache(0, kv_ref, None, P, True), **pieces("cpu"))
     close(q, q_ref, TOL[ks.dtype], "q")
     close(kv, kv_ref, TOL[ks.dtype], "cache")
     # a run that only reads the cache writes nothing
     kv2 = torch.zeros_like(kv)
-    ks.qk_prepare(qkv.to(DEV), q, batch, LayerCache(0, kv2, None, P, False),
-                  **dict(args, inv_freq=None if inv_freq is None else inv_freq.to(DEV)))
+    ks.qk_prepare(qkv.to(DEV), q, batch, LayerCache(0, kv2, None, P, False), **pieces(DEV))
     assert not kv2.any()
+
+
+def test_qk_prepare_halves_is_the_rotation_of_spite_rope(ks):
+    """`pairing="halves"` against the formula of crates/spite-rope/src/lib.rs:78-92 written out with loops:
+    for i < head_dim/2: freq = theta^(-2i/head_dim), a = pos * freq,
+    x[i] <- x[i] cos a - x[i + half] sin a,  x[i + half] <- x[i] sin a + x[i + half] cos a."""
+    from spite_b200.parts import Rotation
+    nq, nkv, hd, P, theta = 3, 1, 32, 16, 10000.0
+    batch, _ = make_batch([(5, 4)], P, 4, 4, DEV)
+    M = batch.n_tokens
+    qkv = rnd((M, (nq + 2 * nkv) * hd), ks.dtype, 5)
+    inv_freq = torch.tensor([theta ** (-2.0 * i / hd) for i in range(hd // 2)], dtype=torch.float32)
+    kv = torch.zeros((2, 4, nkv, P, hd), dtype=ks.dtype, device=DEV)
+    q = torch.empty((M, nq * hd), dtype=ks.dtype, device=DEV)
+    ks.qk_prepare(qkv.to(DEV), q, batch, LayerCache(0, kv, None, P, True), num_heads=nq,
+                  rotation=Rotation(inv_freq.to(DEV), "halves"), qk_norm=None, temperature=None)
+    x = qkv.double().view(M, nq + 2 * nkv, hd)
+    want = torch.empty((M, nq, hd), dtype=torch.float64)
+    half = hd // 2
+    for t in range(M):
+        pos = 5 + t
+        for h in range(nq):
+            for i in range(half):
+                a = pos * theta ** (-2.0 * i / hd)
+                x0, x1 = float(x[t, h, i]), float(x[t, h, i + half])
+                want[t, h, i] = x0 * math.cos(a) - x1 * math.sin(a)
+                want[t, h, i + half] = x0 * math.sin(a) + x1 * math.cos(a)
+    close(q.view(M, nq, hd), want, TOL[ks.dtype], "half-split rotation")
 
 
 @pytest.mark.parametrize("nq,nkv,hd,window,P", [

@@ -78,9 +78,9 @@ def test_norm_and_position_parts(ctx):
     spec = ctx["plan"].blocks[0].mixer.params["position"]
     pos = build_part("position", spec, ctx["build"])
     ref = plain.rotary_inv_freq(cfg, cfg["head_dim"])
-    assert torch.allclose(pos.frequencies().cpu(), ref, rtol=1e-6, atol=0)
+    assert torch.allclose(pos.rotation().inv_freq.cpu(), ref, rtol=1e-6, atol=0) and pos.rotation().pairing == "neighbours"
     nope = next(b for b in ctx["plan"].blocks if b.mixer.params["position"].kind == "no_position")
-    assert build_part("position", nope.mixer.params["position"], ctx["build"]).frequencies() is None
+    assert build_part("position", nope.mixer.params["position"], ctx["build"]).rotation() is None
 
 
 @pytest.mark.parametrize("kind", ["rotary", "nope"])
@@ -210,9 +210,9 @@ class ToyConfig:
         attn = PartSpec("paged_attention", dict(hidden_size=self.hidden, num_heads=3, num_kv_heads=3, head_dim=16,
                                                 position=PartSpec("no_position", {}), window=("sliding", 11)))
         ffn = PartSpec("dense_swiglu", {"hidden_size": self.hidden, "intermediate_size": 80})
-        blocks = (BlockSpec("prenorm_residual", norm, toy, norm, ffn),
-                  BlockSpec("prenorm_residual", norm, attn, norm, ffn),
-                  BlockSpec("prenorm_residual", norm, toy, norm, ffn))
+        def layer(mixer):
+            return BlockSpec("prenorm_residual", {"mixer_norm": norm, "mixer": mixer, "ffn_norm": norm, "ffn": ffn})
+        blocks = (layer(toy), layer(attn), layer(toy))
         return ModelPlan(self.hidden, self.vocab, blocks, tuple(LayerCall(i, i) for i in range(3)), norm,
                          tie_word_embeddings=True, max_positions=512)
 
@@ -328,7 +328,7 @@ class ToyRoutedConfig:
                                                 position=PartSpec("toy_harmonic_rotation", {"head_dim": 12, "base": 0.37}),
                                                 window=("full", 0)))
         ffn = PartSpec("toy_top2_with_bypass", {"hidden_size": self.hidden, "num_experts": 3, "expert_size": 24})
-        blocks = (BlockSpec("prenorm_residual", norm, attn, norm, ffn),) * 2
+        blocks = (BlockSpec("prenorm_residual", {"mixer_norm": norm, "mixer": attn, "ffn_norm": norm, "ffn": ffn}),) * 2
         return ModelPlan(self.hidden, self.vocab, blocks, tuple(LayerCall(i, i) for i in range(2)), norm,
                          tie_word_embeddings=True, max_positions=256)
 
@@ -352,8 +352,9 @@ def test_a_toy_routed_feed_forward_and_a_toy_position_encoding_are_registered_bu
             self._freq = torch.tensor([base / (i + 1) for i in range(head_dim // 2)], dtype=torch.float32,
                                       device=ctx.device)
 
-        def frequencies(self):
-            return self._freq
+        def rotation(self):
+            from spite_b200.parts import Rotation
+            return Rotation(self._freq, "neighbours")
 
     @register_feed_forward("toy_top2_with_bypass")
     class ToyTop2WithBypass(FeedForward):

@@ -61,13 +61,17 @@ def held_most(steps, page):
 
 def run_cuts(model, path, requests, cuts, tol, rng, pages):
     from spite_b200.engine import Engine
+    results = {}
     for name, steps in cuts.items():
         page = rng.choice(pages)
         engine = Engine(model, cache_tokens=held_most(steps, page), page_size=page, max_requests=4)
+        results[name] = H.run_steps(engine, steps)
         try:
-            H.compare_with_plain(H.run_steps(engine, steps), path, requests, tol)
+            H.compare_with_plain(results[name], path, requests, tol)
         except AssertionError as e:
             raise AssertionError(f"{name}, pages of {page}: {e}") from None
+    if model.dtype == torch.float32:
+        H.assert_cuts_identical(results)          # not only close to the plain implementation: the same bits
     if model.dtype == torch.bfloat16:
         assert model.kernels.gemm_tc_error() == 0 and model.kernels.attention_tc_error() == 0
 

@@ -314,3 +314,37 @@ def test_random_pools_and_budgets_always_make_progress(model, seed):
         assert s.finished[i].finish_reason is FinishReason.MAX_TOKENS, (seed, i)
         assert s.finished[i].output == plain_greedy(model, prompts[i], limits[i]), (seed, i)
     assert s.engine.cache.free_pages() == [s.engine.n_pages] * 2
+
+
+def test_a_kernel_that_gave_up_waiting_stops_the_step_and_nothing_is_lost(model):
+    """The kernel set reports that a kernel gave up a bounded wait (here: a stand-in that says so once).
+    The scheduler raises the typed error at the point where it has the ids, keeps none of them, sends the
+    running requests back to the queue with their pages freed, and the next calls produce the right tokens."""
+    from spite_b200.engine import KernelTimeout
+
+    class GivesUpOnce(TorchReferenceKernels):
+        pending = {}
+
+        def errors(self):
+            out, self.pending = self.pending, {}
+            return out
+
+    kernels = GivesUpOnce()
+    m = Model.from_folder(model.folder, dtype="float32", device="cpu", kernels=kernels)
+    for ahead in (False, True):
+        eng = Engine(m, cache_tokens=512, page_size=16, max_requests=4)
+        s = Scheduler(eng, Sampler(kernels), max_batch_tokens=64, decode_ahead=ahead)
+        for i in (1, 2):
+            s.submit(Request(i, PROMPTS[i], greedy(6)))
+        s.step(); s.step(); s.step()
+        before = {i: list(r.output) for i, r in ((r.id, r) for r in s.running)}
+        kernels.pending = {"gemm_tc": 2}
+        with pytest.raises(KernelTimeout, match="gemm_tc .code 2."):
+            while True:
+                s.step()
+        assert not s.running and [r.id for r in s.waiting] == [1, 2] and s._in_flight is None
+        assert {r.id: r.output for r in s.waiting} == before             # nothing of the bad step was kept
+        assert eng.cache.free_pages() == [eng.n_pages] * 2 and eng.cache.slots.n_free == 4
+        done = s.run_until_done()
+        for i in (1, 2):
+            assert done[i].output == plain_greedy(model, PROMPTS[i], 6) and done[i].preemptions == 1
