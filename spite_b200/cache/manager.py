@@ -264,6 +264,11 @@ class CacheManager:
             freed.append(out)
         return freed
 
+    def pending_pages(self, req_id) -> list[list[int]]:
+        """Per group, the pages that the request's uncommitted reserve took from the pool."""
+        rc = self.get(req_id)
+        return [[rc.tables[g][lp] for lp in lps] for g, lps in enumerate(rc.pending)]
+
     # ---------------------------------------------------------------- views
     def block_table(self, req_id, group: int) -> list[int]:
         return self.get(req_id).tables[group]

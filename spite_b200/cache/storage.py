@@ -88,6 +88,13 @@ class CacheStorage:
         kv = self.kv[g][self._index_in_group[cache_id]] if g is not None else None
         return LayerCache(g, kv, self.state.get(cache_id), self.page_size, write)
 
+    def clear_pages(self, kernels, pages_per_group):
+        """Pages that have just been handed out start at zero in every cache of their group: whatever the
+        last holder left (which may not even be finite) must not meet a masked key's zero weight."""
+        for g, pages in enumerate(pages_per_group):
+            if pages:
+                kernels.clear_pages(self.kv[g], pages)
+
     def clear_state(self, slot: int):
         """A new request takes `slot`: its fixed-size state starts at zero."""
         for t in self.state.values():

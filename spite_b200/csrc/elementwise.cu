@@ -112,6 +112,45 @@ SPITE_API int spite_gather_rows(const void* src, const int* idx, void* dst, int 
     return spite_launch_status();
 }
 
+// Zero pages of a paged cache: `base` holds `n_outer` blocks of `outer_stride` bytes (one per cache of a
+// group and per keys / values), each with pages of `page_bytes`.  grid (pages to clear, n_outer).
+struct PageList { int n; int ids[60]; };
+template <typename Word>
+__global__ void clear_pages_kernel(unsigned char* __restrict__ base, long long outer_stride, long long page_bytes,
+                                   const PageList pages) {
+    pdl_wait();
+    pdl_launch_dependents();
+    Word* dst = (Word*)(base + (size_t)blockIdx.y * outer_stride + (size_t)pages.ids[blockIdx.x] * page_bytes);
+    const long long n = page_bytes / (long long)sizeof(Word);
+    Word zero;
+    memset(&zero, 0, sizeof(Word));
+    for (long long i = threadIdx.x; i < n; i += blockDim.x) dst[i] = zero;
+}
+
+// `page_ids` is host memory (the ids are passed to the kernel by value, 60 a launch).
+SPITE_API int spite_clear_pages(void* base, long long n_outer, long long outer_stride, long long page_bytes,
+                                int n_pages_total, const int* page_ids, int n_ids, void* stream) {
+    if (!base || n_outer < 1 || outer_stride < 1 || page_bytes < 1 || n_pages_total < 1 || n_ids < 0) return SPITE_BAD_ARG;
+    if (n_ids > 0 && !page_ids) return SPITE_BAD_ARG;
+    if (page_bytes % 4 || outer_stride % 4 || ((uintptr_t)base & 3) || n_outer > 65535) return SPITE_UNSUPPORTED;
+    const bool wide = page_bytes % 16 == 0 && outer_stride % 16 == 0 && ((uintptr_t)base & 15) == 0;
+    for (int i = 0; i < n_ids; ++i)
+        if (page_ids[i] < 0 || page_ids[i] >= n_pages_total) return SPITE_BAD_ARG;
+    for (int at = 0; at < n_ids; at += 60) {
+        PageList list;
+        list.n = n_ids - at < 60 ? n_ids - at : 60;
+        for (int i = 0; i < list.n; ++i) list.ids[i] = page_ids[at + i];
+        if (wide)
+            SPITE_LAUNCH(clear_pages_kernel<uint4>, dim3(list.n, (unsigned)n_outer), 256, 0, (cudaStream_t)stream,
+                         (unsigned char*)base, outer_stride, page_bytes, list);
+        else
+            SPITE_LAUNCH(clear_pages_kernel<unsigned>, dim3(list.n, (unsigned)n_outer), 256, 0, (cudaStream_t)stream,
+                         (unsigned char*)base, outer_stride, page_bytes, list);
+        if (spite_launch_status() != SPITE_OK) return SPITE_LAUNCH_FAILED;
+    }
+    return SPITE_OK;
+}
+
 SPITE_API int spite_transform_logits(float* logits, long long n, float scale, float softcap, void* stream) {
     if (!logits || n < 0 || !(scale == scale) || !(softcap == softcap)) return SPITE_BAD_ARG;
     if (n == 0) return SPITE_OK;

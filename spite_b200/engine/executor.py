@@ -147,6 +147,12 @@ class Engine:
                 self.cache.release(r)
             raise
 
+        fresh_pages = [[] for _ in range(self.storage.n_groups)]
+        for e in entries:
+            for g, pages in enumerate(self.cache.pending_pages(e.req_id)):
+                fresh_pages[g] += pages
+        self.storage.clear_pages(self.model.kernels, fresh_pages)
+
         segments, offset = [], 0
         for e in entries:
             rc = self.cache.requests[e.req_id]

@@ -82,6 +82,13 @@ class KernelSet:
         """h[sorted_rows[i], :] (float32) += a[i, :] @ w_down[expert of i]^T; w_down [E, d, F]."""
         raise NotImplementedError
 
+    # ---- cache
+    def clear_pages(self, kv, page_ids):
+        """Zero the pages `page_ids` (a list of ints) of every cache of a group; `kv` is the group's tensor
+        [caches, 2, pages, kv heads, page_size, head_dim].  The engine does this when it hands a page out,
+        so that a request never multiplies a masked key's zero weight with what another request left there."""
+        raise NotImplementedError
+
     # ---- attention
     def qk_prepare(self, qkv, q_out, batch, cache, *, num_heads, rotation, qk_norm, temperature):
         """Encode positions of q and k, normalise, scale q, append k and v to the cache.

@@ -211,6 +211,19 @@ class CudaKernels(KernelSet):
         self._count("elementwise", 1)
         _check(st, "rms_norm")
 
+    def clear_pages(self, kv, page_ids):
+        self._t(kv, None, "cache")
+        if not page_ids:
+            return
+        caches, two, pages = kv.shape[0], kv.shape[1], kv.shape[2]
+        page_bytes = kv.stride(2) * kv.element_size()
+        ids = (C.c_int * len(page_ids))(*page_ids)
+        st = self._lib("elementwise").spite_clear_pages(
+            C.c_void_p(kv.data_ptr()), C.c_longlong(caches * two), C.c_longlong(kv.stride(1) * kv.element_size()),
+            C.c_longlong(page_bytes), pages, ids, len(page_ids), self._stream())
+        self._count("elementwise", -(-len(page_ids) // 60))
+        _check(st, "clear_pages")
+
     # ------------------------------------------------------------------ matrix products
     def _gemm(self, p: GemmParams, what, max_rows_per_group, gather_src=None):
         """Pick the kernel.  bfloat16: up to 16 rows (a decode step) go to the TMA weight-streaming

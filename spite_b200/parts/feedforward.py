@@ -71,6 +71,7 @@ class MoESigmoidPrescaled(FeedForward):
         self.f, self.fs = int(expert_size), int(shared_size)
         self.router = self.w_gate_up = self.w_down = self.ws_gate_up = self.ws_down = None
         self.router_beside_shared = os.environ.get("SPITE_NO_SIDE_STREAM", "") == ""
+        self.keep_router_logits = False      # `last_routing.logits` [tokens, experts] stays readable after a forward
 
     def param_specs(self):
         d, E, f, fs = self.d, self.E, self.f, self.fs
@@ -119,11 +120,11 @@ class MoESigmoidPrescaled(FeedForward):
             forked.record(main)
             with torch.cuda.stream(side):
                 side.wait_event(forked)
-                routing = k.moe_route(x, self.router, self.top_k)
+                routing = k.moe_route(x, self.router, self.top_k, want_logits=self.keep_router_logits)
                 routed = torch.cuda.Event()
                 routed.record(side)
         else:
-            routing = k.moe_route(x, self.router, self.top_k)
+            routing = k.moe_route(x, self.router, self.top_k, want_logits=self.keep_router_logits)
         self.last_routing = routing
         if self.fs:
             a = torch.empty((M, self.fs), dtype=x.dtype, device=x.device)
@@ -131,8 +132,9 @@ class MoESigmoidPrescaled(FeedForward):
             k.linear(a, self.ws_down, h, accumulate=True)
         if side is not None:
             main.wait_event(routed)
-            for t in (routing.expert_ids, routing.weights, routing.offsets, routing.sorted_rows):
-                t.record_stream(main)                        # made on the side stream, read on this one
+            for t in (routing.expert_ids, routing.weights, routing.offsets, routing.sorted_rows, routing.logits):
+                if t is not None:
+                    t.record_stream(main)                        # made on the side stream, read on this one
         for slot in range(self.top_k):
             a = torch.empty((M, self.f), dtype=x.dtype, device=x.device)
             k.grouped_linear_swiglu(x, self.w_gate_up, routing.sorted_rows[slot], routing.offsets[slot],

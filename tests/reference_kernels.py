@@ -27,6 +27,10 @@ class TorchReferenceKernels(KernelSet):
     def embed(self, table, token_ids, out_h, *, scale=1.0):
         out_h.copy_(table[token_ids.long()].float() * scale)
 
+    def clear_pages(self, kv, page_ids):
+        if page_ids:
+            kv[:, :, torch.tensor(page_ids, dtype=torch.long)] = 0
+
     def transform_logits(self, logits, *, scale=1.0, softcap=None):
         logits.mul_(scale)
         if softcap:

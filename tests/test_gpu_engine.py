@@ -81,6 +81,27 @@ def test_mixed_batches_reusing_pages(setup, seed, page_size):
     assert eng.cache.free_pages() == [eng.n_pages] * len(eng.cache.pools)
 
 
+def poison_free_pages(engine):
+    """Every page that no request holds gets NaN in every cache: what a request whose activations
+    overflowed may leave behind when it ends."""
+    for g, pool in enumerate(engine.cache.pools):
+        if pool._free:
+            engine.storage.kv[g][:, :, torch.tensor(pool._free, device=engine.storage.kv[g].device)] = float("nan")
+
+
+def test_what_a_page_held_before_is_never_seen(setup):
+    """Free pages are filled with NaN before every step, so every page a request receives (its first, the
+    ones it grows into, the ones it gets again after its window let them go) arrives poisoned.  The logits
+    stay those of the plain implementation: a masked key's zero weight never meets the old contents."""
+    path, model, requests, tol = setup
+    n_prompt = {r: max(2, len(t) - 12) for r, t in requests.items()}
+    steps = H.steps_mixed(requests, n_prompt, 3)
+    eng = _engine(model, steps, 16)
+    results = H.run_steps(eng, steps, before_step=poison_free_pages)
+    assert all(bool(torch.isfinite(v).all()) for v in results.values())
+    H.compare_with_plain(results, path, requests, tol)
+
+
 def test_first_tokens_of_a_sequence(setup):
     """Positions 0..3 alone: one key, the first rotation angles, a page's first rows."""
     path, model, requests, tol = setup
@@ -128,7 +149,11 @@ def test_sizes_of_the_tcgen05_kernels(tmp_path):
     steps = H.steps_mixed(requests, n_prompt, 5, sizes=(2, 9, 50, 70))
     eng = _engine(model, steps, 64)
     assert eng.n_pages * 64 < sum(H._round64(len(t)) for t in requests.values())
-    H.compare_with_plain(H.run_steps(eng, steps), path, requests, TOL["bfloat16"])
+    # free pages hold NaN before every step: the rows of a live page behind a request's last position,
+    # inside the 64-key tile that the tensor cores multiply, must have been cleared when the page was handed out
+    results = H.run_steps(eng, steps, before_step=poison_free_pages)
+    assert all(bool(torch.isfinite(v).all()) for v in results.values())
+    H.compare_with_plain(results, path, requests, TOL["bfloat16"])
     assert model.kernels.attention_tc_error() == 0 and model.kernels.gemm_tc_error() == 0
     assert all(by_library[lib] > 0 for lib in ("attention_tc", "attention_rows", "attention_mma", "gemm_stream"))
 
