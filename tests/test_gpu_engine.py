@@ -20,7 +20,7 @@ pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parent.parent
 # float32: sums in another order than the plain implementation's.  bfloat16: 8 bits of
 # mantissa at some thirty rounding points between the embedding and the logits.
-TOL = {"float32": 2e-5, "bfloat16": 4e-2}
+TOL = {"float32": 2e-5, "bfloat16": 2e-2}
 MARGIN = {"A": 0.012, "B": 0.03}      # router logit margin that bfloat16 rounding cannot flip
 
 

@@ -146,6 +146,7 @@ def _compare(results, refs, requests, tol, what):
         err = float((row - ref[p]).abs().max()) / float(ref.abs().max())
         worst = max(worst, err)
         assert err <= tol, f"{what}: request {r!r}, position {p}: error {err:.3e} of the logit scale exceeds {tol:.1e}"
+    H.note_error(worst, tol)
     return worst
 
 

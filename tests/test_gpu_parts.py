@@ -448,20 +448,21 @@ def test_greedy_generation_through_the_entry_point(folder, dtype):
     compared = 0
     for p, g in zip(prompts, got):
         assert len(g) == 12
-        # follow the plain implementation as long as its own choice is clear
+        # Follow the engine's tokens and ask the plain implementation at every position which tokens it could
+        # have chosen: in float32 its argmax alone, in bfloat16 every token whose logit lies within 2 % of the
+        # logit scale of the maximum (three times the largest error the engine's bfloat16 logits show)
         ids = list(p)
         for i, tok in enumerate(g):
             logits = plain.forward(cfg, W, ids)[-1]
-            top2 = torch.topk(logits, 2).values
-            gap = float(top2[0] - top2[1]) / float(logits.abs().max())
-            if dtype == "bfloat16" and gap < 0.05:
-                break                                         # rounding may decide this one; stop comparing here
-            assert tok == plain.greedy_pick(logits), f"token {i} of prompt of {len(p)}"
+            slack = 0.02 * float(logits.abs().max()) if dtype == "bfloat16" else 0.0
+            allowed = torch.nonzero(logits >= logits.max() - slack).flatten().tolist()
+            if len(allowed) == 1:
+                assert tok == plain.greedy_pick(logits), f"token {i} of prompt of {len(p)}"
+                compared += 1
+            else:
+                assert tok in allowed, f"token {i} of prompt of {len(p)}: {tok} is none of {allowed}"
             ids.append(tok)
-            compared += 1
-        if dtype == "float32":
-            assert i == 11
-    assert compared >= 12 * len(prompts) // 2, f"only {compared} of {12 * len(prompts)} tokens had a clear choice"
+    assert compared >= (48 if dtype == "float32" else 12), f"only {compared} of 48 tokens had a clear choice"
     assert generate(path, prompts[1:2], max_tokens=5, temperature=0.0, dtype=dtype, device=DEV,
                     cache_tokens=128, page_size=16, max_requests=2) == [got[1][:5]]
     # the decode steps above were launched ahead of the reading of their ids; the plain loop gives the same
