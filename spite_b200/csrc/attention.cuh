@@ -71,6 +71,20 @@ struct AttnMmaExtra {
     int seg_max_tokens;
 };
 
+// The same for the decode kernel whose last-arriving block merges the key splits itself.
+struct AttnDecodeExtra {
+    const int* cu_seqlens;       // [segments + 1]
+    float* partial;              // [blocks, kv heads, splits, 16, head_dim + 4]   (splits > 1)
+    int* tickets;                // [blocks, kv heads], zero between launches      (splits > 1)
+    int n_segments;
+    int tokens_per_block;
+    int n_splits;
+    int seg_min_tokens;
+    int seg_max_tokens;
+    int cache_settled;           // the cache rows of positions before each request's first token of this step were
+                                 // written at least two launches ago on this stream: they may be read before the wait
+};
+
 __device__ __forceinline__ int window_lowest(int kind, int size, int pos) {
     if (kind == SPITE_WINDOW_CHUNK) return (pos / size) * size;
     if (kind == SPITE_WINDOW_SLIDING) return max(0, pos - size + 1);

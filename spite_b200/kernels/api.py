@@ -98,8 +98,11 @@ class KernelSet:
         (floor, scale) or None: q *= ln(floor((pos + 1) / floor) + 1) * scale + 1."""
         raise NotImplementedError
 
-    def paged_attention(self, q, out, batch, cache, *, num_heads, window, softmax_scale):
-        """out[M, nq hd] = softmax(q K^T * scale over the visible cached keys) V."""
+    def paged_attention(self, q, out, batch, cache, *, num_heads, window, softmax_scale, cache_settled=False):
+        """out[M, nq hd] = softmax(q K^T * scale over the visible cached keys) V.
+        `cache_settled`: the caller promises that the cache rows of positions before each request's first
+        token of this step were written by earlier steps (not by the one or two kernels launched just
+        before this call), so a kernel may fetch them while the kernel before still runs."""
         raise NotImplementedError
 
     # ---- mixture of experts

@@ -34,6 +34,7 @@ LIBRARIES = {
     "gemm_stream": (["gemm_stream.cu"], []),
     "attention": (["attention.cu"], []),
     "attention_mma": (["attention_mma.cu"], []),
+    "attention_decode": (["attention_decode.cu"], []),
     "attention_rows": (["attention_rows.cu"], []),
     "attention_tc": (["attention_tc.cu"], []),
     "moe": (["moe.cu"], []),

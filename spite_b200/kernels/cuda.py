@@ -7,6 +7,7 @@ from __future__ import annotations
 
 import collections
 import ctypes as C
+import math
 import os
 
 import torch
@@ -59,6 +60,12 @@ class AttnMmaExtra(C.Structure):
                 ("seg_min_tokens", C.c_int), ("seg_max_tokens", C.c_int)]
 
 
+class AttnDecodeExtra(C.Structure):
+    _fields_ = [("cu_seqlens", C.c_void_p), ("partial", C.c_void_p), ("tickets", C.c_void_p),
+                ("n_segments", C.c_int), ("tokens_per_block", C.c_int), ("n_splits", C.c_int),
+                ("seg_min_tokens", C.c_int), ("seg_max_tokens", C.c_int), ("cache_settled", C.c_int)]
+
+
 class SampleParams(C.Structure):
     _fields_ = [("logits", C.c_void_p), ("work", C.c_void_p), ("temperature", C.c_void_p),
                 ("top_k", C.c_void_p), ("top_p", C.c_void_p), ("min_p", C.c_void_p),
@@ -70,7 +77,7 @@ class SampleParams(C.Structure):
 # Libraries whose kernels wait on mbarriers with a limit.  A kernel that gives up records a code in its
 # library's word of one small buffer in pinned host memory, which the device writes directly: the host
 # reads it after any point at which it has waited for a step's results, without another copy or wait.
-_WAITING_LIBRARIES = ("gemm_tc", "gemm_tc_pair", "gemm_stream", "attention_tc")
+_WAITING_LIBRARIES = ("gemm_tc", "gemm_tc_pair", "gemm_stream", "attention_tc", "attention_decode")
 _error_words = None          # pinned int32 [len(_WAITING_LIBRARIES)], one per process
 _configured: set = set()
 
@@ -109,7 +116,10 @@ class CudaKernels(KernelSet):
         self.use_tcgen05_attention = os.environ.get("SPITE_NO_TCGEN05_ATTENTION", "") == ""
         # fewest tokens of a request in a step that go to the tcgen05 attention kernel (0: one full tile of rows)
         self.attention_tc_min_tokens = int(os.environ.get("SPITE_ATTENTION_TC_MIN_TOKENS", "0"))
-        self.attention_max_splits = int(os.environ.get("SPITE_ATTENTION_MAX_SPLITS", "32"))    # most key splits of decode attention (more cost the merge more than they gain)
+        self.attention_max_splits = int(os.environ.get("SPITE_ATTENTION_MAX_SPLITS", "24"))    # most key splits of decode attention: beyond about
+        # twenty the merge by the last block costs more than the extra blocks bring (one request at 8,192 keys: 22 us
+        # with 37 splits, 17.6 us with 18)
+        self.use_decode_attention = os.environ.get("SPITE_NO_DECODE_ATTENTION", "") == ""     # the TMA-fed decode kernel
         # row counts up to which the weight-streaming kernel is preferred over the tcgen05 one
         self.skinny_max_rows = int(os.environ.get("SPITE_SKINNY_MAX_ROWS", "16"))
         self.skinny_blocks = int(float(os.environ.get("SPITE_SKINNY_BLOCKS_PER_SM", "2")) * self.sm_count)
@@ -122,7 +132,8 @@ class CudaKernels(KernelSet):
         self.skinny_tall_rows = int(os.environ.get("SPITE_SKINNY_TALL_ROWS", "0"))
         # the TMA weight-streaming kernel for decode products: k elements per work item, shared memory per block
         self.use_stream = os.environ.get("SPITE_NO_STREAM_GEMM", "") == ""
-        self.stream_split_k = int(os.environ.get("SPITE_STREAM_SPLIT_K", "2048"))
+        self.stream_split_k = int(os.environ.get("SPITE_STREAM_SPLIT_K", "0"))     # 0: splits chosen per product
+        self.stream_item_cost = float(os.environ.get("SPITE_STREAM_ITEM_COST", "4"))   # fixed cost of an item, in k blocks
         # (shared memory per block, blocks per multiprocessor) for up to 3 tokens and for more: measured in the decode
         # step at Scout shapes, one token 2.90 ms with (110 KiB, 2) against 3.01 with (74 KiB, 3), eight tokens 7.10
         # against 7.02, sixty-four alike.  SPITE_STREAM_SMEM / SPITE_STREAM_BLOCKS_PER_SM set both alike.
@@ -295,7 +306,7 @@ class CudaKernels(KernelSet):
         cols = 64 if swiglu else 128
         tiles = -(-p.N // cols) * (min(p.n_groups, p.M) if grouped else 1)
         smem, blocks = self.stream_shape[p.M > 3]
-        splits = 1 if tiles >= 6 * blocks else max(1, min(16, p.K // self.stream_split_k))
+        splits = self._stream_splits(tiles, p.K // 64, blocks)
         scratch, n_floats = None, 0
         if splits > 1:
             if tiles > self._tickets_n:
@@ -310,6 +321,25 @@ class CudaKernels(KernelSet):
         return self._lib("gemm_stream").spite_gemm_stream(
             C.byref(p), max_rows_per_group, blocks, smem, splits, C.c_void_p(_ptr(scratch)),
             C.c_longlong(n_floats), C.c_void_p(_ptr(tickets)), self._tickets_n, C.c_void_p(stream))
+
+    def _stream_splits(self, tiles: int, k_blocks: int, slots: int) -> int:
+        """k splits of the weight-streaming kernel.  A product of few row tiles (a dense projection at a few
+        tokens: 40 to 128 tiles for 296 to 444 resident blocks) would leave most multiprocessors without
+        work, and the ones that have some are then bound by what a single one can pull; so the tiles are cut
+        along k until the (tile, split) items fill the resident blocks about once.  The cost of a choice is
+        its rounds of items times (k blocks per item + a fixed cost per item for filling the ring, the
+        partial sums and the ticket); at least four k blocks stay together."""
+        if self.stream_split_k:                                  # a fixed k per item, for measurements
+            return 1 if tiles >= 6 * slots else max(1, min(16, k_blocks * 64 // self.stream_split_k))
+        if tiles >= 4 * slots:
+            return 1
+        best, best_cost = 1, None
+        for s in range(1, max(1, min(32, k_blocks // 4)) + 1):
+            rounds = -(-tiles * s // slots)
+            cost = rounds * (-(-k_blocks // s) + self.stream_item_cost)
+            if best_cost is None or cost < best_cost:
+                best, best_cost = s, cost
+        return best
 
     def attention_tc_error(self) -> int:
         """Error code left by a tcgen05 attention block that gave up waiting (0: none); clears it. Synchronises."""
@@ -424,7 +454,7 @@ class CudaKernels(KernelSet):
         self._count("attention", 1)
         _check(st, "qk_prepare")
 
-    def paged_attention(self, q, out, batch, cache, *, num_heads, window, softmax_scale):
+    def paged_attention(self, q, out, batch, cache, *, num_heads, window, softmax_scale, cache_settled=False):
         self._t(q, self.dtype, "q"); self._t(out, self.dtype, "out")
         p = AttentionParams(q=q.data_ptr(), out=out.data_ptr(), num_heads=num_heads,
                             window_kind=_WINDOW[window.kind], window_size=int(window.size),
@@ -475,6 +505,9 @@ class CudaKernels(KernelSet):
                 return
             if batch.context_bucket:            # fixed launch shape for a captured step
                 longest = batch.context_bucket if window.kind == "full" else min(batch.context_bucket, window.size)
+            if c.head_dim in (64, 128) and c.page_size % 64 == 0 and self.use_decode_attention:
+                self._attention_decode(p, b, c, batch, n_small, tpb, big_from - 1, longest, num_heads, cache_settled)
+                return
             tiles = -(-longest // 16) + 1
             base = n_small * c.num_kv_heads
             # key splits: fill the resident blocks (three per multiprocessor) once if the step is
@@ -486,7 +519,7 @@ class CudaKernels(KernelSet):
                 splits = 1
             else:
                 splits = max(range(1, 5), key=lambda s: (base * s / slots) / -(-base * s // slots))
-            splits = max(1, min(splits, tiles // 8, self.attention_max_splits))
+            splits = max(1, min(splits, tiles // 8, self.attention_max_splits, 32))
             o_part = ml_part = None
             if splits > 1:
                 # one row per token place of this kernel's blocks: tokens of longer segments take none
@@ -506,6 +539,40 @@ class CudaKernels(KernelSet):
                                                           self._stream())
         self._count("attention", 1)
         _check(st, "paged_attention")
+
+    def _attention_decode(self, p, b, c, batch, n_small, tpb, seg_max, longest, num_heads, cache_settled):
+        """Decoded tokens (and portions too short for the row kernels) on the TMA-fed decode kernel: as many
+        key splits as fill the resident blocks once, partial results merged by the last block of a split set."""
+        stage = 2 * c.head_dim * 64 * 2                         # 64 keys and 64 values of one kv head
+        tiles = -(-longest // 64) + 1
+        base = n_small * c.num_kv_heads
+        per_sm = max(1, min(4, (225 * 1024) // (3 * stage + 2048)))
+        slots = per_sm * self.sm_count
+        if base <= slots:
+            splits = slots // base
+        elif base >= 4 * slots:
+            splits = 1
+        else:
+            splits = max(range(1, 5), key=lambda s: (base * s / slots) / -(-base * s // slots))
+        splits = max(1, min(splits, tiles // 2, self.attention_max_splits))
+        n_stages = max(2, min(3 if per_sm > 1 else 6, -(-tiles // splits)))
+        partial = tickets = None
+        if splits > 1:
+            if base > self._tickets_n:
+                raise KernelError(f"paged_attention: {base} (request block, kv head) pairs exceed the {self._tickets_n} tickets")
+            partial = torch.empty((base * splits * 16 * (c.head_dim + 4),), dtype=torch.float32, device=self.device)
+            self.attention_scratch_bytes = partial.numel() * 4
+            stream = torch.cuda.current_stream().cuda_stream
+            tickets = self._tickets.get(stream)
+            if tickets is None:
+                tickets = self._tickets[stream] = torch.zeros(self._tickets_n, dtype=torch.int32, device=self.device)
+        x = AttnDecodeExtra(cu_seqlens=batch.cu_seqlens.data_ptr(), partial=_ptr(partial), tickets=_ptr(tickets),
+                            n_segments=len(batch.segments), tokens_per_block=tpb, n_splits=splits,
+                            seg_min_tokens=0, seg_max_tokens=seg_max, cache_settled=int(bool(cache_settled)))
+        st = self._lib("attention_decode").spite_paged_attention_decode(
+            C.byref(p), C.byref(b), C.byref(c), C.byref(x), n_small, n_stages, self._stream())
+        self._count("attention_decode", 1)
+        _check(st, "paged_attention (decode)")
 
     # ------------------------------------------------------------------ mixture of experts
     def moe_route(self, x, w_router, top_k, want_logits=False) -> Routing:

@@ -24,7 +24,7 @@ from .base import Mixer, ParamSpec, QkNorm, build_part, register_mixer
 @register_mixer("paged_attention")
 class PagedAttention(Mixer):
     graph_safe = True
-    kernel_libraries = ("gemm_simt", "attention", "attention_mma", "attention_rows", "attention_tc")
+    kernel_libraries = ("gemm_simt", "attention", "attention_mma", "attention_rows", "attention_tc", "attention_decode")
 
     def __init__(self, ctx, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  position: PartSpec, window=("full", 0), qk_norm_eps=None, qk_norm_gain=False,
@@ -40,7 +40,7 @@ class PagedAttention(Mixer):
         if ctx.dtype == torch.bfloat16 and self.hd % 16 == 0 and self.hd <= 128 and self.nq // self.nkv <= 16:
             libs += ["attention_mma", "attention_rows"]
             if self.hd in (64, 128):
-                libs.append("attention_tc")
+                libs += ["attention_tc", "attention_decode"]
         self.kernel_libraries = tuple(libs)
         self.window = window if isinstance(window, Window) else Window(window[0], int(window[1]))
         self.position = build_part("position", position, ctx)
@@ -90,6 +90,8 @@ class PagedAttention(Mixer):
         k.qk_prepare(qkv, q, batch, cache, num_heads=self.nq, rotation=self.position.rotation(),
                      qk_norm=self.qk_norm, temperature=self.temperature)
         o = torch.empty_like(q)
+        # keys and values of earlier positions were cached by earlier steps; this step's own were written by
+        # the prepare kernel just before, which is what the attention kernel waits for
         k.paged_attention(q, o, batch, cache, num_heads=self.nq, window=self.window,
-                          softmax_scale=self.softmax_scale)
+                          softmax_scale=self.softmax_scale, cache_settled=True)
         k.linear(o, self.wo, h, accumulate=True)

@@ -142,7 +142,7 @@ class TorchReferenceKernels(KernelSet):
                 kv[0, page, :, p % P, :] = k[t].to(kv.dtype)
                 kv[1, page, :, p % P, :] = v[t].to(kv.dtype)
 
-    def paged_attention(self, q, out, batch, cache, *, num_heads, window, softmax_scale):
+    def paged_attention(self, q, out, batch, cache, *, num_heads, window, softmax_scale, cache_settled=False):
         kv = cache.kv
         nkv, P, hd = kv.shape[2], kv.shape[3], kv.shape[4]
         nq = num_heads

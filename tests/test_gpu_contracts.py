@@ -195,7 +195,8 @@ def test_sampling_entry_points(libs):
 
 # ---------------------------------------------------------------------------- attention
 def attention_case(hd=64, nq=4, nkv=2, page=64, M=3):
-    from spite_b200.kernels.cuda import AttentionParams, AttnMmaExtra, PagedCache, QkPrepareParams, StepTokens
+    from spite_b200.kernels.cuda import (AttentionParams, AttnDecodeExtra, AttnMmaExtra, PagedCache, QkPrepareParams,
+                                         StepTokens)
     kv = torch.zeros((2, 4, nkv, page, hd), dtype=torch.bfloat16, device=DEV)
     q = torch.ones((M, nq * hd), dtype=torch.bfloat16, device=DEV)
     qkv = torch.ones((M, (nq + 2 * nkv) * hd), dtype=torch.bfloat16, device=DEV)
@@ -212,9 +213,11 @@ def attention_case(hd=64, nq=4, nkv=2, page=64, M=3):
                         softmax_scale=0.125)
     x = AttnMmaExtra(cu_seqlens=cu.data_ptr(), o_part=None, ml_part=None, n_segments=1, tokens_per_block=1,
                      n_splits=1, seg_min_tokens=0, seg_max_tokens=1 << 30)
+    xd = AttnDecodeExtra(cu_seqlens=cu.data_ptr(), partial=None, tickets=None, n_segments=1, tokens_per_block=1,
+                         n_splits=1, seg_min_tokens=0, seg_max_tokens=1 << 30, cache_settled=0)
     qp = QkPrepareParams(qkv=qkv.data_ptr(), q_out=out.data_ptr(), inv_freq=None, qk_norm_eps=0.0,
                          temperature_floor=0, temperature_scale=0.0, num_heads=nq, write_cache=1)
-    return dict(p=p, b=b, c=c, x=x, qp=qp, out=out, kv=kv, keep=keep)
+    return dict(p=p, b=b, c=c, x=x, xd=xd, qp=qp, out=out, kv=kv, keep=keep)
 
 
 def attention_calls(libs):
@@ -226,16 +229,20 @@ def attention_calls(libs):
             C.byref(k["p"]), C.byref(k["b"]), C.byref(k["c"]), C.byref(k["x"]), 1, None)),
         ("attention_tc", lambda k: libs["attention_tc"].spite_paged_attention_tc(
             C.byref(k["p"]), C.byref(k["b"]), C.byref(k["c"]), C.byref(k["x"]), 1, 148, None)),
+        ("attention_decode", lambda k: libs["attention_decode"].spite_paged_attention_decode(
+            C.byref(k["p"]), C.byref(k["b"]), C.byref(k["c"]), C.byref(k["xd"]), 3, 3, None)),
     ]
 
 
-@pytest.mark.parametrize("which", range(4))
+@pytest.mark.parametrize("which", range(5))
 def test_attention_refuses_malformed_calls(libs, which):
     name, call = attention_calls(libs)[which]
     edits = [("p", "q", None), ("p", "out", None), ("b", "positions", None), ("b", "block_table", None),
              ("c", "kv", None), ("p", "num_heads", 0), ("p", "num_heads", 3), ("p", "window_kind", 5),
              ("b", "table_width", 0), ("b", "n_tokens", -1)]
-    if name != "attention":
+    if name == "attention_decode":
+        edits += [("xd", "cu_seqlens", None), ("xd", "n_segments", 0), ("xd", "tokens_per_block", 0), ("xd", "n_splits", 4)]
+    elif name != "attention":
         edits += [("x", "cu_seqlens", None), ("x", "n_segments", 0), ("x", "tokens_per_block", 0)]
     for struct, field, value in edits:
         k = attention_case()
@@ -250,14 +257,16 @@ def test_attention_refuses_malformed_calls(libs, which):
 def test_attention_refuses_sizes_outside_its_domain(libs):
     calls = dict(attention_calls(libs))
     k = attention_case(hd=24)                                          # head size that is no multiple of 16
-    for name in ("attention_mma", "attention_rows", "attention_tc"):
+    for name in ("attention_mma", "attention_rows", "attention_tc", "attention_decode"):
         assert calls[name](k) == UNSUPPORTED and untouched(k["out"]), name
-    k = attention_case(hd=32)                                          # the tcgen05 kernel takes 64 and 128 only
-    assert calls["attention_tc"](k) == UNSUPPORTED and untouched(k["out"])
+    k = attention_case(hd=32)                                          # the TMA-fed kernels take 64 and 128 only
+    for name in ("attention_tc", "attention_decode"):
+        assert calls[name](k) == UNSUPPORTED and untouched(k["out"]), name
     k = attention_case(hd=64, page=16)                                 # and pages of a multiple of 64 keys
-    assert calls["attention_tc"](k) == UNSUPPORTED and untouched(k["out"])
+    for name in ("attention_tc", "attention_decode"):
+        assert calls[name](k) == UNSUPPORTED and untouched(k["out"]), name
     k = attention_case(hd=64, nq=34, nkv=2)                            # 17 query heads on a kv head
-    for name in ("attention_mma", "attention_rows"):
+    for name in ("attention_mma", "attention_rows", "attention_decode"):
         assert calls[name](k) == UNSUPPORTED and untouched(k["out"]), name
     k = attention_case(hd=258)                                         # beyond the general kernel's 256
     assert calls["attention"](k) == UNSUPPORTED and untouched(k["out"])

@@ -175,4 +175,4 @@ def test_scout_layer_sizes_in_bfloat16_on_the_same_weights(scout):
         print(f"scout bfloat16, {cut}: worst error {worst:.2e} of the logit scale")
     assert model.kernels.errors() == {}
     used = model.kernels.launches_by_library
-    assert all(used[lib] > 0 for lib in ("gemm_tc", "gemm_stream", "attention_tc", "attention_mma")), dict(used)
+    assert all(used[lib] > 0 for lib in ("gemm_tc", "gemm_stream", "attention_tc", "attention_decode")), dict(used)

@@ -275,6 +275,52 @@ def test_paged_attention(ks, nq, nkv, hd, window, P):
     assert float(w_far[far - win.lowest_visible(300)]) > 0.5
 
 
+@pytest.mark.parametrize("nq,nkv,hd,window,P", [
+    (40, 8, 128, ("full", 0), 64), (40, 8, 128, ("chunk", 8192), 64), (10, 2, 128, ("chunk", 1000), 64),
+    (6, 1, 64, ("sliding", 777), 64), (16, 1, 128, ("full", 0), 128), (3, 3, 64, ("chunk", 96), 64),
+    (32, 2, 64, ("full", 0), 64)])
+def test_paged_attention_decode(nq, nkv, hd, window, P):
+    """Decoded tokens deep in long contexts on the TMA-fed decode kernel: dozens of key splits merged by the
+    block that comes last, a window that starts and ends inside a 64-key tile, pages behind the window given
+    back (and poisoned), requests of very different lengths in one call, a first token, two-token portions
+    (several tokens in one block), and one far key among thousands that carries a row's attention."""
+    from spite_b200.kernels.cuda import CudaKernels
+    ks = CudaKernels(torch.bfloat16, DEV)
+    win = Window(*window)
+    specs = [(8191, 1), (5000, 1), (0, 1), (63, 1), (64, 2), (3000, 2), (129, 1), (1023, 1)]
+    n_pages = sum(-(-(s + n) // P) for s, n in specs) + 5
+    batch, tables = make_batch(specs, P, n_pages, 50, DEV)
+    M = batch.n_tokens
+    g = torch.Generator().manual_seed(51)
+    k_all = [torch.randn((s + n, nkv, hd), generator=g).to(torch.bfloat16) for s, n in specs]
+    v_all = [torch.randn((s + n, nkv, hd), generator=g).to(torch.bfloat16) for s, n in specs]
+    q = torch.randn((M, nq, hd), generator=g)
+    far = 11 if win.kind == "full" else win.lowest_visible(8191) + 1
+    q[0] = k_all[0][far, 0, :].float() * (16.0 / math.sqrt(hd))       # row 0: the token at position 8191
+    q = q.to(torch.bfloat16)
+    kv = torch.zeros((2, n_pages, nkv, P, hd), dtype=torch.bfloat16)
+    fill_cache(kv, tables, [(s + n, 0) for s, n in specs], k_all, v_all, P)
+    bt = batch.block_tables[0]
+    for s, (start, n) in enumerate(specs):                           # pages wholly behind the window are gone
+        for pg in range(win.lowest_visible(start) // P):
+            kv[:, tables[s][pg]] = float("nan")
+            bt[s, pg] = -1
+    out = torch.empty((M, nq * hd), dtype=torch.bfloat16, device=DEV)
+    scale = 1.0 / math.sqrt(hd)
+    before = ks.launches_by_library["attention_decode"]
+    for _ in range(2):                                               # twice: the tickets must be back at zero
+        out.fill_(float("nan"))
+        ks.paged_attention(q.reshape(M, nq * hd).to(DEV), out, batch, LayerCache(0, kv.to(DEV), None, P, False),
+                           num_heads=nq, window=win, softmax_scale=scale)
+        ref = dense_attention_reference(q, k_all, v_all, specs, nq, nkv, win, scale)
+        close(out.view(M, nq, hd), ref, TOL[torch.bfloat16], f"decode attention {window}")
+    assert ks.launches_by_library["attention_decode"] == before + 2 and ks.errors() == {}
+    assert ks.attention_scratch_bytes > 0 or win.kind != "full"       # the keys were split among blocks
+    lo = win.lowest_visible(8191)
+    w_far = torch.softmax((k_all[0][lo:8192, 0].double() @ q[0, 0].double()) * scale, 0)
+    assert float(w_far[far - lo]) > 0.5
+
+
 def dense_attention_reference(q, k_all, v_all, specs, nq, nkv, win, scale):
     """softmax(q k^T) v per request with a dense mask, float64; q [M, nq, hd] and the keys already rounded."""
     out = torch.empty(q.shape, dtype=torch.float64)
@@ -339,12 +385,14 @@ def test_paged_attention_tcgen05(nq, nkv, hd, window, P):
     assert float(w_far[far - lo]) > 0.5
 
 
-@pytest.mark.parametrize("n_tokens,library", [(1, "attention_mma"), (9, "attention_rows"), (60, "attention_tc")])
+@pytest.mark.parametrize("n_tokens,library", [(1, "attention_decode"), (1, "attention_mma"), (9, "attention_rows"),
+                                              (60, "attention_tc")])
 def test_paged_attention_long_context(n_tokens, library):
     """The last tokens of a 40,000-token context on each bfloat16 attention kernel: thousands of key tiles,
     key splits and their merge for the single token, hundreds of pages in random order."""
     from spite_b200.kernels.cuda import CudaKernels
     ks = CudaKernels(torch.bfloat16, DEV)
+    ks.use_decode_attention = library != "attention_mma"
     nq, nkv, hd, P, C = 10, 2, 128, 64, 40000
     n_pages = C // P + 3
     batch, tables = make_batch([(C - n_tokens, n_tokens)], P, n_pages, 50, DEV)
