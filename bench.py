@@ -5,6 +5,13 @@ step's HBM roofline fraction, and decoding at batch 1 and 64.
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
 
 A "step" is one decode step of the whole batch.  Prints one JSON line.
+
+Two further workloads print a line of the same kind (they are extra modes; the default line stays the one above):
+
+    python bench.py --config maverick    # Llama-4-Maverick layer shapes, 4 layers (dense, MoE of 128 experts, dense, MoE):
+                                         # 64 requests with prompts of 16 to 4,096 tokens through the scheduler
+    python bench.py --config long        # Scout layer shapes, 8 layers: a prompt of 131,072 tokens in portions of
+                                         # 8,192, then 256 decode steps at batch 1 and at batch 4
 """
 from __future__ import annotations
 
@@ -114,21 +121,181 @@ def prefill_flops(cfg, T):
     return cfg["num_hidden_layers"] * per_layer + 2 * d * cfg["vocab_size"]    # one logits row
 
 
-def run_ours(args):
+def prefill_roofline_ms(cfg, T, pk):
+    """The time a prefill of T tokens cannot beat kernel by kernel: every product at the sustained bf16 rate or
+    the time to read its weights once, whichever is longer, the attention at the bf16 rate, the head's weights."""
+    d, hd, nq, nkv = cfg["hidden_size"], cfg["head_dim"], cfg["num_attention_heads"], cfg["num_key_value_heads"]
+    f, E, k = cfg["intermediate_size"], cfg["num_local_experts"], cfg["num_experts_per_tok"]
+    fl, bw = pk["bf16_tflops_sustained"] * 1e12, pk["hbm_gbs"] * 1e9
+    both = lambda flops, nbytes: max(flops / fl, nbytes / bw)
+    step = int(cfg.get("interleave_moe_layer_step", 1))
+    total = 0.0
+    for L in range(cfg["num_hidden_layers"]):
+        total += both(2 * T * d * (nq + 2 * nkv) * hd, 2 * d * (nq + 2 * nkv) * hd) + both(2 * T * nq * hd * d, 2 * nq * hd * d)
+        total += (2 * 2 * nq * hd * T * (T + 1) // 2) / fl
+        if step > 0 and (L + 1) % step == 0:
+            total += both(2 * T * d * 3 * f, 2 * 3 * d * f)                             # shared expert
+            total += both(2 * T * k * d * 3 * f, 2 * 3 * d * f * min(E, T * k))         # routed experts
+        else:
+            fm = cfg["intermediate_size_mlp"]
+            total += both(2 * T * d * 3 * fm, 2 * 3 * d * fm)
+    return (total + 2 * d * cfg["vocab_size"] / bw) * 1e3
+
+
+def build_model(cfgd):
     import torch
     from spite_b200.config import Llama4Config
-    from spite_b200.engine import Engine, Model, StepEntry
-    from spite_b200.engine.scheduler import Request, Scheduler
+    from spite_b200.engine import Model
     from spite_b200.kernels import build as kb
-    from spite_b200.sampling import Sampler, SamplingParams
-
     torch.cuda.set_device(0)
-    dev = "cuda:0"
-    cfgd = dict(SCOUT, num_hidden_layers=args.layers)
     cfg = Llama4Config.from_dict(cfgd)
-    model = Model.from_config(cfg, dtype="bfloat16", device=dev)
+    model = Model.from_config(cfg, dtype="bfloat16", device="cuda:0")
     kb.ensure_built(model.kernel_libraries() + ["sampling"])
     model.init_random(seed=0, std=0.02)
+    return cfg, model
+
+
+def distinct_experts(model):
+    """Per layer, how many experts the tokens of the last step used (0 for layers without experts)."""
+    import torch
+    out = []
+    for blk in model.blocks:
+        r = getattr(blk.ffn, "last_routing", None)
+        out.append(torch.unique(r.expert_ids).numel() if r is not None else 0)
+    return out
+
+
+def base_line(metric, value, unit, steps, warmup, ms_per_step, config, data="synthetic (random token ids, random weights N(0,0.02))"):
+    return {"metric": metric, "value": round(value, 2), "unit": unit, "n_gpus": 1, "steps": steps, "warmup": warmup,
+            "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": data, "config": config}
+
+
+def run_maverick(args):
+    """BASELINE configuration 4: sparse routing over 128 experts in mixed batches.  64 requests with prompts of 16
+    to 4,096 random tokens and 32 new tokens each go through the public entry point (scheduler, portions of
+    prompts beside decoded tokens under a budget of 4,096 tokens a step).  `value` is all tokens run (prompt and
+    new) per second of device time; a "step" here is one step of the scheduler."""
+    import random
+    import torch
+    from spite_b200.api import LLM
+    cfgd = dict(SCOUT, num_hidden_layers=4, interleave_moe_layer_step=2, num_local_experts=128,
+                intermediate_size_mlp=16384, rope_scaling=None)
+    cfg, model = build_model(cfgd)
+    n_req, new = 64, 32
+    llm = LLM(model, ctx=8192, cache_tokens=n_req * 4224, max_requests=n_req, max_batch_tokens=4096)
+    rng = random.Random(0)
+    prompts = [[rng.randrange(cfg.vocab_size) for _ in range(rng.randint(16, 4096))] for _ in range(n_req)]
+    llm.generate(prompts[:4], max_tokens=4, temperature=0.0)          # loads and warms every kernel
+    pinned = [torch.tensor(p, dtype=torch.int32).pin_memory() for p in prompts]
+    clocks = ClockSampler()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    l0 = model.kernels.launches
+    with clocks:
+        e0.record()
+        outs = llm.generate([p.tolist() for p in pinned], max_tokens=new, temperature=0.0)
+        e1.record()
+        torch.cuda.synchronize()
+    llm.engine.check()
+    ms = e0.elapsed_time(e1)
+    n_in, n_out = sum(map(len, prompts)), sum(map(len, outs))
+    c = llm.last_counters
+    line = base_line("tokens/s through the scheduler (Llama-4-Maverick-shaped, 64 requests, prompts 16-4096)",
+                     (n_in + n_out) * 1e3 / ms, "tok/s", c["steps"], 1, ms / max(c["steps"], 1),
+                     {"model": "llama4-maverick-shaped", "layers": 4, "layers_full": 48, "dense_layers": 2, "moe_layers": 2,
+                      "hidden": 5120, "q_heads": 40, "kv_heads": 8, "head_dim": 128, "experts": 128, "top_k": 1,
+                      "expert_ffn": 8192, "dense_ffn": 16384, "vocab": 202048, "requests": n_req,
+                      "prompt_tokens": n_in, "new_tokens": n_out, "max_batch_tokens": 4096, "page_size": 64,
+                      "parallelism": "single-gpu"})
+    line.update({"gpu_launches": model.kernels.launches - l0, "clocks": clocks.summary(),
+                 "scheduler": {"steps": c["steps"], "preemptions": c["preemptions"], "steps_ahead": c["steps_ahead"]},
+                 "e2e": {"value": round((n_in + n_out) * 1e3 / ms, 2), "unit": "tok/s",
+                         "h2d_bytes_per_step": round(4 * 4 * (n_in + n_out) / max(c["steps"], 1)), "d2h_bytes_per_step": 4 * n_req,
+                         "note": "the whole run goes through LLM.generate: host token lists in, host token lists out"}})
+    print(json.dumps(line))
+
+
+def run_long(args):
+    """BASELINE configuration 5: one request with a prompt of 131,072 tokens run in portions of 8,192 (many chunk
+    windows on the chunked layers, the whole context on the layers without rotation), then 256 decode steps at
+    batch 1, and the same at batch 4 (four such requests).  `value` is the decode rate at batch 1."""
+    import torch
+    from spite_b200.engine import Engine, StepEntry
+    layers, C, portion, n_dec = args.layers if args.layers != FULL_LAYERS else 8, 131072, 8192, 256
+    cfgd = dict(SCOUT, num_hidden_layers=layers, max_position_embeddings=C + 1024)
+    cfg, model = build_model(cfgd)
+    ks, pk = model.kernels, peaks()
+    pk, pk_src = pk
+    engine = Engine(model, cache_tokens=4 * (C + 1024), page_size=64, max_requests=4, max_positions=C + 1024)
+    g = torch.Generator().manual_seed(3)
+    toks = torch.randint(0, cfg.vocab_size, (C,), generator=g, dtype=torch.int32).pin_memory()
+    clocks = ClockSampler()
+
+    def prefill(rid):
+        ms = []
+        for i in range(0, C, portion):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            engine.step([StepEntry(rid, toks[i:i + portion].tolist(), [portion - 1] if i + portion == C else [])])
+            e1.record()
+            torch.cuda.synchronize()
+            ms.append(e0.elapsed_time(e1))
+        return ms
+
+    def decode(rids, steps, warmup=3):
+        ids = torch.randint(0, cfg.vocab_size, (steps + warmup, len(rids)), generator=g).tolist()
+        for i in range(warmup):
+            ks.argmax(engine.step([StepEntry(r, [ids[i][j]], [0]) for j, r in enumerate(rids)]))
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(warmup, warmup + steps):
+            ks.argmax(engine.step([StepEntry(r, [ids[i][j]], [0]) for j, r in enumerate(rids)]))
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        ctxs = [engine.cached_tokens(r) for r in rids]
+        nbytes = decode_bytes(model, engine, ctxs, [float(n) for n in distinct_experts(model)])
+        return ms, nbytes / (ms * 1e-3) / 1e9
+
+    l0 = ks.launches
+    with clocks:
+        pre = prefill(0)
+        ms1, gbs1 = decode([0], n_dec)
+    for r in (1, 2, 3):
+        prefill(r)
+    ms4, gbs4 = decode([0, 1, 2, 3], n_dec)
+    engine.check()
+    line = base_line("decode tok/s at batch 1 after a 131,072-token prompt (Llama-4-Scout-shaped)", 1e3 / ms1, "tok/s",
+                     n_dec, 3, ms1,
+                     {"model": "llama4-scout-shaped", "layers": layers, "layers_full": 48, "hidden": 5120, "q_heads": 40,
+                      "kv_heads": 8, "head_dim": 128, "experts": 16, "top_k": 1, "expert_ffn": 8192, "vocab": 202048,
+                      "chunk": 8192, "nope_every": 4, "global_batch": 1, "seq_len": C, "portion": portion,
+                      "page_size": 64, "parallelism": "single-gpu",
+                      "l2": "inputs larger than L2 (weights and cache read per step exceed 126 MB)"})
+    line.update({
+        "gpu_launches": ks.launches - l0, "clocks": clocks.summary(),
+        "prefill": {"value": round(C * 1e3 / sum(pre), 1), "tokens": C, "ms": round(sum(pre), 1),
+                    "ms_first_portion": round(pre[0], 2), "ms_last_portion": round(pre[-1], 2)},
+        "roofline": {"bound": "hbm", "achieved": round(gbs1, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(gbs1 / pk["hbm_gbs"], 4), "peaks": pk_src},
+        "points": {"decode_b1": round(1e3 / ms1, 1), "decode_b1_ms": round(ms1, 3), "decode_b1_hbm_frac": round(gbs1 / pk["hbm_gbs"], 4),
+                   "decode_b4": round(4e3 / ms4, 1), "decode_b4_ms": round(ms4, 3), "decode_b4_hbm_frac": round(gbs4 / pk["hbm_gbs"], 4)},
+        "e2e": {"value": round(1e3 / ms1, 2), "unit": "tok/s", "h2d_bytes_per_step": 4 * (6 + 2 * ((C + 1024) // 64 + 1)),
+                "d2h_bytes_per_step": 0, "note": "token ids come from pinned host memory every step; the sampled ids stay on the device"}})
+    print(json.dumps(line))
+
+
+def run_ours(args):
+    import torch
+    from spite_b200.engine import Engine, StepEntry
+    from spite_b200.engine.scheduler import Request, Scheduler
+    from spite_b200.sampling import Sampler, SamplingParams
+
+    dev = "cuda:0"
+    cfgd = dict(SCOUT, num_hidden_layers=args.layers)
+    cfg, model = build_model(cfgd)
     ks = model.kernels
     B, ctx = args.batch, args.context
     page = 64
@@ -187,8 +354,12 @@ def run_ours(args):
         pflops = prefill_flops(cfgd, T)
         if os.environ.get("SPITE_BENCH_VERBOSE"):
             print("prefill runs (ms):", [round(x, 2) for x in pre_ms], file=sys.stderr)
+        floor = prefill_roofline_ms(cfgd, T, pk)
+        # frac: the step's flops / time / the sustained bf16 peak.  frac_kernel_roofline: the time the step's kernels
+        # cannot beat one by one (the experts' weights make their products memory-bound at this length) / time
         return {"value": round(T * 1000.0 / pms, 1), "tokens": T, "ms": round(pms, 3),
-                "frac": round(pflops / (pms * 1e-3) / (pk["bf16_tflops_sustained"] * 1e12), 4)}
+                "frac": round(pflops / (pms * 1e-3) / (pk["bf16_tflops_sustained"] * 1e12), 4),
+                "roofline_ms": round(floor, 3), "frac_kernel_roofline": round(floor / pms, 4)}
 
     if args.only_prefill:
         print(json.dumps({"prefill": measure_prefill(), "layers": args.layers}))
@@ -196,20 +367,21 @@ def run_ours(args):
     clocks = ClockSampler()
     ms_step, launches, _ = timed_decode(B, args.steps, args.warmup, clocks)
     value = B * 1000.0 / ms_step
-    # experts the batch's tokens use, layer by layer: the mean over a few more (untimed) steps of the same kind
-    probe = 8
-    occupy(B, ctx - probe - 1)
-    ptoks = torch.randint(0, vocab, (probe, B), generator=g).tolist()
-    distinct = [0.0] * len(model.blocks)
-    for i in range(probe):
-        engine.step([StepEntry(r, [ptoks[i][r]], [0]) for r in range(B)])
-        for li, blk in enumerate(model.blocks):
-            r = getattr(blk.ffn, "last_routing", None)
-            if r is not None:
-                distinct[li] += torch.unique(r.expert_ids).numel() / probe
-    end_ctx = ctx - 1
-    nbytes = decode_bytes(model, engine, [end_ctx] * B, distinct)
+    def step_bytes(n_req):
+        """Bytes a decode step of `n_req` requests at the end of the context has to read; the experts its tokens
+        use, layer by layer, are the mean over a few more (untimed) steps of the same kind."""
+        probe = 8
+        occupy(n_req, ctx - probe - 1)
+        ptoks = torch.randint(0, vocab, (probe, n_req), generator=g).tolist()
+        distinct = [0.0] * len(model.blocks)
+        for i in range(probe):
+            engine.step([StepEntry(r, [ptoks[i][r]], [0]) for r in range(n_req)])
+            for li, n in enumerate(distinct_experts(model)):
+                distinct[li] += n / probe
+        return decode_bytes(model, engine, [ctx - 1] * n_req, distinct)
+    nbytes = step_bytes(B)
     achieved = nbytes / (ms_step * 1e-3) / 1e9
+    engine.check()
     if args.only_decode:
         print(json.dumps({"decode_ms_per_step": round(ms_step, 4), "tok_per_s": round(value, 1), "batch": B,
                           "layers": args.layers, "launches": launches, "GBps": round(achieved, 1)}))
@@ -247,12 +419,19 @@ def run_ours(args):
     points = {}
     if not args.skip_points:
         for nb in (1, 64):
-            ms_b, _, _ = timed_decode(nb, max(4, args.steps // 2), 3)
-            points[f"decode_b{nb}"] = round(nb * 1000.0 / ms_b, 1)
+            pc = ClockSampler()
+            ms_b, _, _ = timed_decode(nb, max(4, args.steps // 2), 3, pc)
+            gbs = step_bytes(nb) / (ms_b * 1e-3) / 1e9
+            # each point with its own step time, fraction of the HBM roofline and clocks (flat: the record keeps one level)
+            points.update({f"decode_b{nb}": round(nb * 1000.0 / ms_b, 1), f"decode_b{nb}_ms": round(ms_b, 4),
+                           f"decode_b{nb}_GBps": round(gbs, 1), f"decode_b{nb}_hbm_frac": round(gbs / pk["hbm_gbs"], 4),
+                           f"decode_b{nb}_sm_mhz": pc.summary()["sm_mhz"]})
         for r in list(engine.cache.requests):
             engine.finish(r)
+    engine.check()
 
     prefill = measure_prefill()
+    engine.check()
 
     line = {
         "metric": "decode tok/s (Llama-4-Scout-shaped, batch 8, context 8192)",
@@ -301,6 +480,8 @@ def main(argv=None):
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--config", choices=["scout", "maverick", "long"], default="scout",
+                    help="scout: the benchmark line; maverick, long: two further workloads, one line each")
     ap.add_argument("--layers", type=int, default=FULL_LAYERS)
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=8192)
@@ -314,6 +495,12 @@ def main(argv=None):
     if args.gpus != 1:
         print(f"bench.py measures one GPU; --gpus {args.gpus} is not supported by this engine")
         return 2
+    if args.config == "maverick":
+        run_maverick(args)
+        return 0
+    if args.config == "long":
+        run_long(args)
+        return 0
     if args.warmup < 3:
         args.warmup = 3
     if args.steps < 1 or args.steps + args.warmup + 16 > args.context:
