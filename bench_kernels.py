@@ -35,6 +35,7 @@ def main(argv=None):
     ap.add_argument("--small", action="store_true")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--case", default="", help="run only the cases whose name contains this text")
+    ap.add_argument("--experts", type=int, default=16, help="experts of the grouped products (128: Maverick's)")
     args = ap.parse_args(argv)
     dev = "cuda:0"
     torch.cuda.set_device(0)
@@ -42,7 +43,7 @@ def main(argv=None):
     pk, src = peaks()
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)       # larger than L2
     bf = torch.bfloat16
-    d, F, V, nq, nkv, hd, E = 5120, 8192, 202048, 40, 8, 128, 16
+    d, F, V, nq, nkv, hd, E = 5120, 8192, 202048, 40, 8, 128, args.experts
     if args.small:
         V = 32768
     rnd = lambda *s: (torch.randn(s, device=dev, dtype=torch.float32) * 0.05).to(bf)
@@ -149,7 +150,7 @@ def main(argv=None):
         offsets = torch.zeros(E + 1, dtype=torch.int32, device=dev)
         offsets[1:] = torch.cumsum(torch.bincount(ids, minlength=E), 0)
         return order.indices.to(torch.int32), offsets, int(ids.unique().numel())
-    for fam, Ms in (("moe_decode", (1, 8, 64)), ("moe_prefill", (512,) if args.small else (2048, 8192))):
+    for fam, Ms in (("moe_decode", (1, 8, 64)), ("moe_prefill", (512,) if args.small else (256, 512, 1024, 2048, 8192))):
         if not want(fam):
             continue
         w_gu, w_dn = rnd(E, 2 * F, d), rnd(E, d, F)

@@ -72,7 +72,7 @@ class Model:
     def kernel_libraries(self) -> list[str]:
         libs = {"elementwise", "gemm_simt"}
         if self.dtype == torch.bfloat16:
-            libs |= {"gemm_skinny", "gemm_stream", "gemm_tc", "gemm_tc_pair"}
+            libs |= {"gemm_skinny", "gemm_stream", "gemm_tc", "gemm_tc_pair", "gemm_tc_experts"}
         for _, part in self.parts():
             libs.update(part.kernel_libraries)
         return sorted(libs)

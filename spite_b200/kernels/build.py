@@ -31,6 +31,7 @@ LIBRARIES = {
     "gemm_skinny": (["gemm_skinny.cu"], []),
     "gemm_tc": (["gemm_tc.cu"], []),
     "gemm_tc_pair": (["gemm_tc_pair.cu"], []),
+    "gemm_tc_experts": (["gemm_tc_experts.cu"], []),
     "gemm_stream": (["gemm_stream.cu"], []),
     "attention": (["attention.cu"], []),
     "attention_mma": (["attention_mma.cu"], []),

@@ -77,7 +77,7 @@ class SampleParams(C.Structure):
 # Libraries whose kernels wait on mbarriers with a limit.  A kernel that gives up records a code in its
 # library's word of one small buffer in pinned host memory, which the device writes directly: the host
 # reads it after any point at which it has waited for a step's results, without another copy or wait.
-_WAITING_LIBRARIES = ("gemm_tc", "gemm_tc_pair", "gemm_stream", "attention_tc", "attention_decode")
+_WAITING_LIBRARIES = ("gemm_tc", "gemm_tc_pair", "gemm_stream", "attention_tc", "attention_decode", "gemm_tc_experts")
 _error_words = None          # pinned int32 [len(_WAITING_LIBRARIES)], one per process
 _configured: set = set()
 
@@ -130,6 +130,10 @@ class CudaKernels(KernelSet):
         # (down): what the pair saves in shared-memory traffic, the part-filled last tile of 256 rows gives back.
         self.tc_pair_min_group_rows = int(os.environ.get("SPITE_TC_PAIR_MIN_GROUP_ROWS", "512")) or (1 << 30)
         self.skinny_tall_rows = int(os.environ.get("SPITE_SKINNY_TALL_ROWS", "0"))
+        # grouped products with at most this many rows per group on average run with the operands swapped
+        self.use_tc_experts = os.environ.get("SPITE_NO_TC_EXPERTS", "") == ""
+        self.tc_experts_max_group_rows = int(os.environ.get("SPITE_TC_EXPERTS_MAX_GROUP_ROWS", "64"))
+        self.tc_experts_down_min_groups = 64
         # the TMA weight-streaming kernel for decode products: k elements per work item, shared memory per block
         self.use_stream = os.environ.get("SPITE_NO_STREAM_GEMM", "") == ""
         self.stream_split_k = int(os.environ.get("SPITE_STREAM_SPLIT_K", "0"))     # 0: splits chosen per product
@@ -275,6 +279,14 @@ class CudaKernels(KernelSet):
                     _check(st, "gather_rows")
                     p = GemmParams.from_buffer_copy(p)
                     p.A = keep.data_ptr()          # rows are in place now; a_rows only indexes the row scale
+                if grouped and self.use_tc_experts and self._few_rows_per_group(p):
+                    # groups of few rows each (experts of a prompt portion): the weights as the 128-row operand, a
+                    # group's tokens as the instruction's columns
+                    st = self._lib("gemm_tc_experts").spite_gemm_tc_experts(C.byref(p), self.sm_count, self._stream())
+                    if st != -2:
+                        self._count("gemm_tc_experts", 1)
+                        _check(st, what + " (tcgen05, experts)")
+                        return
                 if p.M >= (self.tc_pair_min_group_rows * p.n_groups if grouped else self.tc_pair_min_rows):
                     # a product of many rows (per group) on pairs of multiprocessors (tcgen05 cta_group::2)
                     st = self._lib("gemm_tc_pair").spite_gemm_tc_pair(C.byref(p), self.sm_count // 2, self._stream())
@@ -298,6 +310,21 @@ class CudaKernels(KernelSet):
         st = self._lib("gemm_simt").spite_gemm_simt(self._dt, C.byref(p), self._stream())
         self._count("gemm_simt", 1)
         _check(st, what)
+
+    def _few_rows_per_group(self, p) -> bool:
+        """Does a grouped product go to the kernel with swapped operands?  Measured on B200 at Scout's expert
+        shapes (us, swapped against 128-row tiles).  Gate/up with SwiGLU, 16 experts: 427/437 at 256 tokens,
+        437/464 at 1,024, 630/503 at 2,048 (half the groups then exceed a token tile and run twice); 128
+        experts: 3,159/3,300 at 1,024, 3,284/3,849 at 8,192.  Down product into the residual stream, 16
+        experts: 264/244 at 256, 276/254 at 1,024, 344/293 at 2,048; 128 experts: 1,749/1,705 at 2,048,
+        1,905/2,006 at 8,192.  So: gate/up up to 64 rows a group on average, the down product only with
+        many groups of 32 to 64 rows."""
+        avg = p.M / p.n_groups
+        if p.epilogue == EPI_SWIGLU:
+            return avg <= self.tc_experts_max_group_rows
+        if p.epilogue == EPI_ADD_F32:
+            return p.n_groups >= self.tc_experts_down_min_groups and 32 <= avg <= self.tc_experts_max_group_rows
+        return False
 
     def _gemm_stream(self, p, max_rows_per_group, grouped):
         """The TMA weight-streaming kernel for decode steps: picks the k splits so that the work items
@@ -352,8 +379,9 @@ class CudaKernels(KernelSet):
         """Error code left by a product kernel's block that gave up waiting (0: none); clears it. Synchronises."""
         torch.cuda.synchronize(self.device)
         words = _error_buffer()
-        code = int(words[0]) or int(words[1]) or int(words[2])
+        code = int(words[0]) or int(words[1]) or int(words[2]) or int(words[5])
         words[:3] = 0
+        words[5] = 0
         return code
 
     def linear(self, x, w, out, *, accumulate=False, row_scale=None):

@@ -63,6 +63,28 @@ def gemm_calls(libs):
     ]
 
 
+def test_the_experts_product_refuses_malformed_calls(libs):
+    lib = libs["gemm_tc_experts"]
+    offsets = torch.tensor([0, 2, 4], dtype=torch.int32, device=DEV)
+
+    def case(**kw):
+        p, keep = gemm_case(M=4, N=64, K=128)
+        p.group_offsets, p.n_groups, p.epilogue, p.w_group_stride = offsets.data_ptr(), 2, 2, 64 * 128
+        p.C = canary((4, 64)).data_ptr()
+        for k, v in kw.items():
+            setattr(p, k, v)
+        return p, keep
+    for kw, want in ((dict(A=None), BAD_ARG), (dict(W=None), BAD_ARG), (dict(C=None), BAD_ARG), (dict(group_offsets=None), BAD_ARG),
+                     (dict(n_groups=0), BAD_ARG), (dict(N=0), BAD_ARG), (dict(K=0), BAD_ARG), (dict(lda=8), BAD_ARG),
+                     (dict(epilogue=7), BAD_ARG), (dict(epilogue=0), UNSUPPORTED), (dict(K=100, lda=100), UNSUPPORTED),
+                     (dict(w_group_stride=5), UNSUPPORTED), (dict(n_groups=4000), UNSUPPORTED)):
+        p, keep = case(**kw)
+        assert lib.spite_gemm_tc_experts(C.byref(p), 148, None) == want, kw
+    assert lib.spite_gemm_tc_experts(None, 148, None) == BAD_ARG
+    p, keep = case()
+    assert lib.spite_gemm_tc_experts(C.byref(p), 0, None) == BAD_ARG
+
+
 @pytest.mark.parametrize("which", range(5))
 def test_products_refuse_malformed_calls(libs, which):
     name, call = gemm_calls(libs)[which]

@@ -113,12 +113,18 @@ def test_linear_swiglu(ks, M, F, K):
 @pytest.mark.parametrize("M,E,F,K", [(1, 3, 24, 48), (9, 5, 40, 96), (150, 7, 72, 64), (64, 16, 48, 128),
                                      (60, 3, 24, 64), (8, 128, 16, 32), (1500, 16, 160, 256), (300, 4, 128, 72),
                                      (7, 5, 40, 4096), (16, 9, 72, 128), (1, 3, 2048, 64), (8, 16, 100, 6144), (4, 3, 4096, 64),
-                                     (1700, 3, 160, 256), (2100, 4, 72, 64), (18000, 35, 48, 64)])
+                                     (1700, 3, 160, 256), (2100, 4, 72, 64), (18000, 35, 48, 64),
+                                     # groups of few rows at prompt lengths: the kernel with the weights as the 128-row
+                                     # operand; one group far larger than the rest (cut into token tiles), widths and
+                                     # depths that are no multiple of a tile
+                                     (2048, 16, 256, 512), (4096, 128, 136, 192), (700, 9, 200, 328), (520, 5, 128, 64)])
 def test_grouped_products(ks, M, E, F, K):
     """Tokens sorted by expert, some experts empty; SwiGLU in, scatter-add out."""
     g = torch.Generator().manual_seed(10)
     ids = torch.randint(0, E, (M,), generator=g)
     ids[ids == 1] = 0                                   # expert 1 stays empty
+    if M in (700, 520):
+        ids[:M - 200] = E - 1                           # one group with most of the tokens
     order = torch.sort(ids, stable=True)
     rows = order.indices.to(torch.int32)
     offsets = torch.zeros(E + 1, dtype=torch.int32)
@@ -128,13 +134,23 @@ def test_grouped_products(ks, M, E, F, K):
     scale = torch.rand(M, generator=g) + 0.5
     r = ref_set(ks.dtype)
     a = torch.zeros((M, F), dtype=ks.dtype, device=DEV)
+    swapped = ks.launches_by_library["gemm_tc_experts"]
     ks.grouped_linear_swiglu(x.to(DEV), w_gu.to(DEV), rows.to(DEV), offsets.to(DEV), scale.to(DEV), a)
+    if ks.dtype == torch.bfloat16 and 16 < M <= 64 * E and K % 8 == 0:
+        assert ks.launches_by_library["gemm_tc_experts"] == swapped + 1   # few rows a group: the weights are the 128-row operand
     a_ref = torch.zeros((M, F), dtype=torch.float64)
     r.grouped_linear_swiglu(x, w_gu, rows, offsets, scale, a_ref)
     close(a, a_ref, TOL[ks.dtype], "grouped_linear_swiglu")
     h = rnd((M, K), torch.float32, 14)
     hd = h.to(DEV).clone()
+    if M in (4096, 700, 520) and ks.dtype == torch.bfloat16:
+        # the down product with swapped operands too, whatever the sizes (a group of 300 to 500 rows is cut in two)
+        ks.tc_experts_max_group_rows, ks.tc_experts_down_min_groups = 256, 1
+    swapped = ks.launches_by_library["gemm_tc_experts"]
     ks.grouped_linear_accumulate(a, w_d.to(DEV), rows.to(DEV), offsets.to(DEV), hd)
+    if M in (4096, 700, 520) and ks.dtype == torch.bfloat16:
+        assert ks.launches_by_library["gemm_tc_experts"] == swapped + 1
+    ks.tc_experts_max_group_rows, ks.tc_experts_down_min_groups = 64, 64
     h_ref = h.double().clone()
     r.grouped_linear_accumulate(a.cpu(), w_d, rows, offsets, h_ref)
     close(hd, h_ref, 2e-5 if ks.dtype == torch.float32 else 2e-3, "grouped_linear_accumulate")
