@@ -352,7 +352,7 @@ def run_ours(args):
             pre_ms.append(e0.elapsed_time(e1))
         pms = sorted(pre_ms[1:])[2]                       # the median of five runs after one warm-up
         pflops = prefill_flops(cfgd, T)
-        if os.environ.get("SPITE_BENCH_VERBOSE"):
+        if args.verbose:
             print("prefill runs (ms):", [round(x, 2) for x in pre_ms], file=sys.stderr)
         floor = prefill_roofline_ms(cfgd, T, pk)
         # frac: the step's flops / time / the sustained bf16 peak.  frac_kernel_roofline: the time the step's kernels
@@ -489,6 +489,7 @@ def main(argv=None):
     ap.add_argument("--no-graphs", action="store_true", help="launch every kernel of a decode step by itself")
     ap.add_argument("--only-decode", action="store_true", help="measure the decode step only (for profiling)")
     ap.add_argument("--only-prefill", action="store_true", help="measure the prefill step only (for profiling)")
+    ap.add_argument("--verbose", action="store_true", help="print the single prefill timings to standard error")
     args = ap.parse_args(argv)
     if args.impl == "reference":
         return run_reference(args)

@@ -202,6 +202,24 @@ def main(argv=None):
             attention_case("attention_prefill", 1, 2048, 8192, ("chunk", 8192))
             attention_case("attention_prefill", 1, 8192, 131072, ("full", 0))     # a late portion of a long prompt
 
+    # ---- rotation + per-head norm + cache append, at decode and at prompt lengths
+    if want("small"):
+        from spite_b200.parts import QkNorm, Rotation
+        for M in (8, 2048):
+            pages_per = -(-M // P) + 1
+            segs = [Segment(0, 0, 0, M, 0, True)]
+            batch = build_step_batch(segs, [[0] * M], [[]], [[list(range(pages_per))]], dev)
+            inv_freq = torch.tensor([500000.0 ** (-2.0 * i / hd) for i in range(hd // 2)], dtype=torch.float32, device=dev)
+            def make_prepare(M=M, batch=batch, pages_per=pages_per):
+                qkv = rnd(M, (nq + 2 * nkv) * hd)
+                q = torch.empty((M, nq * hd), dtype=bf, device=dev)
+                kv = torch.zeros((2, pages_per, nkv, P, hd), dtype=bf, device=dev)
+                cache = LayerCache(0, kv, None, P, True)
+                return lambda: ks.qk_prepare(qkv, q, batch, cache, num_heads=nq, rotation=Rotation(inv_freq, "neighbours"),
+                                             qk_norm=QkNorm(1e-5), temperature=None)
+            nbytes = M * ((nq + 2 * nkv) * hd * 2 + (nq + 2 * nkv) * hd * 2)
+            report("small", f"qk_prepare M={M}", timed_rotating(make_prepare, max(nbytes, 64 << 20) if M == 8 else nbytes), nbytes=nbytes)
+
     # ---- the small kernels of a decode step
     if want("small"):
         for M in (8, 64):

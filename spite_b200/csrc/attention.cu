@@ -24,7 +24,9 @@ __device__ __forceinline__ void store_pair(__nv_bfloat16* p, float a, float b) {
 
 // grid (tokens, ceil(heads_total / heads_per_block)), block 32 * warps: a warp takes the heads
 // blockIdx.y * heads_per_block + warp, + warps, ... of q, k and v, one at a time.
-template <typename T>
+// HALVES: the two halves of the rotating part pair up (else neighbours; then every index below is known when
+// the kernel is compiled, and a pair moves as one word).
+template <typename T, bool HALVES>
 __global__ void __launch_bounds__(256) qk_prepare_kernel(const QkPrepareParams p, const StepTokens b,
                                                          const PagedCache c, const int heads_per_block) {
     pdl_wait();
@@ -50,20 +52,29 @@ __global__ void __launch_bounds__(256) qk_prepare_kernel(const QkPrepareParams p
     // same for every head: cos and sin of pos * inv_freq[i], once per warp.
     constexpr int MAXP = 4;                                  // pairs per lane: head_dim <= 256
     const int rot = p.inv_freq ? p.rotary_dim : 0;
-    const bool halves = p.pairing == SPITE_PAIR_HALVES;
+    constexpr bool halves = HALVES;
+    // cos and sin of a position's angles are the same for every head: the block computes each once (the exact
+    // sincosf of an angle of thousands of radians is the most expensive thing here) and its warps read them
+    __shared__ float cs_s[128], sn_s[128];
+    for (int i = threadIdx.x; 2 * i < rot; i += blockDim.x) sincosf((float)pos * p.inv_freq[i], &sn_s[i], &cs_s[i]);
+    __syncthreads();
     float cs[MAXP], sn[MAXP];
-    int e0[MAXP], e1[MAXP];
+    int e0[MAXP], e1[MAXP];                                  // (neighbours: known at compile time, no registers)
 #pragma unroll
     for (int r = 0; r < MAXP; ++r) {
         const int i = lane + 32 * r;
         cs[r] = 1.f; sn[r] = 0.f;
         e0[r] = 2 * i; e1[r] = 2 * i + 1;
         if (2 * i < rot) {
-            sincosf((float)pos * p.inv_freq[i], &sn[r], &cs[r]);
+            cs[r] = cs_s[i]; sn[r] = sn_s[i];
             if (halves) { e0[r] = i; e1[r] = i + rot / 2; }
         }
     }
 
+    // (Measured and not kept: a warp loading four heads before working on the first, 61 against 33 us for 2,048
+    // tokens of 56 heads; one head a warp with more blocks, 51 us.)
+    const bool norm = p.qk_norm_eps > 0.f;
+    const bool norm_first = norm && p.norm_before_rotation;
     for (int head = blockIdx.y * heads_per_block + warp; head < head_end; head += n_warps) {
         const T* in = (const T*)p.qkv + (size_t)t * heads_total * hd + (size_t)head * hd;
         const bool is_q = head < nq, is_v = head >= nq + nkv;
@@ -86,8 +97,6 @@ __global__ void __launch_bounds__(256) qk_prepare_kernel(const QkPrepareParams p
         }
         // q or k (rotation: crates/spite-rope/src/lib.rs:83-91; norm after it: llama4.rs:161-176)
         const float* gain = is_q ? p.q_gain : p.k_gain;
-        const bool norm = p.qk_norm_eps > 0.f;
-        const bool norm_first = norm && p.norm_before_rotation;
         float x0[MAXP], x1[MAXP];
 #pragma unroll
         for (int r = 0; r < MAXP; ++r) {
@@ -232,15 +241,21 @@ SPITE_API int spite_qk_prepare(int dtype, const QkPrepareParams* p, const StepTo
     const int heads = p->num_heads + 2 * c->num_kv_heads;
     // few tokens: four heads a block, so that the step still fills the device; many: a block per token
     const bool many = b->n_tokens >= 1024;
-    const int heads_per_block = many ? heads : 4;
+    const int heads_per_block = many ? 16 : 4;
     const int threads = many ? 256 : 128;
     dim3 grid(b->n_tokens, (heads + heads_per_block - 1) / heads_per_block);
     if (grid.y > 65535) return SPITE_UNSUPPORTED;
     if (((uintptr_t)p->qkv | (uintptr_t)p->q_out | (uintptr_t)c->kv) & 7) return SPITE_UNSUPPORTED;   // pairs move as one word
     cudaStream_t st = (cudaStream_t)stream;
-    if (dtype == SPITE_DT_F32) SPITE_LAUNCH(qk_prepare_kernel<float>, grid, threads, 0, st, *p, *b, *c, heads_per_block);
-    else if (dtype == SPITE_DT_BF16) SPITE_LAUNCH(qk_prepare_kernel<__nv_bfloat16>, grid, threads, 0, st, *p, *b, *c, heads_per_block);
-    else return SPITE_BAD_ARG;
+    const bool halves = p->pairing == SPITE_PAIR_HALVES && p->inv_freq;
+    if (dtype != SPITE_DT_F32 && dtype != SPITE_DT_BF16) return SPITE_BAD_ARG;
+    if (dtype == SPITE_DT_F32) {
+        if (halves) SPITE_LAUNCH((qk_prepare_kernel<float, true>), grid, threads, 0, st, *p, *b, *c, heads_per_block);
+        else SPITE_LAUNCH((qk_prepare_kernel<float, false>), grid, threads, 0, st, *p, *b, *c, heads_per_block);
+    } else {
+        if (halves) SPITE_LAUNCH((qk_prepare_kernel<__nv_bfloat16, true>), grid, threads, 0, st, *p, *b, *c, heads_per_block);
+        else SPITE_LAUNCH((qk_prepare_kernel<__nv_bfloat16, false>), grid, threads, 0, st, *p, *b, *c, heads_per_block);
+    }
     return spite_launch_status();
 }
 

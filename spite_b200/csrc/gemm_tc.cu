@@ -246,10 +246,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 // the tile's width plus a fixed cost for filling and draining the pipeline.
 int choose_bnh(const GemmParams& p, int row_tiles, int n_blocks) {
     const bool dual = p.epilogue == EPI_SWIGLU;
-    if (const char* e = getenv("SPITE_TC_BNH")) {              // a forced half-tile height, for measurements
-        const int v = atoi(e);
-        if (v >= 32 && v <= 128 && v % (dual ? 32 : 16) == 0) return v;
-    }
     int best = 128;
     long long best_cost = -1;
     for (int bnh = 128; bnh >= 32; bnh -= 16) {

@@ -230,13 +230,8 @@ static inline EncodeTiledFn encode_fn() {
 
 // L2 promotion of the TMA loads: 256 bytes (a load of a 128-byte row segment brings its neighbour along;
 // every kernel here walks its rows onward, so the neighbour is the next k block).  Measured on B200 in the
-// decode step against 128 bytes: 1,096 against 1,053 tokens/s.  SPITE_TMA_L2_PROMOTION=128|64|0 overrides.
-static inline CUtensorMapL2promotion l2_promotion() {
-    static int v = -1;
-    if (v < 0) { const char* e = getenv("SPITE_TMA_L2_PROMOTION"); v = e ? atoi(e) : 256; }
-    return v == 128 ? CU_TENSOR_MAP_L2_PROMOTION_L2_128B : v == 64 ? CU_TENSOR_MAP_L2_PROMOTION_L2_64B
-         : v == 0 ? CU_TENSOR_MAP_L2_PROMOTION_NONE : CU_TENSOR_MAP_L2_PROMOTION_L2_256B;
-}
+// decode step against 128 bytes: 1,096 against 1,053 tokens/s.
+static inline CUtensorMapL2promotion l2_promotion() { return CU_TENSOR_MAP_L2_PROMOTION_L2_256B; }
 
 // bfloat16 tensor of `rank` dimensions (innermost first), 128-byte swizzle, zero fill outside.
 // `strides_bytes` has rank - 1 entries (the innermost dimension is contiguous).

@@ -112,39 +112,40 @@ class CudaKernels(KernelSet):
         self.attention_scratch_bytes = 0   # partial results of the last split-key attention call
         self.launches_by_library = collections.Counter()   # the same, by kernel library
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
-        self.use_tcgen05 = os.environ.get("SPITE_NO_TCGEN05", "") == ""
-        self.use_tcgen05_attention = os.environ.get("SPITE_NO_TCGEN05_ATTENTION", "") == ""
-        # fewest tokens of a request in a step that go to the tcgen05 attention kernel (0: one full tile of rows)
-        self.attention_tc_min_tokens = int(os.environ.get("SPITE_ATTENTION_TC_MIN_TOKENS", "0"))
-        self.attention_max_splits = int(os.environ.get("SPITE_ATTENTION_MAX_SPLITS", "24"))    # most key splits of decode attention: beyond about
-        # twenty the merge by the last block costs more than the extra blocks bring (one request at 8,192 keys: 22 us
-        # with 37 splits, 17.6 us with 18)
-        self.use_decode_attention = os.environ.get("SPITE_NO_DECODE_ATTENTION", "") == ""     # the TMA-fed decode kernel
+        # Which kernel takes which shape.  The numbers are measured choices (what was measured stands beside
+        # each); they are plain attributes, so a measurement script can set another value on the object.
+        # One switch is read from the environment, for finding a fault: SPITE_NO_TCGEN05=1 keeps every
+        # tcgen05 kernel (products and attention) out, and shapes fall to the mma.sync and CUDA-core kernels.
+        no_tc = os.environ.get("SPITE_NO_TCGEN05", "") not in ("", "0")
+        self.use_tcgen05 = not no_tc
+        self.use_tcgen05_attention = not no_tc
+        self.attention_tc_min_tokens = 0       # fewest tokens of a request in a step that go to the tcgen05 attention (0: one full tile of rows)
+        # most key splits of decode attention: beyond about twenty the merge by the last block costs more than the
+        # extra blocks bring (one request at 8,192 keys: 22 us with 37 splits, 17.6 us with 18)
+        self.attention_max_splits = 24
+        self.use_decode_attention = True       # the TMA-fed decode kernel (head sizes 64 and 128, pages of a multiple of 64 keys)
         # row counts up to which the weight-streaming kernel is preferred over the tcgen05 one
-        self.skinny_max_rows = int(os.environ.get("SPITE_SKINNY_MAX_ROWS", "16"))
-        self.skinny_blocks = int(float(os.environ.get("SPITE_SKINNY_BLOCKS_PER_SM", "2")) * self.sm_count)
-        # one-group products of at least this many rows run on pairs of multiprocessors (0: never)
-        self.tc_pair_min_rows = int(os.environ.get("SPITE_TC_PAIR_MIN_ROWS", "256")) or (1 << 30)
-        # grouped products with at least this many rows per group on average do too (0: never).  Measured at
-        # Scout's expert shapes with 512 rows a group: 1324 against 1340 us (gate/up) and 676 against 682 us
-        # (down): what the pair saves in shared-memory traffic, the part-filled last tile of 256 rows gives back.
-        self.tc_pair_min_group_rows = int(os.environ.get("SPITE_TC_PAIR_MIN_GROUP_ROWS", "512")) or (1 << 30)
-        self.skinny_tall_rows = int(os.environ.get("SPITE_SKINNY_TALL_ROWS", "0"))
+        self.skinny_max_rows = 16
+        self.skinny_blocks = 2 * self.sm_count
+        # one-group products of at least this many rows run on pairs of multiprocessors
+        self.tc_pair_min_rows = 256
+        # grouped products with at least this many rows per group on average do too.  Measured at Scout's expert
+        # shapes with 512 rows a group: 1324 against 1340 us (gate/up) and 676 against 682 us (down): what the pair
+        # saves in shared-memory traffic, the part-filled last tile of 256 rows gives back.
+        self.tc_pair_min_group_rows = 512
+        self.skinny_tall_rows = 0
         # grouped products with at most this many rows per group on average run with the operands swapped
-        self.use_tc_experts = os.environ.get("SPITE_NO_TC_EXPERTS", "") == ""
-        self.tc_experts_max_group_rows = int(os.environ.get("SPITE_TC_EXPERTS_MAX_GROUP_ROWS", "64"))
+        self.use_tc_experts = True
+        self.tc_experts_max_group_rows = 64
         self.tc_experts_down_min_groups = 64
-        # the TMA weight-streaming kernel for decode products: k elements per work item, shared memory per block
-        self.use_stream = os.environ.get("SPITE_NO_STREAM_GEMM", "") == ""
-        self.stream_split_k = int(os.environ.get("SPITE_STREAM_SPLIT_K", "0"))     # 0: splits chosen per product
-        self.stream_item_cost = float(os.environ.get("SPITE_STREAM_ITEM_COST", "4"))   # fixed cost of an item, in k blocks
-        # (shared memory per block, blocks per multiprocessor) for up to 3 tokens and for more: measured in the decode
-        # step at Scout shapes, one token 2.90 ms with (110 KiB, 2) against 3.01 with (74 KiB, 3), eight tokens 7.10
-        # against 7.02, sixty-four alike.  SPITE_STREAM_SMEM / SPITE_STREAM_BLOCKS_PER_SM set both alike.
-        smem, per_sm = os.environ.get("SPITE_STREAM_SMEM"), os.environ.get("SPITE_STREAM_BLOCKS_PER_SM")
-        few = (int(smem or 110 * 1024), float(per_sm or 2))
-        more = (int(smem or 74 * 1024), float(per_sm or 3))
-        self.stream_shape = [(sm, int(b * self.sm_count)) for sm, b in (few, more)]
+        # the TMA weight-streaming kernel for decode products
+        self.use_stream = True
+        self.stream_split_k = 0                # a fixed k per work item (0: splits chosen per product, see _stream_splits)
+        self.stream_item_cost = 4.0            # fixed cost of a work item, in k blocks
+        # (shared memory per block, resident blocks) for up to 3 tokens and for more: measured in the decode step at
+        # Scout shapes, one token 2.90 ms with (110 KiB, 2 per multiprocessor) against 3.01 with (74 KiB, 3), eight
+        # tokens 7.10 against 7.02, sixty-four alike; one block per multiprocessor with 110 or 200 KiB: 3.2 and 3.1 ms
+        self.stream_shape = [(110 * 1024, 2 * self.sm_count), (74 * 1024, 3 * self.sm_count)]
         self._tickets, self._tickets_n = {}, 65536       # arrival counters of the k splits (zero between calls), per stream
 
     # ------------------------------------------------------------------ helpers

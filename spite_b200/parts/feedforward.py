@@ -7,8 +7,6 @@ input, SwiGLU experts, unweighted sum).
 """
 from __future__ import annotations
 
-import os
-
 import torch
 
 from ..config.specs import ConfigError
@@ -70,7 +68,7 @@ class MoESigmoidPrescaled(FeedForward):
         self.d, self.E, self.top_k = int(hidden_size), int(num_experts), int(top_k)
         self.f, self.fs = int(expert_size), int(shared_size)
         self.router = self.w_gate_up = self.w_down = self.ws_gate_up = self.ws_down = None
-        self.router_beside_shared = os.environ.get("SPITE_NO_SIDE_STREAM", "") == ""
+        self.router_beside_shared = True     # the router's two short kernels on a side stream beside the shared expert
         self.keep_router_logits = False      # `last_routing.logits` [tokens, experts] stays readable after a forward
 
     def param_specs(self):

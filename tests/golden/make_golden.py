@@ -122,4 +122,6 @@ def main(ref: Path):
 
 
 if __name__ == "__main__":
-    main(Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference"))
+    if len(sys.argv) != 2:
+        sys.exit("usage: make_golden.py <checkout of giveen/spite>")
+    main(Path(sys.argv[1]))
