@@ -236,6 +236,17 @@ def main(argv=None):
                 logits = torch.randn((M, V), device=dev)
                 return lambda: ks.argmax(logits)
             report("small", f"argmax M={M} V={V}", timed_rotating(make_argmax, M * V * 4), nbytes=M * V * 4)
+            def make_sample(M=M):
+                logits = torch.randn((M, V), device=dev) * 3
+                f32 = lambda v: torch.full((M,), v, dtype=torch.float32, device=dev)
+                ctxt = torch.randint(0, V, (M * 64,), dtype=torch.int32, device=dev)
+                offs = torch.arange(0, M * 64 + 1, 64, dtype=torch.int32, device=dev)
+                state = torch.arange(M, dtype=torch.int64, device=dev)
+                return lambda: ks.sample(logits, temperature=f32(0.7), top_k=torch.zeros(M, dtype=torch.int32, device=dev),
+                                         top_p=f32(0.95), min_p=f32(0.0), repetition_penalty=f32(1.1), context=ctxt,
+                                         context_offsets=offs, rng_state=state)
+            report("small", f"sample (temperature 0.7, top-p 0.95, penalty 1.1) M={M} V={V}",
+                   timed_rotating(make_sample, M * V * 4), nbytes=M * V * 4)
     return 0
 
 

@@ -19,6 +19,10 @@
  *    process exits.
  *  - rows * vocab must not exceed that size; a larger request is refused with
  *    status -2 and nothing is launched or written.
+ *  - A row that fits the shared memory of a cluster of eight blocks (up to
+ *    393,216 logits) is sampled there, as `spite_sample` does it, and the array
+ *    is not touched; longer rows go through the array.  The size limit above
+ *    holds either way, so that a caller need not know which applies.
  *  - All calls share the one array.  It keeps what the last call left in it;
  *    the kernel overwrites every element it reads before reading it, so nothing
  *    has to be cleared between calls.  Two calls that can run at the same time

@@ -229,6 +229,9 @@ def test_a_toy_mixer_with_state_is_registered_built_and_stepped():
 
     @register_mixer("toy_decaying_sum")
     class ToyDecayingSum(Mixer):
+        # nothing below reads device data on the host: a step of single tokens can be captured in a CUDA graph
+        graph_safe = True
+
         def __init__(self, ctx, hidden_size, decay):
             super().__init__(ctx)
             self.d, self.decay = hidden_size, decay
@@ -243,6 +246,14 @@ def test_a_toy_mixer_with_state_is_registered_built_and_stepped():
             return None, FixedState((self.d,), torch.float32)
 
         def forward(self, x, h, batch, cache):
+            if batch.max_seg_len == 1:
+                # one token a request: every request's state in one go, by its slot.  A row that pads a
+                # captured step is a copy of the first row and writes the same state to the same slot.
+                slots = batch.slots.long()
+                s = cache.state[slots] * self.decay + x.float() @ self.w_in.T
+                cache.state[slots] = s
+                h += s @ self.w_out.T
+                return
             for seg in batch.segments:                      # a request's tokens in order
                 rows = slice(seg.offset, seg.offset + seg.n_tokens)
                 u = x[rows].float() @ self.w_in.T
@@ -256,7 +267,7 @@ def test_a_toy_mixer_with_state_is_registered_built_and_stepped():
     register_architecture("ToyStateForTests")(ToyConfig)
     cfg = config_from_dict({"architectures": ["ToyStateForTests"], "hidden": 48, "vocab": 97})
     model = Model.from_config(cfg, dtype="float32", device=DEV).init_random(seed=5, std=0.15)
-    assert not model.graph_safe()
+    assert model.graph_safe()
     specs = model.cache_specs()
     assert specs[0][0] is None and specs[0][1].shape == (48,) and specs[1][1] is None
 
@@ -284,17 +295,17 @@ def test_a_toy_mixer_with_state_is_registered_built_and_stepped():
             h = h + (plain.silu(gu[:, :f]) * gu[:, f:]) @ blk.ffn.w_down.float().T
         return (plain.rms_norm(h, model.final_norm.weight, 1e-5) @ model.embed_table.float().T).cpu()
 
-    a, b = H.random_tokens(97, 40, 1), H.random_tokens(97, 33, 2)
+    a, b = H.random_tokens(97, 45, 1), H.random_tokens(97, 38, 2)
     ref_a, ref_b = plain_toy(a), plain_toy(b)
     eng = Engine(model, cache_tokens=192, page_size=16, max_requests=3)
-    assert not eng.cuda_graphs
+    assert eng.cuda_graphs                                  # state slots and captured decode steps go together
     scale = float(ref_a.abs().max())
-    whole = eng.step([("a", a, list(range(40)))]).cpu()
+    whole = eng.step([("a", a, list(range(45)))]).cpu()
     eng.finish("a")
     assert float((whole - ref_a).abs().max()) / scale < 2e-5
     # mixed: a in portions and single tokens beside b; a reuses the slot a just gave back
     got_a, got_b, ia, ib = [], [], 0, 0
-    plan = [(7, 5), (2, 1), (1, 9), (12, 1), (1, 1), (1, 0), (9, 2), (1, 14), (6, 0)]
+    plan = [(7, 5), (2, 1), (1, 9), (12, 1), (1, 1), (1, 1), (1, 1), (1, 1), (1, 1), (1, 1), (1, 0), (9, 2), (1, 14), (6, 0)]
     for na, nb in plan:
         entries = []
         if na:
@@ -304,7 +315,7 @@ def test_a_toy_mixer_with_state_is_registered_built_and_stepped():
         out = eng.step(entries).cpu()
         got_a.append(out[:na]); got_b.append(out[na:na + nb])
         ia, ib = ia + na, ib + nb
-    assert ia == 40 and ib == 33
+    assert ia == 45 and ib == 38 and eng.graph_replays >= 4   # the steps of one token each came from a CUDA graph
     assert float((torch.cat(got_a) - ref_a).abs().max()) / scale < 2e-5
     assert float((torch.cat(got_b) - ref_b).abs().max()) / scale < 2e-5
     eng.finish("a"); eng.finish("b")
