@@ -141,7 +141,8 @@ class CudaKernels(KernelSet):
         # the TMA weight-streaming kernel for decode products
         self.use_stream = True
         self.stream_split_k = 0                # a fixed k per work item (0: splits chosen per product, see _stream_splits)
-        self.stream_item_cost = 4.0            # fixed cost of a work item, in k blocks
+        # fixed cost of a work item, in k blocks; 8 against 4: eight tokens 6.74 against 6.84 ms, one and 64 tokens alike
+        self.stream_item_cost = 8.0
         # (shared memory per block, resident blocks) for up to 3 tokens and for more: measured in the decode step at
         # Scout shapes, one token 2.90 ms with (110 KiB, 2 per multiprocessor) against 3.01 with (74 KiB, 3), eight
         # tokens 7.10 against 7.02, sixty-four alike; one block per multiprocessor with 110 or 200 KiB: 3.2 and 3.1 ms
