@@ -420,7 +420,8 @@ def run_ours(args):
     if not args.skip_points:
         for nb in (1, 64):
             pc = ClockSampler()
-            ms_b, _, _ = timed_decode(nb, max(4, args.steps // 2), 3, pc)
+            # long enough for the clock sampler to see it: a step of one token takes a few milliseconds
+            ms_b, _, _ = timed_decode(nb, max(4, args.steps * 4 if nb == 1 else args.steps // 2), 3, pc)
             gbs = step_bytes(nb) / (ms_b * 1e-3) / 1e9
             # each point with its own step time, fraction of the HBM roofline and clocks (flat: the record keeps one level)
             points.update({f"decode_b{nb}": round(nb * 1000.0 / ms_b, 1), f"decode_b{nb}_ms": round(ms_b, 4),
