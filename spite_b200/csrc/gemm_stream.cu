@@ -10,10 +10,17 @@
 // tokens as the 8 columns), so no sums cross warps.  Registers stay few, and two blocks (of this
 // kernel, or the last of this and the first of the next) share a multiprocessor.
 //
-// Work items are (group with tokens, tile of 128 weight rows, k split); blocks are persistent and
-// take items with a stride of the grid, the ring running on across items.  With k splits the
-// partial tiles go through a float32 scratch in global memory; the block that arrives last at the
-// tile's ticket adds them in the order of the splits, so a sum's order does not depend on timing.
+// Work items are (group with tokens, tile of weight rows, k split); blocks are persistent and
+// take items with a stride of the grid, the ring running on across items.
+//
+// A product with few output rows (an output projection: 5120) has too few tiles of 128 rows for
+// the resident blocks.  Two ways to more items, both chosen by the caller.  k slices inside the block
+// (S = 2, 4, 8): a stage holds S boxes of 128/S rows x 64 k, S k blocks side by side, and the warps
+// are 8/S row groups x S slices; a tile has 128/S rows and the slices' sums meet in shared memory
+// when the item ends, in the order of the slices: no traffic, no waiting for another block.  And k
+// splits across blocks: the partial tiles go through a float32 scratch in global memory, and the block
+// that arrives last at the tile's ticket adds them in the order of the splits (a fence, an atomic and
+// a second pass: about 2.7 us an item).  Either way a sum's order does not depend on timing.
 // A one-group product knows its items without the step's earlier kernels: its producer requests the
 // first weights before griddepcontrol.wait.
 // (Dealing every block one equal run of k blocks across tile borders was measured too: faster alone,
@@ -25,8 +32,8 @@
 namespace {
 using namespace tc;
 
-constexpr int ROWS = 128, BK = 64;
-constexpr int W_BYTES = ROWS * BK * 2;                  // 16 KiB
+constexpr int ROWS = 128, BK = 64;                      // weight rows and k of a stage's boxes together: 128 x 64 elements
+constexpr int W_BYTES = ROWS * BK * 2;                  // 16 KiB a stage, however it is cut
 constexpr int CONSUMERS = 8;                            // warps; warp CONSUMERS is the producer
 constexpr int THREADS = (CONSUMERS + 1) * 32;
 constexpr int MAX_STAGES = 12;
@@ -43,6 +50,9 @@ struct Tail {
     int abort_flag, n_active, last;
     int active[MAX_GROUPS];
 };
+// After the tail, with k slices: the sums of the warps of slices 1 .. S - 1 on their way to the warps of slice 0,
+// [warp - R][lane][NT / 2] floats.
+constexpr int slices_bytes(int nt, int s) { return s > 1 ? (CONSUMERS - CONSUMERS / s) * 32 * (nt / 2) * 4 : 0; }
 
 __device__ __forceinline__ void mma16816(float (&d)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
@@ -68,28 +78,32 @@ __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;\
 struct Item {
     int group, lo, m;             // group, its first row in the sorted order, its tokens
     int tile, n0;                 // tile id (group slot x row tiles + row tile) and first output column
-    int split, kb0, kb1;          // k split and its range of 64-wide k blocks
+    int split, kb0, kb1;          // k split and its range of stages (64 S wide each)
 };
 
-// NT: token columns (8 or 16).  `n_splits` k splits per tile; `scratch` holds tiles x n_splits x NT x 128
-// floats, `tickets` one zeroed int per tile (left zeroed).
-template <int NT, int EPI>
+// NT: token columns (8 or 16).  S: k slices inside the block.  `n_splits` k splits per tile; `scratch` holds
+// tiles x n_splits x NT x (128 / S) floats, `tickets` one zeroed int per tile (left zeroed).
+template <int NT, int EPI, int S>
 __global__ void __launch_bounds__(THREADS, 3)
 gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const GemmParams p, const int n_stages,
                    const int n_splits, float* __restrict__ scratch, int* __restrict__ tickets, const WaitControl waits) {
     constexpr bool DUAL = (EPI == EPI_SWIGLU);
-    constexpr int COLS = DUAL ? ROWS / 2 : ROWS;                 // output columns of a tile
-    constexpr int X_BYTES = NT * BK * 2;                         // 1 or 2 KiB
-    constexpr int STAGE = W_BYTES + (X_BYTES < 1024 ? 1024 : X_BYTES);
+    constexpr int TR = ROWS / S;                                 // weight rows of a tile
+    constexpr int R = CONSUMERS / S;                             // row groups of 16 (SwiGLU: 8 gate + 8 up) rows
+    constexpr int COLS = DUAL ? TR / 2 : TR;                     // output columns of a tile
+    constexpr int BOX_BYTES = TR * BK * 2;                       // one slice's weights
+    constexpr int X_BYTES = NT * BK * 2;                         // one slice's tokens: 1 or 2 KiB
+    constexpr int STAGE = W_BYTES + (S * X_BYTES < 1024 ? 1024 : S * X_BYTES);
     constexpr int NB = NT / 8;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     Tail* tail = (Tail*)(smem + (size_t)n_stages * STAGE);
+    float* const slice_sums = (float*)(tail + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const bool grouped = p.group_offsets != nullptr;
     const int row_tiles = (p.N + COLS - 1) / COLS;
-    const int num_kb = p.K / BK;
+    const int num_kb = p.K / (BK * S);                        // stages along k
     const int w_rows = DUAL ? 2 * p.N : p.N;
     volatile int* abort_flag = &tail->abort_flag;
     int* const err_word = waits.error_word ? waits.error_word : &g_stream_error;
@@ -114,11 +128,15 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const GemmParams p
             for (int j = 0; j < pre; ++j) {
                 const unsigned bar = smem_u32(&tail->full[j]), dst = smem_u32(smem + j * STAGE);
                 mbar_expect_tx(bar, W_BYTES);
-                if (DUAL) {
-                    tma_load_2d_hint(dst, &map_w, (kb0 + j) * BK, rt * COLS, bar, w_policy);
-                    tma_load_2d_hint(dst + W_BYTES / 2, &map_w, (kb0 + j) * BK, p.N + rt * COLS, bar, w_policy);
-                } else {
-                    tma_load_2d_hint(dst, &map_w, (kb0 + j) * BK, rt * COLS, bar, w_policy);
+#pragma unroll
+                for (int sl = 0; sl < S; ++sl) {
+                    const int kx = ((kb0 + j) * S + sl) * BK;
+                    if (DUAL) {
+                        tma_load_2d_hint(dst + sl * BOX_BYTES, &map_w, kx, rt * COLS, bar, w_policy);
+                        tma_load_2d_hint(dst + sl * BOX_BYTES + BOX_BYTES / 2, &map_w, kx, p.N + rt * COLS, bar, w_policy);
+                    } else {
+                        tma_load_2d_hint(dst + sl * BOX_BYTES, &map_w, kx, rt * COLS, bar, w_policy);
+                    }
                 }
             }
         }
@@ -165,7 +183,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const GemmParams p
         const __nv_bfloat16* X = (const __nv_bfloat16*)p.A;
         for (int i = blockIdx.x; i < total && ok; i += gridDim.x) {
             const Item it = item_at(i);
-            // this lane's 16-byte chunks of the token tile: chunk q = lane + 32 j, token q / 8, k chunk q % 8
+            // this lane's 16-byte chunks of a slice's token tile: chunk q = lane + 32 j, token q / 8, k chunk q % 8
             const __nv_bfloat16* src[NT / 4];
             unsigned off[NT / 4];
 #pragma unroll
@@ -185,26 +203,34 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const GemmParams p
                     --skip_tma;
                 } else if (lane == 0) {
                     mbar_expect_tx(bar, W_BYTES);
-                    if (DUAL) {
-                        tma_load_2d_hint(dst, &map_w, kb * BK, wy, bar, w_policy);
-                        tma_load_2d_hint(dst + W_BYTES / 2, &map_w, kb * BK, wy + p.N, bar, w_policy);
-                    } else {
-                        tma_load_2d_hint(dst, &map_w, kb * BK, wy, bar, w_policy);
+#pragma unroll
+                    for (int sl = 0; sl < S; ++sl) {
+                        const int kx = (kb * S + sl) * BK;
+                        if (DUAL) {
+                            tma_load_2d_hint(dst + sl * BOX_BYTES, &map_w, kx, wy, bar, w_policy);
+                            tma_load_2d_hint(dst + sl * BOX_BYTES + BOX_BYTES / 2, &map_w, kx, wy + p.N, bar, w_policy);
+                        } else {
+                            tma_load_2d_hint(dst + sl * BOX_BYTES, &map_w, kx, wy, bar, w_policy);
+                        }
                     }
                 }
 #pragma unroll
-                for (int j = 0; j < NT / 4; ++j) cp_async16(dst + off[j], src[j] + (size_t)kb * BK);
+                for (int sl = 0; sl < S; ++sl)
+#pragma unroll
+                    for (int j = 0; j < NT / 4; ++j)
+                        cp_async16(dst + sl * X_BYTES + off[j], src[j] + ((size_t)kb * S + sl) * BK);
                 cp_async_arrive(bar);
             }
         }
         asm volatile("cp.async.wait_all;\n" ::: "memory");
     } else {
-        // ---- consumers: warp w owns rows 16 w .. 16 w + 15 of the tile (SwiGLU: gate rows 8 w .. + 7 and
-        //      the up rows of the same output columns as fragment rows 8 .. 15)
+        // ---- consumers: warp w works on slice w / R; it owns rows 16 r .. 16 r + 15 (r = w % R) of the tile
+        //      (SwiGLU: gate rows 8 r .. + 7 and the up rows of the same output columns as fragment rows 8 .. 15)
         const int g = lane >> 2, c = lane & 3;
+        const int rg = warp % R, slice = warp / R;
         const int mrow = (lane & 7) + ((lane >> 3) & 1) * 8;     // fragment row this lane addresses for ldmatrix
-        const int arow = DUAL ? (mrow < 8 ? 8 * warp + mrow : ROWS / 2 + 8 * warp + mrow - 8) : 16 * warp + mrow;
-        const unsigned a_off = arow * 128, a_swz = arow & 7, a_k = lane >> 4;
+        const int arow = DUAL ? (mrow < 8 ? 8 * rg + mrow : TR / 2 + 8 * rg + mrow - 8) : 16 * rg + mrow;
+        const unsigned a_off = slice * BOX_BYTES + arow * 128, a_swz = arow & 7, a_k = lane >> 4;
         const int brow = lane & 7;
         const unsigned b_k = (lane >> 3) & 1;
         int s = 0;
@@ -220,7 +246,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const GemmParams p
             for (int kb = it.kb0; kb < it.kb1; ++kb, s = (s + 1 == n_stages ? 0 : s + 1), ph ^= (s == 0)) {
                 ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&tail->full[s]), ph, abort_flag, err_word, 2, wait_limit));
                 if (!ok) break;
-                const unsigned wbase = smem_u32(smem + s * STAGE), xbase = wbase + W_BYTES;
+                const unsigned wbase = smem_u32(smem + s * STAGE), xbase = wbase + W_BYTES + slice * X_BYTES;
 #pragma unroll
                 for (int ks = 0; ks < BK / 16; ++ks) {
                     unsigned a[4];
@@ -238,7 +264,29 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const GemmParams p
             }
             // A warp whose wait ran out leaves at once only if the epilogue has no block-wide steps; else it
             // goes through this item's barriers with the others (storing nothing) and all leave together.
-            if (!ok && n_splits == 1) break;
+            if (!ok && n_splits == 1 && S == 1) break;
+
+            // ---- the k slices' sums meet in the warps of slice 0, in the order of the slices
+            if (S > 1) {
+                consumer_sync();                              // the sums of the item before have been read
+                if (slice > 0) {
+#pragma unroll
+                    for (int j = 0; j < NB; ++j)
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) slice_sums[((warp - R) * 32 + lane) * (4 * NB) + 4 * j + e] = acc[j][e];
+                }
+                consumer_sync();
+                if (slice == 0) {
+#pragma unroll
+                    for (int sl = 1; sl < S; ++sl)
+#pragma unroll
+                        for (int j = 0; j < NB; ++j)
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) acc[j][e] += slice_sums[(((sl - 1) * R + rg) * 32 + lane) * (4 * NB) + 4 * j + e];
+                }
+                if (n_splits == 1 && *abort_flag) break;      // the same answer in every warp, after the barrier
+            }
+            const bool writer = slice == 0;
 
             // ---- epilogue.  This lane holds, for token 8 j + 2 c + (e & 1), fragment rows g (e < 2) and g + 8.
             auto finish = [&](int t, int col, float v, float v2) {      // output column n0 + col of token t
@@ -255,34 +303,38 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const GemmParams p
                 else ((__nv_bfloat16*)p.C)[o] = __float2bfloat16_rn(silu_f32(v * sc) * (v2 * sc));
             };
             if (n_splits == 1) {
+                if (writer) {
+#pragma unroll
+                    for (int j = 0; j < NB; ++j)
+#pragma unroll
+                        for (int e = 0; e < 2; ++e) {
+                            const int t = 8 * j + 2 * c + e;
+                            if (DUAL) {
+                                finish(t, 8 * rg + g, acc[j][e], acc[j][e + 2]);
+                            } else {
+                                finish(t, 16 * rg + g, acc[j][e], 0.f);
+                                finish(t, 16 * rg + g + 8, acc[j][e + 2], 0.f);
+                            }
+                        }
+                }
+                continue;
+            }
+            // partial tile: scratch[tile][split][token][tile row]; tile rows of the SwiGLU form: gate rows, then up rows
+            float* part = scratch + ((size_t)it.tile * n_splits + it.split) * NT * TR;
+            const int r_lo = DUAL ? 8 * rg + g : 16 * rg + g;
+            const int r_hi = DUAL ? TR / 2 + 8 * rg + g : 16 * rg + g + 8;
+            if (writer) {
 #pragma unroll
                 for (int j = 0; j < NB; ++j)
 #pragma unroll
                     for (int e = 0; e < 2; ++e) {
                         const int t = 8 * j + 2 * c + e;
-                        if (DUAL) {
-                            finish(t, 8 * warp + g, acc[j][e], acc[j][e + 2]);
-                        } else {
-                            finish(t, 16 * warp + g, acc[j][e], 0.f);
-                            finish(t, 16 * warp + g + 8, acc[j][e + 2], 0.f);
+                        if (t < it.m && ok) {
+                            __stcg(part + t * TR + r_lo, acc[j][e]);
+                            __stcg(part + t * TR + r_hi, acc[j][e + 2]);
                         }
                     }
-                continue;
             }
-            // partial tile: scratch[tile][split][token][tile row]; tile rows of the SwiGLU form: 0..63 gate, 64..127 up
-            float* part = scratch + ((size_t)it.tile * n_splits + it.split) * NT * ROWS;
-            const int r_lo = DUAL ? 8 * warp + g : 16 * warp + g;
-            const int r_hi = DUAL ? ROWS / 2 + 8 * warp + g : 16 * warp + g + 8;
-#pragma unroll
-            for (int j = 0; j < NB; ++j)
-#pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                    const int t = 8 * j + 2 * c + e;
-                    if (t < it.m && ok) {
-                        __stcg(part + t * ROWS + r_lo, acc[j][e]);
-                        __stcg(part + t * ROWS + r_hi, acc[j][e + 2]);
-                    }
-                }
             __threadfence();
             consumer_sync();
             if (threadIdx.x == 0) {
@@ -293,13 +345,13 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const GemmParams p
             consumer_sync();
             if (tail->last) {
                 __threadfence();
-                const float* all = scratch + (size_t)it.tile * n_splits * NT * ROWS;
+                const float* all = scratch + (size_t)it.tile * n_splits * NT * TR;
                 for (int idx = threadIdx.x; idx < COLS * it.m; idx += CONSUMERS * 32) {
                     const int col = idx % COLS, t = idx / COLS;
                     float v = 0.f, v2 = 0.f;
                     for (int sp = 0; sp < n_splits; ++sp) {
-                        v += __ldcg(all + ((size_t)sp * NT + t) * ROWS + col);
-                        if (DUAL) v2 += __ldcg(all + ((size_t)sp * NT + t) * ROWS + ROWS / 2 + col);
+                        v += __ldcg(all + ((size_t)sp * NT + t) * TR + col);
+                        if (DUAL) v2 += __ldcg(all + ((size_t)sp * NT + t) * TR + TR / 2 + col);
                     }
                     finish(t, col, v, v2);
                 }
@@ -311,67 +363,89 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const GemmParams p
     }
 }
 
-template <int NT, int EPI>
+template <int NT, int EPI, int S>
 int launch(const GemmParams& p, int n_blocks, int smem_budget, int n_splits, float* scratch, int* tickets, cudaStream_t st) {
     constexpr bool DUAL = (EPI == EPI_SWIGLU);
+    constexpr int TR = ROWS / S;
     constexpr int X_BYTES = NT * BK * 2;
-    constexpr int STAGE = W_BYTES + (X_BYTES < 1024 ? 1024 : X_BYTES);
+    constexpr int STAGE = W_BYTES + (S * X_BYTES < 1024 ? 1024 : S * X_BYTES);
     const long long w_rows = (long long)(DUAL ? 2 : 1) * p.N * p.n_groups;
     CUtensorMap mw;
     cuuint64_t dims[2] = {(cuuint64_t)p.K, (cuuint64_t)w_rows};
     cuuint64_t strides[1] = {(cuuint64_t)p.K * 2};
-    cuuint32_t box[2] = {BK, (cuuint32_t)(DUAL ? ROWS / 2 : ROWS)};
+    cuuint32_t box[2] = {BK, (cuuint32_t)(DUAL ? TR / 2 : TR)};
     if (!make_map(&mw, p.W, 2, dims, strides, box)) return SPITE_LAUNCH_FAILED;
-    int n_stages = (smem_budget - (int)sizeof(Tail) - 1024) / STAGE;
+    constexpr int FIXED = (int)sizeof(Tail) + slices_bytes(NT, S) + 1024;
+    int n_stages = (smem_budget - FIXED) / STAGE;
     if (n_stages > MAX_STAGES) n_stages = MAX_STAGES;
-    if (n_stages < 2) return SPITE_BAD_ARG;
-    const size_t smem = (size_t)n_stages * STAGE + sizeof(Tail) + 1024;
-    auto k = gemm_stream_kernel<NT, EPI>;
+    if (n_stages < 2) return SPITE_UNSUPPORTED;                    // (16 tokens x 8 slices are 32 KiB a stage)
+    const size_t smem = (size_t)n_stages * STAGE + FIXED;
+    auto k = gemm_stream_kernel<NT, EPI, S>;
     if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||
         cudaFuncSetAttribute(k, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared) != cudaSuccess)
         return SPITE_LAUNCH_FAILED;
-    const int cols = DUAL ? ROWS / 2 : ROWS;
+    const int cols = DUAL ? TR / 2 : TR;
     const long long tiles = (long long)((p.N + cols - 1) / cols) * (p.group_offsets ? (p.n_groups < p.M ? p.n_groups : p.M) : 1) * n_splits;
     const int grid = (int)(tiles < n_blocks ? tiles : n_blocks);
     SPITE_LAUNCH(k, grid, THREADS, smem, st, mw, p, n_stages, n_splits, scratch, tickets, s_waits);
     return spite_launch_status();
 }
 
+template <int NT, int EPI>
+int launch_slices(int k_slices, const GemmParams& p, int n_blocks, int smem_budget, int n_splits, float* scratch, int* tickets,
+                  cudaStream_t st) {
+    switch (k_slices) {
+        case 1: return launch<NT, EPI, 1>(p, n_blocks, smem_budget, n_splits, scratch, tickets, st);
+        case 2: return launch<NT, EPI, 2>(p, n_blocks, smem_budget, n_splits, scratch, tickets, st);
+        case 4: return launch<NT, EPI, 4>(p, n_blocks, smem_budget, n_splits, scratch, tickets, st);
+        case 8: return EPI == EPI_SWIGLU ? SPITE_UNSUPPORTED       // (tiles of 8 gate and 8 up rows: nobody needs them)
+                                         : launch<NT, EPI == EPI_SWIGLU ? EPI_STORE : EPI, 8>(p, n_blocks, smem_budget, n_splits, scratch, tickets, st);
+        default: return SPITE_BAD_ARG;
+    }
+}
+
 }  // namespace
 
-// `max_rows_per_group` <= 16.  `n_blocks`: resident blocks (two per multiprocessor fit when `smem_budget`,
-// the bytes of shared memory a block may take, is at most about 110 KiB, three at 74 KiB).  `n_splits`: k splits per tile
-// (1: no scratch needed).  `scratch`: groups-with-tokens x row tiles x n_splits x 16 x 128 floats;
-// `tickets`: that many tiles' ints, zero before the first call; calls that share them must not overlap.
-SPITE_API int spite_gemm_stream(const GemmParams* p, int max_rows_per_group, int n_blocks, int smem_budget, int n_splits,
-                                float* scratch, long long scratch_floats, int* tickets, int n_tickets, void* stream) {
+// `max_rows_per_group` <= 16.  `k_slices` (1, 2, 4 or 8; 8 not with SwiGLU): a tile has 128 / k_slices weight rows
+// (SwiGLU: half of them gate, half up) and K must be a multiple of 64 k_slices.  `n_blocks`: resident blocks
+// (two per multiprocessor fit when `smem_budget`, the bytes of shared memory a block may take, is at most about
+// 110 KiB, three at 74 KiB).  `n_splits`: k splits per tile across blocks (1: no scratch needed).  `scratch`:
+// groups-with-tokens x row tiles x n_splits x 16 x (128 / k_slices) floats; `tickets`: that many tiles' ints,
+// zero before the first call; calls that share them must not overlap.
+SPITE_API int spite_gemm_stream(const GemmParams* p, int max_rows_per_group, int k_slices, int n_blocks, int smem_budget,
+                                int n_splits, float* scratch, long long scratch_floats, int* tickets, int n_tickets,
+                                void* stream) {
     if (!p || !p->A || !p->W || !p->C) return SPITE_BAD_ARG;
     if (p->M < 0 || p->N <= 0 || p->K <= 0 || p->lda < p->K || p->ldc < p->N || n_blocks < 1 || n_splits < 1) return SPITE_BAD_ARG;
     if (p->group_offsets ? p->n_groups < 1 : p->n_groups != 1) return SPITE_BAD_ARG;
     if (p->epilogue < 0 || p->epilogue > EPI_SWIGLU) return SPITE_BAD_ARG;
-    if (p->K % BK || p->lda % 8 || (((uintptr_t)p->A | (uintptr_t)p->W) & 15)) return SPITE_UNSUPPORTED;
+    if (k_slices != 1 && k_slices != 2 && k_slices != 4 && k_slices != 8) return SPITE_BAD_ARG;
+    if (p->K % (BK * k_slices) || p->lda % 8 || (((uintptr_t)p->A | (uintptr_t)p->W) & 15)) return SPITE_UNSUPPORTED;
+    if (k_slices == 8 && p->epilogue == EPI_SWIGLU) return SPITE_UNSUPPORTED;
     if (max_rows_per_group < 1 || max_rows_per_group > 16 || p->n_groups > MAX_GROUPS) return SPITE_UNSUPPORTED;
     if (p->n_groups > 1 && p->w_group_stride != (long long)(p->epilogue == EPI_SWIGLU ? 2 : 1) * p->N * p->K)
         return SPITE_UNSUPPORTED;                              // groups must be stacked without gaps
     if (p->M == 0) return SPITE_OK;
-    if (n_splits > p->K / BK) n_splits = p->K / BK;
+    const int stages_k = p->K / (BK * k_slices);
+    if (n_splits > stages_k) n_splits = stages_k;
     const int nt = max_rows_per_group <= 8 ? 8 : 16;
-    const int cols = p->epilogue == EPI_SWIGLU ? ROWS / 2 : ROWS;
+    const int tr = ROWS / k_slices;
+    const int cols = p->epilogue == EPI_SWIGLU ? tr / 2 : tr;
     const long long tiles = (long long)((p->N + cols - 1) / cols) * (p->group_offsets ? (p->n_groups < p->M ? p->n_groups : p->M) : 1);
     if (n_splits > 1) {
-        if (!scratch || !tickets || tiles > n_tickets || tiles * n_splits * nt * ROWS > scratch_floats) return SPITE_BAD_ARG;
+        if (!scratch || !tickets || tiles > n_tickets || tiles * n_splits * nt * tr > scratch_floats) return SPITE_BAD_ARG;
     }
     cudaStream_t st = (cudaStream_t)stream;
-#define SPITE_STREAM_CASE(E)                                                                                     \
-    case E:                                                                                                      \
-        return nt == 8 ? launch<8, E>(*p, n_blocks, smem_budget, n_splits, scratch, tickets, st)                  \
-                       : launch<16, E>(*p, n_blocks, smem_budget, n_splits, scratch, tickets, st);
+#define SPITE_STREAM_CASE(E)                                                                                              \
+    case E:                                                                                                               \
+        return nt == 8 ? launch_slices<8, E>(k_slices, *p, n_blocks, smem_budget, n_splits, scratch, tickets, st)          \
+                       : launch_slices<16, E>(k_slices, *p, n_blocks, smem_budget, n_splits, scratch, tickets, st);
     switch (p->epilogue) {
         SPITE_STREAM_CASE(EPI_STORE)
         SPITE_STREAM_CASE(EPI_STORE_F32)
         SPITE_STREAM_CASE(EPI_ADD_F32)
-        default: return nt == 8 ? launch<8, EPI_SWIGLU>(*p, n_blocks, smem_budget, n_splits, scratch, tickets, st)
-                                : launch<16, EPI_SWIGLU>(*p, n_blocks, smem_budget, n_splits, scratch, tickets, st);
+        default: return nt == 8 ? launch_slices<8, EPI_SWIGLU>(k_slices, *p, n_blocks, smem_budget, n_splits, scratch, tickets, st)
+                                : launch_slices<16, EPI_SWIGLU>(k_slices, *p, n_blocks, smem_budget, n_splits, scratch, tickets, st);
     }
 #undef SPITE_STREAM_CASE
 }

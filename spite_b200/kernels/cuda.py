@@ -140,9 +140,15 @@ class CudaKernels(KernelSet):
         self.tc_experts_down_min_groups = 64
         # the TMA weight-streaming kernel for decode products
         self.use_stream = True
-        self.stream_split_k = 0                # a fixed k per work item (0: splits chosen per product, see _stream_splits)
-        # fixed cost of a work item, in k blocks; 8 against 4: eight tokens 6.74 against 6.84 ms, one and 64 tokens alike
-        self.stream_item_cost = 8.0
+        # what a work item costs besides its stages, in stages of 16 KiB: any item; one whose sums cross blocks (a
+        # fence, a ticket, a second pass: about 2.7 us) and every k split of it; one whose k slices meet in shared memory
+        self.stream_item_cost = 2.0
+        self.stream_split_item_cost = 6.0
+        self.stream_split_cost = 1.5
+        self.stream_slice_cost = 1.0
+        self.stream_max_slices = 8             # 1: tiles of 128 rows only
+        self.stream_slices_min_rows = 4        # products of fewer rows keep tiles of 128 rows (see _stream_cut)
+        self.stream_force = None               # (k slices, k splits) for every call, for measurements
         # (shared memory per block, resident blocks) for up to 3 tokens and for more: measured in the decode step at
         # Scout shapes, one token 2.90 ms with (110 KiB, 2 per multiprocessor) against 3.01 with (74 KiB, 3), eight
         # tokens 7.10 against 7.02, sixty-four alike; one block per multiprocessor with 110 or 200 KiB: 3.2 and 3.1 ms
@@ -329,18 +335,21 @@ class CudaKernels(KernelSet):
         return False
 
     def _gemm_stream(self, p, max_rows_per_group, grouped):
-        """The TMA weight-streaming kernel for decode steps: picks the k splits so that the work items
-        are many enough to spread evenly, and lends the scratch for their partial sums."""
+        """The TMA weight-streaming kernel for decode steps: picks the tile height (k slices inside the block)
+        and the k splits across blocks so that the work items are many enough to spread evenly, and lends the
+        scratch for the partial sums of the splits."""
         swiglu = p.epilogue == EPI_SWIGLU
-        cols = 64 if swiglu else 128
-        tiles = -(-p.N // cols) * (min(p.n_groups, p.M) if grouped else 1)
+        groups = min(p.n_groups, p.M) if grouped else 1
         smem, blocks = self.stream_shape[p.M > 3]
-        splits = self._stream_splits(tiles, p.K // 64, blocks)
+        nt = 8 if max_rows_per_group <= 8 else 16
+        slices, splits = self.stream_force or self._stream_cut(p.M, p.N, p.K, groups, swiglu, blocks, smem, nt)
+        rows = 128 // slices
+        tiles = -(-p.N // (rows // 2 if swiglu else rows)) * groups
         scratch, n_floats = None, 0
         if splits > 1:
             if tiles > self._tickets_n:
                 return -2
-            n_floats = tiles * splits * (8 if max_rows_per_group <= 8 else 16) * 128
+            n_floats = tiles * splits * nt * rows
             scratch = torch.empty(n_floats, dtype=torch.float32, device=self.device)
         # the k splits' arrival counters: one set per stream, since calls that share a set must not overlap
         stream = torch.cuda.current_stream().cuda_stream
@@ -348,26 +357,48 @@ class CudaKernels(KernelSet):
         if tickets is None and splits > 1:
             tickets = self._tickets[stream] = torch.zeros(self._tickets_n, dtype=torch.int32, device=self.device)
         return self._lib("gemm_stream").spite_gemm_stream(
-            C.byref(p), max_rows_per_group, blocks, smem, splits, C.c_void_p(_ptr(scratch)),
+            C.byref(p), max_rows_per_group, slices, blocks, smem, splits, C.c_void_p(_ptr(scratch)),
             C.c_longlong(n_floats), C.c_void_p(_ptr(tickets)), self._tickets_n, C.c_void_p(stream))
 
-    def _stream_splits(self, tiles: int, k_blocks: int, slots: int) -> int:
-        """k splits of the weight-streaming kernel.  A product of few row tiles (a dense projection at a few
-        tokens: 40 to 128 tiles for 296 to 444 resident blocks) would leave most multiprocessors without
-        work, and the ones that have some are then bound by what a single one can pull; so the tiles are cut
-        along k until the (tile, split) items fill the resident blocks about once.  The cost of a choice is
-        its rounds of items times (k blocks per item + a fixed cost per item for filling the ring, the
-        partial sums and the ticket); at least four k blocks stay together."""
-        if self.stream_split_k:                                  # a fixed k per item, for measurements
-            return 1 if tiles >= 6 * slots else max(1, min(16, k_blocks * 64 // self.stream_split_k))
-        if tiles >= 4 * slots:
-            return 1
-        best, best_cost = 1, None
-        for s in range(1, max(1, min(32, k_blocks // 4)) + 1):
-            rounds = -(-tiles * s // slots)
-            cost = rounds * (-(-k_blocks // s) + self.stream_item_cost)
-            if best_cost is None or cost < best_cost:
-                best, best_cost = s, cost
+    def _stream_cut(self, M: int, N: int, K: int, groups: int, swiglu: bool, slots: int, smem: int, nt: int):
+        """(k slices inside a block, k splits across blocks) of the weight-streaming kernel.  A product of few
+        tiles of 128 rows (a dense projection at a few tokens: 40 to 128 tiles for 296 to 444 resident blocks)
+        would leave most multiprocessors without work, and the ones that have some are then bound by what a
+        single one can pull; so the items are made smaller until they fill the resident blocks about once:
+        lower tiles with the k blocks of a stage side by side (the sums meet in shared memory), or k splits
+        across blocks (partial sums through global memory, a ticket, a second pass over as many partial tiles
+        as there are splits).  The cost of a choice is its rounds of items times (stages an item + what an
+        item costs besides); at least four stages stay together.
+
+        Measured on B200, us, (slices, splits) forced.  Eight tokens (444 blocks): qkv 7168 x 5120: (1, 5) 19.6,
+        (2, 1) 20.9, (4, 1) 17.3, (8, 1) 21.3, (2, 2) 18.9; output projection 5120 x 5120: (1, 7) 16.5, (4, 1)
+        14.2, (8, 1) 13.0, (4, 2) 13.1; shared down 5120 x 8192: (1, 7) 21.6, (4, 1) 20.8, (8, 1) 18.6; seven
+        experts' gate/up: (1, 1) 220, (1, 2) 199.5, (2, 1) 197.4, (4, 1) 195.5, (8, 1) 260 (stages of eight 2 KiB
+        boxes); their down product: (1, 1) 117.6, (2, 1) 113.5, (4, 1) 107.3, (8, 1) 113.4.  One token (296
+        blocks with rings twice as deep): slices bring nothing, qkv (1, 5) 17.5, (2, 2) 17.0, (4, 1) 19.5;
+        output projection (1, 7) 13.9, (2, 2) 14.1, (4, 1) 17.1; so up to three tokens the tiles stay at 128 rows."""
+        best, best_cost = (1, 1), None
+        for slices in (1, 2, 4, 8):
+            if K % (64 * slices) or (swiglu and slices == 8):
+                continue
+            if slices > 1 and (M <= self.stream_slices_min_rows - 1 or slices > self.stream_max_slices):
+                continue
+            stage_bytes = 16384 + max(1024, slices * nt * 128)
+            if slices > 1 and (smem - 5504 - (8 - 8 // slices) * 64 * nt) // stage_bytes < 2:
+                continue                                          # a ring of one stage
+            rows = 128 // slices
+            tiles = -(-N // (rows // 2 if swiglu else rows)) * groups
+            stages = K // (64 * slices)
+            for s in range(1, max(1, min(32, stages // 4)) + 1):
+                rounds = -(-tiles * s // slots)
+                fixed = self.stream_item_cost + (self.stream_slice_cost if slices > 1 else 0.0)
+                if s > 1:
+                    fixed += self.stream_split_item_cost + self.stream_split_cost * s
+                cost = rounds * (-(-stages // s) + fixed)
+                if best_cost is None or cost < best_cost:
+                    best, best_cost = (slices, s), cost
+                if tiles * s >= 4 * slots:
+                    break
         return best
 
     def attention_tc_error(self) -> int:

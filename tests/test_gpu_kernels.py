@@ -98,6 +98,78 @@ def test_linear(ks, M, N, K):
         assert ks.gemm_tc_error() == 0, "a tensor-core block gave up waiting"
 
 
+@pytest.mark.parametrize("slices,splits", [(1, 1), (1, 3), (2, 1), (2, 2), (4, 1), (4, 2), (8, 1), (8, 2)])
+@pytest.mark.parametrize("M", [1, 7, 13])
+def test_streaming_products_with_k_slices_and_k_splits(slices, splits, M):
+    """The weight-streaming kernel with every way of cutting its work: tiles of 128 / slices rows whose k slices
+    meet in shared memory, and k splits across blocks through the scratch; plain, SwiGLU, added into float32
+    with a row scale, and grouped by expert.  Widths that are no multiple of a tile; the same bits twice."""
+    from spite_b200.kernels.cuda import CudaKernels
+    ks = CudaKernels(torch.bfloat16, DEV)
+    ks.stream_force = (slices, splits)
+    if M > 8 and slices == 8:
+        ks.stream_shape = [ks.stream_shape[0]] * 2            # stages of 16 tokens x 8 slices are 32 KiB: the deeper ring
+    r = ref_set(torch.bfloat16)
+    N, K, F, E = 200, 1024, 104, 5                            # 1024 = 2 stages of 8 slices
+    x, w = rnd((M, K), torch.bfloat16, 4), rnd((N, K), torch.bfloat16, 5, 0.2)
+    before = ks.launches_by_library["gemm_stream"]
+    outs = []
+    for _ in range(2):
+        out = torch.full((M, N), 7.0, dtype=torch.bfloat16, device=DEV)
+        ks.linear(x.to(DEV), w.to(DEV), out)
+        outs.append(out)
+    assert torch.equal(outs[0], outs[1])
+    ref = torch.empty((M, N), dtype=torch.float64)
+    r.linear(x, w, ref)
+    close(outs[0], ref, TOL[torch.bfloat16], "linear")
+    h, scale = rnd((M, N), torch.float32, 6), rnd((M,), torch.float32, 7)
+    hd = h.to(DEV).clone()
+    ks.linear(x.to(DEV), w.to(DEV), hd, accumulate=True, row_scale=scale.to(DEV))
+    ref_h = h.double().clone()
+    r.linear(x, w, ref_h, accumulate=True, row_scale=scale)
+    close(hd, ref_h, 2e-5, "linear accumulate")
+    logits = torch.empty((M, N), dtype=torch.float32, device=DEV)
+    ks.linear(x.to(DEV), w.to(DEV), logits)
+    close(logits, ref, 1e-5 * K, "linear f32 out")
+    launches = 4
+    if slices < 8:                                            # SwiGLU tiles of 8 gate and 8 up rows are not built
+        wg = rnd((2 * F, K), torch.bfloat16, 9, 0.3)
+        a = torch.empty((M, F), dtype=torch.bfloat16, device=DEV)
+        ks.linear_swiglu(x.to(DEV), wg.to(DEV), a, row_scale=(scale.abs() + 0.5).to(DEV))
+        a_ref = torch.empty((M, F), dtype=torch.float64)
+        r.linear_swiglu(x, wg, a_ref, row_scale=scale.abs() + 0.5)
+        close(a, a_ref, TOL[torch.bfloat16], "linear_swiglu")
+        launches += 1
+    # grouped: expert 1 stays empty
+    g = torch.Generator().manual_seed(10 + M)
+    ids = torch.randint(0, E, (M,), generator=g)
+    ids[ids == 1] = 0
+    order = torch.sort(ids, stable=True)
+    rows = order.indices.to(torch.int32)
+    offsets = torch.zeros(E + 1, dtype=torch.int32)
+    offsets[1:] = torch.cumsum(torch.bincount(ids, minlength=E), 0)
+    w_gu, w_d = rnd((E, 2 * F, K), torch.bfloat16, 12, 0.3), rnd((E, K, 128), torch.bfloat16, 13, 0.3)
+    tok_scale = torch.rand(M, generator=g) + 0.5
+    if slices < 8:
+        a = torch.zeros((M, F), dtype=torch.bfloat16, device=DEV)
+        ks.grouped_linear_swiglu(x.to(DEV), w_gu.to(DEV), rows.to(DEV), offsets.to(DEV), tok_scale.to(DEV), a)
+        a_ref = torch.zeros((M, F), dtype=torch.float64)
+        r.grouped_linear_swiglu(x, w_gu, rows, offsets, tok_scale, a_ref)
+        close(a, a_ref, TOL[torch.bfloat16], "grouped_linear_swiglu")
+        launches += 1
+    if 128 % (64 * slices) == 0:                              # the down product's depth here is 128
+        a2 = rnd((M, 128), torch.bfloat16, 15)
+        h2 = rnd((M, K), torch.float32, 14)
+        hd2 = h2.to(DEV).clone()
+        ks.grouped_linear_accumulate(a2.to(DEV), w_d.to(DEV), rows.to(DEV), offsets.to(DEV), hd2)
+        h2_ref = h2.double().clone()
+        r.grouped_linear_accumulate(a2, w_d, rows, offsets, h2_ref)
+        close(hd2, h2_ref, 2e-3, "grouped_linear_accumulate")
+        launches += 1
+    assert ks.launches_by_library["gemm_stream"] == before + launches       # every one of them ran in that kernel
+    assert ks.errors() == {}
+
+
 @pytest.mark.parametrize("M,F,K", [(3, 24, 48), (70, 100, 96), (8, 40, 512), (40, 17, 96), (64, 72, 64), (129, 256, 192), (700, 136, 320), (1100, 1000, 128),
                                    (5, 100, 4096), (16, 72, 6144), (12, 200, 128)])
 def test_linear_swiglu(ks, M, F, K):
