@@ -535,19 +535,27 @@ def test_moe_route(ks, M, d, E, k):
 
 
 # ---------------------------------------------------------------------------- sampling
-def test_argmax_prefers_the_highest_index(ks):
+@pytest.mark.parametrize("V", [1000, 16384, 202048, 50001])
+def test_argmax_prefers_the_highest_index(ks, V):
+    """Rows of 16,384 logits and more are read by a cluster of eight blocks: equal maxima in different blocks'
+    parts, at both ends of the row and of a part, a constant row, a row without a finite value."""
     if ks.dtype != torch.float32:
         pytest.skip("logits are float32 in both sets")
-    V = 1000
-    l = rnd((6, V), torch.float32, 50)
-    l[0, 17] = l[0, 600] = 9.0
+    part = -(-V // 8)
+    l = rnd((9, V), torch.float32, 50)
+    l[0, 17] = l[0, V // 2 + 88] = 9.0
     l[1, V - 1] = 9.0
     l[2, 0] = 9.0
     l[3] = 0.0
+    l[4, part - 1] = l[4, part] = 9.0                     # the last of one block's part and the first of the next
+    l[5, 3 * part] = l[5, 5] = 9.0
+    l[6, 7 * part - 1] = 9.0
+    l[7] = -float("inf")
+    l[8, 2 * part + 1] = 9.0
     got = ks.argmax(l.to(DEV)).cpu()
     ref = ref_set(torch.float32).argmax(l)
     assert got.tolist() == ref.tolist()
-    assert got[0] == 600 and got[1] == V - 1 and got[2] == 0 and got[3] == V - 1
+    assert got.tolist() == [V // 2 + 88, V - 1, 0, V - 1, part, 3 * part, 7 * part - 1, V - 1, 2 * part + 1]
 
 
 @pytest.mark.parametrize("V", [512, 1000, 202048])
