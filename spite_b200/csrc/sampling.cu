@@ -632,6 +632,7 @@ SPITE_API int spite_sample(const SampleParams* p, int rows, void* stream) {
 // who needs this, the size limit, and the rules on sharing and on the first call.
 // ---------------------------------------------------------------------------------
 #include "sampling_noalloc.h"
+#include <atomic>
 
 // Scratch of the no-allocation entry point.  In host code this name is only a handle
 // for cudaGetSymbolAddress; it is never passed to a kernel as if it were a pointer.
@@ -640,22 +641,24 @@ static __device__ __align__(256) float g_sample_noalloc_scratch[SPITE_SAMPLE_NOA
 namespace {
 
 constexpr int NOALLOC_MAX_DEVICES = 64;
-float* g_noalloc_scratch_addr[NOALLOC_MAX_DEVICES] = {};     // device address of the array, per device
+// device address of the array, per device; atomic, since the first calls of two host threads may both look it
+// up (they store the same value)
+std::atomic<float*> g_noalloc_scratch_addr[NOALLOC_MAX_DEVICES] = {};
 
 // The device address of the scratch array on the current device; looked up once per
 // device with that device current.  Returns null if the runtime refuses.
 float* noalloc_scratch_for_current_device() {
     int dev = -1;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= NOALLOC_MAX_DEVICES) return nullptr;
-    if (!g_noalloc_scratch_addr[dev]) {
-        float* ptr = nullptr;
+    float* ptr = g_noalloc_scratch_addr[dev].load(std::memory_order_acquire);
+    if (!ptr) {
         if (cudaGetSymbolAddress((void**)&ptr, g_sample_noalloc_scratch) != cudaSuccess) {
             (void)cudaGetLastError();
             return nullptr;
         }
-        g_noalloc_scratch_addr[dev] = ptr;
+        g_noalloc_scratch_addr[dev].store(ptr, std::memory_order_release);
     }
-    return g_noalloc_scratch_addr[dev];
+    return ptr;
 }
 
 }  // namespace
