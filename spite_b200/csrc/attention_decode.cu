@@ -27,6 +27,8 @@ using namespace tc;
 constexpr int CONSUMERS = 4;
 constexpr int THREADS = (CONSUMERS + 1) * 32;
 constexpr int BN = 64;                                    // keys of a tile
+constexpr int MERGE_CHUNKS = 2;                           // runs of splits whose partial results are added side by side
+constexpr int MERGE_BATCH = 12;                           // loads of a thread that are on their way together
 constexpr int BOX_BYTES = BN * 128;                       // 64 rows of 64 elements
 constexpr int MAX_STAGES = 8;
 
@@ -326,9 +328,9 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const __grid_const
     // ---- The block that brings the last partial result merges them all, in split order.  (Measured and not
     //      kept: merging in two rounds, groups of splits first; a second fence and ticket cost more than the
     //      shorter sums saved: 23.7 against 22.0 us at 37 splits, 22.0 against 17.6 us at 18.)
-    __threadfence();
     consumer_sync();
     if (threadIdx.x == 0) {
+        __threadfence();                                     // after the barrier: it covers what the other threads stored
         int* ticket = x.tickets + (size_t)blockIdx.x * nkv + kvh;
         const int arrived = atomicAdd(ticket, 1);
         tail->last = (arrived == x.n_splits - 1);
@@ -337,21 +339,34 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const __grid_const
     consumer_sync();
     if (!tail->last) return;
     __threadfence();
+    // What the merge costs is the latency of its loads from L2, so they are made few rounds of many: one round
+    // for every split's maximum and sum, then the output elements with the splits cut into MERGE_CHUNKS runs whose
+    // loads are all on their way together.  The order of every sum is fixed: splits in order within a run, the
+    // runs in order.
     const int count = x.n_splits;
-    float* w_s = (float*)smem;                               // [16][count] weights of the splits, then [16] inverse sums
-    float* inv_s = w_s + 16 * count;
+    float* w_s = (float*)smem;                               // [16][count] weights of the splits
+    float* l_sp = w_s + 16 * count;                          // [16][count] their sums
+    float* inv_s = l_sp + 16 * count;                        // [16] inverse of the merged sums
+    float* run_s = inv_s + 16;                               // [16][MERGE_CHUNKS][HD] sums of the runs
+    for (int i = threadIdx.x; i < n_rows * count; i += CONSUMERS * 32) {
+        const int r = i / count, sp = i % count;
+        const float2 ml = __ldcg((const float2*)(part_all + ((size_t)sp * 16 + r) * ROW + HD));
+        w_s[r * count + sp] = ml.x;
+        l_sp[r * count + sp] = ml.y;
+    }
+    consumer_sync();
     for (int r = warp; r < n_rows; r += CONSUMERS) {
         float m = -INFINITY;
-        for (int sp = lane; sp < count; sp += 32) m = fmaxf(m, __ldcg(part_all + ((size_t)sp * 16 + r) * ROW + HD));
+        for (int sp = lane; sp < count; sp += 32) m = fmaxf(m, w_s[r * count + sp]);
         m = warp_max(m);
         float l = 0.f;
         for (int sp0 = 0; sp0 < count; sp0 += 32) {           // sums in split order: lane order within 32, then the next 32
             const int sp = sp0 + lane;
-            float w = 0.f, ls = 0.f;
+            float ls = 0.f;
             if (sp < count) {
-                const float ms = __ldcg(part_all + ((size_t)sp * 16 + r) * ROW + HD);
-                w = ms > -INFINITY ? expf(ms - m) : 0.f;
-                ls = __ldcg(part_all + ((size_t)sp * 16 + r) * ROW + HD + 1) * w;
+                const float ms = w_s[r * count + sp];
+                const float w = ms > -INFINITY ? expf(ms - m) : 0.f;
+                ls = l_sp[r * count + sp] * w;
                 w_s[r * count + sp] = w;
             }
             l += warp_sum(ls);
@@ -359,19 +374,37 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const __grid_const
         if (lane == 0) inv_s[r] = 1.0f / fmaxf(l, 1e-30f);
     }
     consumer_sync();
-    // every thread sums four output elements over the splits, in split order; the loads of eight splits are
-    // on their way together (the sum itself is short, the latency of one block's loads is what costs)
-    for (int e = threadIdx.x; e < n_rows * (HD / 4); e += CONSUMERS * 32) {
-        const int r = e / (HD / 4), d4 = e % (HD / 4);
+    const int per_run = (count + MERGE_CHUNKS - 1) / MERGE_CHUNKS;
+    for (int e = threadIdx.x; e < n_rows * (HD / 4) * MERGE_CHUNKS; e += CONSUMERS * 32) {
+        const int d4 = e % (HD / 4), c = (e / (HD / 4)) % MERGE_CHUNKS, r = e / ((HD / 4) * MERGE_CHUNKS);
         const float4* from = (const float4*)(part_all + (size_t)r * ROW) + d4;
         const float* w = w_s + r * count;
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 8
-        for (int sp = 0; sp < count; ++sp) {
-            const float4 v = __ldcg(from + (size_t)sp * (16 * ROW / 4));
-            const float ws = w[sp];
-            acc.x = fmaf(v.x, ws, acc.x); acc.y = fmaf(v.y, ws, acc.y);
-            acc.z = fmaf(v.z, ws, acc.z); acc.w = fmaf(v.w, ws, acc.w);
+        const int sp_end = min(count, (c + 1) * per_run);
+        for (int sp0 = c * per_run; sp0 < sp_end; sp0 += MERGE_BATCH) {
+            // (a loop of known length with the loads first: a loop whose length the compiler does not know
+            // would wait for every load before it asks for the next)
+            float4 v[MERGE_BATCH];
+#pragma unroll
+            for (int j = 0; j < MERGE_BATCH; ++j)
+                v[j] = sp0 + j < sp_end ? __ldcg(from + (size_t)(sp0 + j) * (16 * ROW / 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int j = 0; j < MERGE_BATCH; ++j) {
+                const float ws = sp0 + j < sp_end ? w[sp0 + j] : 0.f;
+                acc.x = fmaf(v[j].x, ws, acc.x); acc.y = fmaf(v[j].y, ws, acc.y);
+                acc.z = fmaf(v[j].z, ws, acc.z); acc.w = fmaf(v[j].w, ws, acc.w);
+            }
+        }
+        *(float4*)(run_s + ((size_t)r * MERGE_CHUNKS + c) * HD + 4 * d4) = acc;
+    }
+    consumer_sync();
+    for (int e = threadIdx.x; e < n_rows * (HD / 4); e += CONSUMERS * 32) {
+        const int r = e / (HD / 4), d4 = e % (HD / 4);
+        float4 acc = *(const float4*)(run_s + (size_t)r * MERGE_CHUNKS * HD + 4 * d4);
+#pragma unroll
+        for (int c = 1; c < MERGE_CHUNKS; ++c) {
+            const float4 v = *(const float4*)(run_s + ((size_t)r * MERGE_CHUNKS + c) * HD + 4 * d4);
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
         }
         const float inv = inv_s[r];
         const int tok = t0 + r / G, head = kvh * G + r % G;
@@ -392,7 +425,7 @@ int launch(const AttentionParams& p, const StepTokens& b, const PagedCache& c, c
     if (!make_map(&mv, (const __nv_bfloat16*)c.kv + c.v_offset, 2, dims, strides, box)) return SPITE_LAUNCH_FAILED;
     const size_t stage = 2 * (size_t)NKB * BOX_BYTES;
     const size_t merge = (size_t)CONSUMERS * 16 * hd * 4 + CONSUMERS * 16 * 2 * 4;
-    const size_t weights = (size_t)(16 * x.n_splits + 16) * 4;
+    const size_t weights = (size_t)(2 * 16 * x.n_splits + 16 + 16 * MERGE_CHUNKS * hd) * 4;
     size_t ring = (size_t)n_stages * stage;
     if (ring < merge) ring = merge;
     if (ring < weights) ring = weights;
