@@ -335,9 +335,9 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const GemmParams p
                         }
                     }
             }
-            __threadfence();
             consumer_sync();
             if (threadIdx.x == 0) {
+                __threadfence();                              // after the barrier: it covers what the other threads stored
                 const int arrived = atomicAdd(&tickets[it.tile], 1);
                 tail->last = (arrived == n_splits - 1);
                 if (tail->last) tickets[it.tile] = 0;
@@ -349,9 +349,22 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const GemmParams p
                 for (int idx = threadIdx.x; idx < COLS * it.m; idx += CONSUMERS * 32) {
                     const int col = idx % COLS, t = idx / COLS;
                     float v = 0.f, v2 = 0.f;
-                    for (int sp = 0; sp < n_splits; ++sp) {
-                        v += __ldcg(all + ((size_t)sp * NT + t) * TR + col);
-                        if (DUAL) v2 += __ldcg(all + ((size_t)sp * NT + t) * TR + TR / 2 + col);
+                    // eight splits' loads are on their way together: a loop whose length the compiler does not know
+                    // would wait for every load (a trip to L2, often the other die's) before it asks for the next
+                    for (int sp0 = 0; sp0 < n_splits; sp0 += 8) {
+                        float a[8], b[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const bool in = sp0 + j < n_splits;
+                            const float* from = all + ((size_t)(sp0 + j) * NT + t) * TR + col;
+                            a[j] = in ? __ldcg(from) : 0.f;
+                            b[j] = DUAL && in ? __ldcg(from + TR / 2) : 0.f;
+                        }
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            v += a[j];
+                            if (DUAL) v2 += b[j];
+                        }
                     }
                     finish(t, col, v, v2);
                 }
