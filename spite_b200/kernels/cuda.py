@@ -98,6 +98,54 @@ def _check(status, what):
         raise KernelError(f"{what}: {_STATUS.get(status, f'status {status}')}")
 
 
+def stream_cut(M: int, N: int, K: int, groups: int, swiglu: bool, slots: int, smem: int, nt: int, *,
+               item_cost: float = 2.0, split_item_cost: float = 6.0, split_cost: float = 1.5, slice_cost: float = 1.0,
+               max_slices: int = 8, slices_min_rows: int = 4):
+    """(k slices inside a block, k splits across blocks) of the weight-streaming kernel for a product of M rows,
+    N output columns (per group) and depth K on `slots` resident blocks of `smem` bytes, `nt` token columns.
+
+    A product of few tiles of 128 rows (a dense projection at a few tokens: 40 to 128 tiles for 296 to 444
+    resident blocks) would leave most multiprocessors without work, and the ones that have some are then
+    bound by what a single one can pull; so the items are made smaller until they fill the resident blocks
+    about once: lower tiles with the k blocks of a stage side by side (the sums meet in shared memory), or k
+    splits across blocks (partial sums through global memory, a ticket, a second pass over as many partial
+    tiles as there are splits).  The cost of a choice is its rounds of items times (stages an item + what an
+    item costs besides, in stages of 16 KiB: `item_cost` for any item, `split_item_cost` + `split_cost` a split
+    if its sums cross blocks, `slice_cost` if its slices meet in shared memory); at least four stages stay
+    together.
+
+    Measured on B200, us, (slices, splits) forced.  Eight tokens (444 blocks): qkv 7168 x 5120: (1, 5) 19.6,
+    (2, 1) 20.9, (4, 1) 17.3, (8, 1) 21.3, (2, 2) 18.9; output projection 5120 x 5120: (1, 7) 16.5, (4, 1)
+    14.2, (8, 1) 13.0, (4, 2) 13.1; shared down 5120 x 8192: (1, 7) 21.6, (4, 1) 20.8, (8, 1) 18.6; seven
+    experts' gate/up: (1, 1) 220, (1, 2) 199.5, (2, 1) 197.4, (4, 1) 195.5; their down product: (1, 1) 117.6,
+    (2, 1) 113.5, (4, 1) 107.3, (8, 1) 113.4.  One token (296 blocks with rings twice as deep): slices bring
+    nothing, qkv (1, 5) 17.5, (2, 2) 17.0, (4, 1) 19.5; output projection (1, 7) 13.9, (2, 2) 14.1, (4, 1)
+    17.1; so products of fewer than `slices_min_rows` rows keep tiles of 128 rows."""
+    best, best_cost = (1, 1), None
+    for slices in (1, 2, 4, 8):
+        if K % (64 * slices) or (swiglu and slices == 8):
+            continue
+        if slices > 1 and (M < slices_min_rows or slices > max_slices):
+            continue
+        stage_bytes = 16384 + max(1024, slices * nt * 128)
+        if slices > 1 and (smem - 5504 - (8 - 8 // slices) * 64 * nt) // stage_bytes < 2:
+            continue                                          # a ring of one stage
+        rows = 128 // slices
+        tiles = -(-N // (rows // 2 if swiglu else rows)) * groups
+        stages = K // (64 * slices)
+        for s in range(1, max(1, min(32, stages // 4)) + 1):
+            rounds = -(-tiles * s // slots)
+            fixed = item_cost + (slice_cost if slices > 1 else 0.0)
+            if s > 1:
+                fixed += split_item_cost + split_cost * s
+            cost = rounds * (-(-stages // s) + fixed)
+            if best_cost is None or cost < best_cost:
+                best, best_cost = (slices, s), cost
+            if tiles * s >= 4 * slots:
+                break
+    return best
+
+
 class CudaKernels(KernelSet):
     def __init__(self, dtype: torch.dtype, device="cuda:0"):
         if dtype not in _DT:
@@ -147,7 +195,7 @@ class CudaKernels(KernelSet):
         self.stream_split_cost = 1.5
         self.stream_slice_cost = 1.0
         self.stream_max_slices = 8             # 1: tiles of 128 rows only
-        self.stream_slices_min_rows = 4        # products of fewer rows keep tiles of 128 rows (see _stream_cut)
+        self.stream_slices_min_rows = 4        # products of fewer rows keep tiles of 128 rows (see stream_cut)
         self.stream_force = None               # (k slices, k splits) for every call, for measurements
         # (shared memory per block, resident blocks) for up to 3 tokens and for more: measured in the decode step at
         # Scout shapes, one token 2.90 ms with (110 KiB, 2 per multiprocessor) against 3.01 with (74 KiB, 3), eight
@@ -361,45 +409,10 @@ class CudaKernels(KernelSet):
             C.c_longlong(n_floats), C.c_void_p(_ptr(tickets)), self._tickets_n, C.c_void_p(stream))
 
     def _stream_cut(self, M: int, N: int, K: int, groups: int, swiglu: bool, slots: int, smem: int, nt: int):
-        """(k slices inside a block, k splits across blocks) of the weight-streaming kernel.  A product of few
-        tiles of 128 rows (a dense projection at a few tokens: 40 to 128 tiles for 296 to 444 resident blocks)
-        would leave most multiprocessors without work, and the ones that have some are then bound by what a
-        single one can pull; so the items are made smaller until they fill the resident blocks about once:
-        lower tiles with the k blocks of a stage side by side (the sums meet in shared memory), or k splits
-        across blocks (partial sums through global memory, a ticket, a second pass over as many partial tiles
-        as there are splits).  The cost of a choice is its rounds of items times (stages an item + what an
-        item costs besides); at least four stages stay together.
-
-        Measured on B200, us, (slices, splits) forced.  Eight tokens (444 blocks): qkv 7168 x 5120: (1, 5) 19.6,
-        (2, 1) 20.9, (4, 1) 17.3, (8, 1) 21.3, (2, 2) 18.9; output projection 5120 x 5120: (1, 7) 16.5, (4, 1)
-        14.2, (8, 1) 13.0, (4, 2) 13.1; shared down 5120 x 8192: (1, 7) 21.6, (4, 1) 20.8, (8, 1) 18.6; seven
-        experts' gate/up: (1, 1) 220, (1, 2) 199.5, (2, 1) 197.4, (4, 1) 195.5, (8, 1) 260 (stages of eight 2 KiB
-        boxes); their down product: (1, 1) 117.6, (2, 1) 113.5, (4, 1) 107.3, (8, 1) 113.4.  One token (296
-        blocks with rings twice as deep): slices bring nothing, qkv (1, 5) 17.5, (2, 2) 17.0, (4, 1) 19.5;
-        output projection (1, 7) 13.9, (2, 2) 14.1, (4, 1) 17.1; so up to three tokens the tiles stay at 128 rows."""
-        best, best_cost = (1, 1), None
-        for slices in (1, 2, 4, 8):
-            if K % (64 * slices) or (swiglu and slices == 8):
-                continue
-            if slices > 1 and (M <= self.stream_slices_min_rows - 1 or slices > self.stream_max_slices):
-                continue
-            stage_bytes = 16384 + max(1024, slices * nt * 128)
-            if slices > 1 and (smem - 5504 - (8 - 8 // slices) * 64 * nt) // stage_bytes < 2:
-                continue                                          # a ring of one stage
-            rows = 128 // slices
-            tiles = -(-N // (rows // 2 if swiglu else rows)) * groups
-            stages = K // (64 * slices)
-            for s in range(1, max(1, min(32, stages // 4)) + 1):
-                rounds = -(-tiles * s // slots)
-                fixed = self.stream_item_cost + (self.stream_slice_cost if slices > 1 else 0.0)
-                if s > 1:
-                    fixed += self.stream_split_item_cost + self.stream_split_cost * s
-                cost = rounds * (-(-stages // s) + fixed)
-                if best_cost is None or cost < best_cost:
-                    best, best_cost = (slices, s), cost
-                if tiles * s >= 4 * slots:
-                    break
-        return best
+        return stream_cut(M, N, K, groups, swiglu, slots, smem, nt, item_cost=self.stream_item_cost,
+                          split_item_cost=self.stream_split_item_cost, split_cost=self.stream_split_cost,
+                          slice_cost=self.stream_slice_cost, max_slices=self.stream_max_slices,
+                          slices_min_rows=self.stream_slices_min_rows)
 
     def attention_tc_error(self) -> int:
         """Error code left by a tcgen05 attention block that gave up waiting (0: none); clears it. Synchronises."""
