@@ -74,6 +74,15 @@ __device__ __forceinline__ void cp_async_arrive(unsigned bar) {
     asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];\n" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;\n" ::"n"(CONSUMERS * 32) : "memory"); }
+// The same barrier, and whether any consumer thread brought `v`: one answer for all of them.  (The producer
+// may raise the abort flag at any moment; consumers that each read it for themselves could disagree, and those
+// that stay would wait at the next barrier for those that left.)
+__device__ __forceinline__ bool consumer_sync_any(bool v) {
+    unsigned any;
+    asm volatile("{\n.reg .pred p, q;\nsetp.ne.u32 q, %1, 0;\nbar.red.or.pred p, 1, %2, q;\nselp.u32 %0, 1, 0, p;\n}\n"
+                 : "=r"(any) : "r"((unsigned)v), "n"(CONSUMERS * 32) : "memory");
+    return any != 0;
+}
 
 struct Item {
     int group, lo, m;             // group, its first row in the sorted order, its tokens
@@ -275,7 +284,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const GemmParams p
 #pragma unroll
                         for (int e = 0; e < 4; ++e) slice_sums[((warp - R) * 32 + lane) * (4 * NB) + 4 * j + e] = acc[j][e];
                 }
-                consumer_sync();
+                const bool stop = consumer_sync_any(*abort_flag != 0);
                 if (slice == 0) {
 #pragma unroll
                     for (int sl = 1; sl < S; ++sl)
@@ -284,7 +293,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const GemmParams p
 #pragma unroll
                             for (int e = 0; e < 4; ++e) acc[j][e] += slice_sums[(((sl - 1) * R + rg) * 32 + lane) * (4 * NB) + 4 * j + e];
                 }
-                if (n_splits == 1 && *abort_flag) break;      // the same answer in every warp, after the barrier
+                if (n_splits == 1 && stop) break;             // the same answer in every warp
             }
             const bool writer = slice == 0;
 
@@ -369,8 +378,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const GemmParams p
                     finish(t, col, v, v2);
                 }
             }
-            consumer_sync();                                  // `last` is read before the next item writes it
-            if (*abort_flag) break;                           // the same answer in every warp, after the barrier
+            if (consumer_sync_any(*abort_flag != 0)) break;   // (`last` is read before the next item writes it)
             ok = true;
         }
     }
