@@ -36,6 +36,7 @@ def main(argv=None):
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--case", default="", help="run only the cases whose name contains this text")
     ap.add_argument("--experts", type=int, default=16, help="experts of the grouped products (128: Maverick's)")
+    ap.add_argument("--rows", default="1,8,64", help="token counts of the decode families")
     args = ap.parse_args(argv)
     dev = "cuda:0"
     torch.cuda.set_device(0)
@@ -111,8 +112,9 @@ def main(argv=None):
 
     # ---- plain products
     shapes = [("qkv", (nq + 2 * nkv) * hd, d), ("o_proj", d, nq * hd), ("shared_down", d, F), ("lm_head", V, d)]
+    decode_rows = tuple(int(m) for m in args.rows.split(","))
     if want("gemm_decode"):
-        for M in (1, 8, 64):
+        for M in decode_rows:
             for name, N, K in shapes:
                 def make(M=M, N=N, K=K, name=name):
                     x, w = rnd(M, K), rnd(N, K)
@@ -150,7 +152,7 @@ def main(argv=None):
         offsets = torch.zeros(E + 1, dtype=torch.int32, device=dev)
         offsets[1:] = torch.cumsum(torch.bincount(ids, minlength=E), 0)
         return order.indices.to(torch.int32), offsets, int(ids.unique().numel())
-    for fam, Ms in (("moe_decode", (1, 8, 64)), ("moe_prefill", (512,) if args.small else (256, 512, 1024, 2048, 8192))):
+    for fam, Ms in (("moe_decode", decode_rows), ("moe_prefill", (512,) if args.small else (256, 512, 1024, 2048, 8192))):
         if not want(fam):
             continue
         w_gu, w_dn = rnd(E, 2 * F, d), rnd(E, d, F)

@@ -114,13 +114,18 @@ def stream_cut(M: int, N: int, K: int, groups: int, swiglu: bool, slots: int, sm
     if its sums cross blocks, `slice_cost` if its slices meet in shared memory); at least four stages stay
     together.
 
-    Measured on B200, us, (slices, splits) forced.  Eight tokens (444 blocks): qkv 7168 x 5120: (1, 5) 19.6,
-    (2, 1) 20.9, (4, 1) 17.3, (8, 1) 21.3, (2, 2) 18.9; output projection 5120 x 5120: (1, 7) 16.5, (4, 1)
-    14.2, (8, 1) 13.0, (4, 2) 13.1; shared down 5120 x 8192: (1, 7) 21.6, (4, 1) 20.8, (8, 1) 18.6; seven
-    experts' gate/up: (1, 1) 220, (1, 2) 199.5, (2, 1) 197.4, (4, 1) 195.5; their down product: (1, 1) 117.6,
-    (2, 1) 113.5, (4, 1) 107.3, (8, 1) 113.4.  One token (296 blocks with rings twice as deep): slices bring
-    nothing, qkv (1, 5) 17.5, (2, 2) 17.0, (4, 1) 19.5; output projection (1, 7) 13.9, (2, 2) 14.1, (4, 1)
-    17.1; so products of fewer than `slices_min_rows` rows keep tiles of 128 rows."""
+    Measured on B200, us, (slices, splits) forced, each product alone.  Eight tokens (444 blocks): qkv 7168 x
+    5120: (1, 5) 19.6, (2, 1) 20.9, (4, 1) 17.3, (8, 1) 21.3, (2, 2) 18.9; output projection 5120 x 5120: (1, 7)
+    16.5, (4, 1) 14.2, (8, 1) 13.0, (4, 2) 13.1; shared down 5120 x 8192: (1, 7) 21.6, (4, 1) 20.8, (8, 1) 18.6;
+    seven experts' gate/up: (1, 1) 220, (1, 2) 199.5, (2, 1) 197.4, (4, 1) 195.5; their down product: (1, 1)
+    117.6, (2, 1) 113.5, (4, 1) 107.3, (8, 1) 113.4.  One token (296 blocks with rings twice as deep): slices
+    bring nothing, qkv (1, 5) 17.5, (2, 2) 17.0, (4, 1) 19.5; output projection (1, 7) 13.9, (2, 2) 14.1, (4, 1)
+    17.1.  In the decode step (ms at 4 / 6 / 8 / 12 / 16 tokens): no slices 4.64 / 5.64 / 6.63 / 8.38 / 9.67;
+    slices everywhere 4.89 / 5.85 / 6.51 / 8.68 / 9.45; for one-group products only 4.73 / 5.62 / 6.52 / 8.41 /
+    9.53; for the experts' products only 4.76 / 5.83 / 6.63 / 8.68 / 9.60.  The experts' products are faster
+    alone with slices and slower in the step: with tiles of 128 rows some blocks end early and the next
+    kernel's blocks start under the rest.  So the caller allows slices for one-group products from
+    `slices_min_rows` rows on (the kernel set's defaults: six), and tiles of 128 rows otherwise."""
     best, best_cost = (1, 1), None
     for slices in (1, 2, 4, 8):
         if K % (64 * slices) or (swiglu and slices == 8):
@@ -195,7 +200,8 @@ class CudaKernels(KernelSet):
         self.stream_split_cost = 1.5
         self.stream_slice_cost = 1.0
         self.stream_max_slices = 8             # 1: tiles of 128 rows only
-        self.stream_slices_min_rows = 4        # products of fewer rows keep tiles of 128 rows (see stream_cut)
+        self.stream_slices_min_rows = 6        # products of fewer rows keep tiles of 128 rows (see stream_cut)
+        self.stream_slices_grouped = False     # ... and so do grouped products
         self.stream_force = None               # (k slices, k splits) for every call, for measurements
         # (shared memory per block, resident blocks) for up to 3 tokens and for more: measured in the decode step at
         # Scout shapes, one token 2.90 ms with (110 KiB, 2 per multiprocessor) against 3.01 with (74 KiB, 3), eight
@@ -390,7 +396,7 @@ class CudaKernels(KernelSet):
         groups = min(p.n_groups, p.M) if grouped else 1
         smem, blocks = self.stream_shape[p.M > 3]
         nt = 8 if max_rows_per_group <= 8 else 16
-        slices, splits = self.stream_force or self._stream_cut(p.M, p.N, p.K, groups, swiglu, blocks, smem, nt)
+        slices, splits = self.stream_force or self._stream_cut(p.M, p.N, p.K, groups, swiglu, blocks, smem, nt, grouped)
         rows = 128 // slices
         tiles = -(-p.N // (rows // 2 if swiglu else rows)) * groups
         scratch, n_floats = None, 0
@@ -408,10 +414,12 @@ class CudaKernels(KernelSet):
             C.byref(p), max_rows_per_group, slices, blocks, smem, splits, C.c_void_p(_ptr(scratch)),
             C.c_longlong(n_floats), C.c_void_p(_ptr(tickets)), self._tickets_n, C.c_void_p(stream))
 
-    def _stream_cut(self, M: int, N: int, K: int, groups: int, swiglu: bool, slots: int, smem: int, nt: int):
+    def _stream_cut(self, M: int, N: int, K: int, groups: int, swiglu: bool, slots: int, smem: int, nt: int,
+                    grouped: bool):
         return stream_cut(M, N, K, groups, swiglu, slots, smem, nt, item_cost=self.stream_item_cost,
                           split_item_cost=self.stream_split_item_cost, split_cost=self.stream_split_cost,
-                          slice_cost=self.stream_slice_cost, max_slices=self.stream_max_slices,
+                          slice_cost=self.stream_slice_cost,
+                          max_slices=self.stream_max_slices if self.stream_slices_grouped or not grouped else 1,
                           slices_min_rows=self.stream_slices_min_rows)
 
     def attention_tc_error(self) -> int:

@@ -21,7 +21,8 @@ def test_the_measured_shapes_get_the_cuts_that_were_fastest():
     assert cut(8, 5120, 5120) == (8, 1)                       # output projection: 320 tiles of 16 rows
     assert cut(8, 5120, 8192) == (8, 1)                       # shared expert, down
     assert cut(8, 8192, 5120, groups=7, swiglu=True)[1] == 1  # seven experts' gate/up: tiles enough without k splits
-    assert cut(8, 5120, 8192, groups=7) == (4, 1)
+    assert cut(8, 5120, 8192, groups=7) == (4, 1)             # (if the caller allows slices for grouped products)
+    assert cut(8, 5120, 8192, groups=7, max_slices=1)[0] == 1
     # one token: tiles of 128 rows, k splits that fill 296 blocks about once
     assert cut(1, 7168, 5120) == (1, 5)
     assert cut(1, 5120, 5120) == (1, 7)
@@ -38,7 +39,7 @@ def test_every_cut_is_one_the_kernel_takes(M, N, K, swiglu, groups):
     slices, splits = cut(M, N, K, groups=min(groups, M), swiglu=swiglu)
     assert slices in (1, 2, 4, 8) and K % (64 * slices) == 0          # a stage is `slices` k blocks of 64
     assert not (swiglu and slices == 8)                                # tiles of 8 gate and 8 up rows are not built
-    assert slices == 1 or M >= 4                                       # few rows keep tiles of 128 rows
+    assert slices == 1 or M >= 4                                       # few rows keep tiles of 128 rows (the function's default)
     stages = K // (64 * slices)
     assert 1 <= splits <= max(1, stages // 4)                          # at least four stages stay together
     nt = 8 if M <= 8 else 16
