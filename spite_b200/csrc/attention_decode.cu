@@ -27,8 +27,7 @@ using namespace tc;
 constexpr int CONSUMERS = 4;
 constexpr int THREADS = (CONSUMERS + 1) * 32;
 constexpr int BN = 64;                                    // keys of a tile
-constexpr int MERGE_CHUNKS = 2;                           // runs of splits whose partial results are added side by side
-constexpr int MERGE_BATCH = 12;                           // loads of a thread that are on their way together
+constexpr int MERGE_BATCH = 24;                           // partial results a thread asks for together when splits are merged
 constexpr int BOX_BYTES = BN * 128;                       // 64 rows of 64 elements
 constexpr int MAX_STAGES = 8;
 
@@ -339,15 +338,26 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const __grid_const
     consumer_sync();
     if (!tail->last) return;
     __threadfence();
-    // What the merge costs is the latency of its loads from L2, so they are made few rounds of many: one round
-    // for every split's maximum and sum, then the output elements with the splits cut into MERGE_CHUNKS runs whose
-    // loads are all on their way together.  The order of every sum is fixed: splits in order within a run, the
-    // runs in order.
+    // What the merge costs is the latency of its loads from L2 (partial results that other multiprocessors have
+    // just written), so they are made few rounds of many.  A thread sums four output elements over the splits, in
+    // split order; the partial outputs of its first elements are asked for at once, MERGE_BATCH splits together,
+    // then every split's maximum and sum in one round, from which the splits' weights follow while the first
+    // loads are still on their way.  (A loop over the splits whose length the compiler does not know would wait
+    // for every load before it asks for the next: 6 us for 24 splits.)
     const int count = x.n_splits;
     float* w_s = (float*)smem;                               // [16][count] weights of the splits
     float* l_sp = w_s + 16 * count;                          // [16][count] their sums
     float* inv_s = l_sp + 16 * count;                        // [16] inverse of the merged sums
-    float* run_s = inv_s + 16;                               // [16][MERGE_CHUNKS][HD] sums of the runs
+    const int n_items = n_rows * (HD / 4);
+    float4 v[MERGE_BATCH];
+    auto ask = [&](int e, int sp0) {
+        const int r = e / (HD / 4), d4 = e % (HD / 4);
+        const float4* from = (const float4*)(part_all + (size_t)r * ROW) + d4;
+#pragma unroll
+        for (int j = 0; j < MERGE_BATCH; ++j)
+            v[j] = e < n_items && sp0 + j < count ? __ldcg(from + (size_t)(sp0 + j) * (16 * ROW / 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
+    };
+    ask(threadIdx.x, 0);
     for (int i = threadIdx.x; i < n_rows * count; i += CONSUMERS * 32) {
         const int r = i / count, sp = i % count;
         const float2 ml = __ldcg((const float2*)(part_all + ((size_t)sp * 16 + r) * ROW + HD));
@@ -374,37 +384,18 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const __grid_const
         if (lane == 0) inv_s[r] = 1.0f / fmaxf(l, 1e-30f);
     }
     consumer_sync();
-    const int per_run = (count + MERGE_CHUNKS - 1) / MERGE_CHUNKS;
-    for (int e = threadIdx.x; e < n_rows * (HD / 4) * MERGE_CHUNKS; e += CONSUMERS * 32) {
-        const int d4 = e % (HD / 4), c = (e / (HD / 4)) % MERGE_CHUNKS, r = e / ((HD / 4) * MERGE_CHUNKS);
-        const float4* from = (const float4*)(part_all + (size_t)r * ROW) + d4;
+    for (int e = threadIdx.x; e < n_items; e += CONSUMERS * 32) {
+        const int r = e / (HD / 4), d4 = e % (HD / 4);
         const float* w = w_s + r * count;
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        const int sp_end = min(count, (c + 1) * per_run);
-        for (int sp0 = c * per_run; sp0 < sp_end; sp0 += MERGE_BATCH) {
-            // (a loop of known length with the loads first: a loop whose length the compiler does not know
-            // would wait for every load before it asks for the next)
-            float4 v[MERGE_BATCH];
-#pragma unroll
-            for (int j = 0; j < MERGE_BATCH; ++j)
-                v[j] = sp0 + j < sp_end ? __ldcg(from + (size_t)(sp0 + j) * (16 * ROW / 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int sp0 = 0; sp0 < count; sp0 += MERGE_BATCH) {
+            if (e != (int)threadIdx.x || sp0 > 0) ask(e, sp0);   // (the first batch of the first item is here already)
 #pragma unroll
             for (int j = 0; j < MERGE_BATCH; ++j) {
-                const float ws = sp0 + j < sp_end ? w[sp0 + j] : 0.f;
+                const float ws = sp0 + j < count ? w[sp0 + j] : 0.f;
                 acc.x = fmaf(v[j].x, ws, acc.x); acc.y = fmaf(v[j].y, ws, acc.y);
                 acc.z = fmaf(v[j].z, ws, acc.z); acc.w = fmaf(v[j].w, ws, acc.w);
             }
-        }
-        *(float4*)(run_s + ((size_t)r * MERGE_CHUNKS + c) * HD + 4 * d4) = acc;
-    }
-    consumer_sync();
-    for (int e = threadIdx.x; e < n_rows * (HD / 4); e += CONSUMERS * 32) {
-        const int r = e / (HD / 4), d4 = e % (HD / 4);
-        float4 acc = *(const float4*)(run_s + (size_t)r * MERGE_CHUNKS * HD + 4 * d4);
-#pragma unroll
-        for (int c = 1; c < MERGE_CHUNKS; ++c) {
-            const float4 v = *(const float4*)(run_s + ((size_t)r * MERGE_CHUNKS + c) * HD + 4 * d4);
-            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
         }
         const float inv = inv_s[r];
         const int tok = t0 + r / G, head = kvh * G + r % G;
@@ -425,7 +416,7 @@ int launch(const AttentionParams& p, const StepTokens& b, const PagedCache& c, c
     if (!make_map(&mv, (const __nv_bfloat16*)c.kv + c.v_offset, 2, dims, strides, box)) return SPITE_LAUNCH_FAILED;
     const size_t stage = 2 * (size_t)NKB * BOX_BYTES;
     const size_t merge = (size_t)CONSUMERS * 16 * hd * 4 + CONSUMERS * 16 * 2 * 4;
-    const size_t weights = (size_t)(2 * 16 * x.n_splits + 16 + 16 * MERGE_CHUNKS * hd) * 4;
+    const size_t weights = (size_t)(2 * 16 * x.n_splits + 16) * 4;
     size_t ring = (size_t)n_stages * stage;
     if (ring < merge) ring = merge;
     if (ring < weights) ring = weights;
