@@ -84,6 +84,21 @@ __device__ __forceinline__ bool consumer_sync_any(bool v) {
     return any != 0;
 }
 
+__device__ __forceinline__ unsigned cluster_rank() {
+    unsigned r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+// Four floats into the shared memory of the cluster's block `rank`, at the place `own` has in this block's.
+__device__ __forceinline__ void cluster_store4(const void* own, unsigned rank, const float (&v)[4]) {
+    unsigned addr = (unsigned)__cvta_generic_to_shared(own), remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(remote) : "r"(addr), "r"(rank));
+    asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};\n" ::"r"(remote), "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]) : "memory");
+}
+
 struct Item {
     int group, lo, m;             // group, its first row in the sorted order, its tokens
     int tile, n0;                 // tile id (group slot x row tiles + row tile) and first output column
@@ -92,7 +107,10 @@ struct Item {
 
 // NT: token columns (8 or 16).  S: k slices inside the block.  `n_splits` k splits per tile; `scratch` holds
 // tiles x n_splits x NT x (128 / S) floats, `tickets` one zeroed int per tile (left zeroed).
-template <int NT, int EPI, int S>
+// CL (with S = 1): the k splits of a tile are the blocks of one thread-block cluster, the grid has one block per
+// (tile, split), and the splits' sums meet in the shared memory of the cluster's first block instead of in
+// global memory: no scratch, no fence, no ticket, no second pass through L2.
+template <int NT, int EPI, int S, bool CL>
 __global__ void __launch_bounds__(THREADS, 3)
 gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const GemmParams p, const int n_stages,
                    const int n_splits, float* __restrict__ scratch, int* __restrict__ tickets, const WaitControl waits) {
@@ -232,6 +250,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const GemmParams p
             }
         }
         asm volatile("cp.async.wait_all;\n" ::: "memory");
+        if (CL && (int)blockIdx.x < total) { cluster_sync(); cluster_sync(); }     // with the consumers, see below
     } else {
         // ---- consumers: warp w works on slice w / R; it owns rows 16 r .. 16 r + 15 (r = w % R) of the tile
         //      (SwiGLU: gate rows 8 r .. + 7 and the up rows of the same output columns as fragment rows 8 .. 15)
@@ -311,8 +330,29 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const GemmParams p
                 else if (EPI == EPI_ADD_F32) ((float*)p.C)[o] += v * sc;
                 else ((__nv_bfloat16*)p.C)[o] = __float2bfloat16_rn(silu_f32(v * sc) * (v2 * sc));
             };
-            if (n_splits == 1) {
-                if (writer) {
+            if (CL) {
+                // the k loops of all the cluster's blocks have ended (the first block's ring is free: the others'
+                // sums land there); then the first block adds them in the order of the splits
+                float* const landing = (float*)smem;              // [split - 1][warp][lane][4 NB]
+                cluster_sync();
+                const unsigned rank = cluster_rank();
+                if (rank > 0 && ok) {
+#pragma unroll
+                    for (int j = 0; j < NB; ++j)
+                        cluster_store4(landing + ((((size_t)rank - 1) * CONSUMERS + warp) * 32 + lane) * (4 * NB) + 4 * j, 0, acc[j]);
+                }
+                cluster_sync();
+                if (rank == 0) {
+                    for (int sp = 1; sp < n_splits; ++sp)
+#pragma unroll
+                        for (int j = 0; j < NB; ++j)
+#pragma unroll
+                            for (int e = 0; e < 4; ++e)
+                                acc[j][e] += landing[((((size_t)sp - 1) * CONSUMERS + warp) * 32 + lane) * (4 * NB) + 4 * j + e];
+                }
+            }
+            if (n_splits == 1 || CL) {
+                if (writer && (!CL || cluster_rank() == 0)) {
 #pragma unroll
                     for (int j = 0; j < NB; ++j)
 #pragma unroll
@@ -384,7 +424,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const GemmParams p
     }
 }
 
-template <int NT, int EPI, int S>
+template <int NT, int EPI, int S, bool CL>
 int launch(const GemmParams& p, int n_blocks, int smem_budget, int n_splits, float* scratch, int* tickets, cudaStream_t st) {
     constexpr bool DUAL = (EPI == EPI_SWIGLU);
     constexpr int TR = ROWS / S;
@@ -401,26 +441,56 @@ int launch(const GemmParams& p, int n_blocks, int smem_budget, int n_splits, flo
     if (n_stages > MAX_STAGES) n_stages = MAX_STAGES;
     if (n_stages < 2) return SPITE_UNSUPPORTED;                    // (16 tokens x 8 slices are 32 KiB a stage)
     const size_t smem = (size_t)n_stages * STAGE + FIXED;
-    auto k = gemm_stream_kernel<NT, EPI, S>;
+    auto k = gemm_stream_kernel<NT, EPI, S, CL>;
     if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||
         cudaFuncSetAttribute(k, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared) != cudaSuccess)
         return SPITE_LAUNCH_FAILED;
     const int cols = DUAL ? TR / 2 : TR;
     const long long tiles = (long long)((p.N + cols - 1) / cols) * (p.group_offsets ? (p.n_groups < p.M ? p.n_groups : p.M) : 1) * n_splits;
-    const int grid = (int)(tiles < n_blocks ? tiles : n_blocks);
-    SPITE_LAUNCH(k, grid, THREADS, smem, st, mw, p, n_stages, n_splits, scratch, tickets, s_waits);
+    if (!CL) {
+        const int grid = (int)(tiles < n_blocks ? tiles : n_blocks);
+        SPITE_LAUNCH(k, grid, THREADS, smem, st, mw, p, n_stages, n_splits, scratch, tickets, s_waits);
+        return spite_launch_status();
+    }
+    // one block per (tile, split), the splits of a tile one cluster; all of them resident at once, or the caller
+    // takes the other way (-2): a second round of clusters would cost more than the cluster saves
+    if (n_splits < 2 || n_splits > 8 || tiles > n_blocks) return SPITE_UNSUPPORTED;
+    if ((size_t)(n_splits - 1) * CONSUMERS * 32 * (NT / 2) * 4 > (size_t)n_stages * STAGE) return SPITE_UNSUPPORTED;   // the landing place is the ring
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)tiles);
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)n_splits;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int fit = 0;
+    if (cudaOccupancyMaxActiveClusters(&fit, k, &cfg) != cudaSuccess) { (void)cudaGetLastError(); return SPITE_UNSUPPORTED; }
+    if ((long long)fit * n_splits < tiles) return SPITE_UNSUPPORTED;
+    cfg.numAttrs = spite_pdl_enabled() ? 2 : 1;
+    (void)cudaLaunchKernelEx(&cfg, k, mw, p, n_stages, n_splits, scratch, tickets, s_waits);
     return spite_launch_status();
 }
 
 template <int NT, int EPI>
-int launch_slices(int k_slices, const GemmParams& p, int n_blocks, int smem_budget, int n_splits, float* scratch, int* tickets,
-                  cudaStream_t st) {
+int launch_slices(int k_slices, bool cluster, const GemmParams& p, int n_blocks, int smem_budget, int n_splits, float* scratch,
+                  int* tickets, cudaStream_t st) {
+    if (cluster) {
+        if (k_slices != 1) return SPITE_BAD_ARG;
+        return launch<NT, EPI, 1, true>(p, n_blocks, smem_budget, n_splits, scratch, tickets, st);
+    }
     switch (k_slices) {
-        case 1: return launch<NT, EPI, 1>(p, n_blocks, smem_budget, n_splits, scratch, tickets, st);
-        case 2: return launch<NT, EPI, 2>(p, n_blocks, smem_budget, n_splits, scratch, tickets, st);
-        case 4: return launch<NT, EPI, 4>(p, n_blocks, smem_budget, n_splits, scratch, tickets, st);
+        case 1: return launch<NT, EPI, 1, false>(p, n_blocks, smem_budget, n_splits, scratch, tickets, st);
+        case 2: return launch<NT, EPI, 2, false>(p, n_blocks, smem_budget, n_splits, scratch, tickets, st);
+        case 4: return launch<NT, EPI, 4, false>(p, n_blocks, smem_budget, n_splits, scratch, tickets, st);
         case 8: return EPI == EPI_SWIGLU ? SPITE_UNSUPPORTED       // (tiles of 8 gate and 8 up rows: nobody needs them)
-                                         : launch<NT, EPI == EPI_SWIGLU ? EPI_STORE : EPI, 8>(p, n_blocks, smem_budget, n_splits, scratch, tickets, st);
+                                         : launch<NT, EPI == EPI_SWIGLU ? EPI_STORE : EPI, 8, false>(p, n_blocks, smem_budget, n_splits, scratch, tickets, st);
         default: return SPITE_BAD_ARG;
     }
 }
@@ -430,12 +500,14 @@ int launch_slices(int k_slices, const GemmParams& p, int n_blocks, int smem_budg
 // `max_rows_per_group` <= 16.  `k_slices` (1, 2, 4 or 8; 8 not with SwiGLU): a tile has 128 / k_slices weight rows
 // (SwiGLU: half of them gate, half up) and K must be a multiple of 64 k_slices.  `n_blocks`: resident blocks
 // (two per multiprocessor fit when `smem_budget`, the bytes of shared memory a block may take, is at most about
-// 110 KiB, three at 74 KiB).  `n_splits`: k splits per tile across blocks (1: no scratch needed).  `scratch`:
-// groups-with-tokens x row tiles x n_splits x 16 x (128 / k_slices) floats; `tickets`: that many tiles' ints,
-// zero before the first call; calls that share them must not overlap.
-SPITE_API int spite_gemm_stream(const GemmParams* p, int max_rows_per_group, int k_slices, int n_blocks, int smem_budget,
-                                int n_splits, float* scratch, long long scratch_floats, int* tickets, int n_tickets,
-                                void* stream) {
+// 110 KiB, three at 74 KiB).  `n_splits`: k splits per tile across blocks (1: no scratch needed).  `cluster`
+// (with k_slices 1 and 2 to 8 splits): the splits of a tile are one thread-block cluster and meet in shared
+// memory; needs no scratch and no tickets, and is refused (-2) when the (tile, split) blocks are not all
+// resident at once.  `scratch`: groups-with-tokens x row tiles x n_splits x 16 x (128 / k_slices) floats;
+// `tickets`: that many tiles' ints, zero before the first call; calls that share them must not overlap.
+SPITE_API int spite_gemm_stream(const GemmParams* p, int max_rows_per_group, int k_slices, int cluster, int n_blocks,
+                                int smem_budget, int n_splits, float* scratch, long long scratch_floats, int* tickets,
+                                int n_tickets, void* stream) {
     if (!p || !p->A || !p->W || !p->C) return SPITE_BAD_ARG;
     if (p->M < 0 || p->N <= 0 || p->K <= 0 || p->lda < p->K || p->ldc < p->N || n_blocks < 1 || n_splits < 1) return SPITE_BAD_ARG;
     if (p->group_offsets ? p->n_groups < 1 : p->n_groups != 1) return SPITE_BAD_ARG;
@@ -453,20 +525,21 @@ SPITE_API int spite_gemm_stream(const GemmParams* p, int max_rows_per_group, int
     const int tr = ROWS / k_slices;
     const int cols = p->epilogue == EPI_SWIGLU ? tr / 2 : tr;
     const long long tiles = (long long)((p->N + cols - 1) / cols) * (p->group_offsets ? (p->n_groups < p->M ? p->n_groups : p->M) : 1);
-    if (n_splits > 1) {
+    if (cluster && (k_slices != 1 || n_splits < 2)) return SPITE_BAD_ARG;
+    if (n_splits > 1 && !cluster) {
         if (!scratch || !tickets || tiles > n_tickets || tiles * n_splits * nt * tr > scratch_floats) return SPITE_BAD_ARG;
     }
     cudaStream_t st = (cudaStream_t)stream;
 #define SPITE_STREAM_CASE(E)                                                                                              \
     case E:                                                                                                               \
-        return nt == 8 ? launch_slices<8, E>(k_slices, *p, n_blocks, smem_budget, n_splits, scratch, tickets, st)          \
-                       : launch_slices<16, E>(k_slices, *p, n_blocks, smem_budget, n_splits, scratch, tickets, st);
+        return nt == 8 ? launch_slices<8, E>(k_slices, cluster != 0, *p, n_blocks, smem_budget, n_splits, scratch, tickets, st)          \
+                       : launch_slices<16, E>(k_slices, cluster != 0, *p, n_blocks, smem_budget, n_splits, scratch, tickets, st);
     switch (p->epilogue) {
         SPITE_STREAM_CASE(EPI_STORE)
         SPITE_STREAM_CASE(EPI_STORE_F32)
         SPITE_STREAM_CASE(EPI_ADD_F32)
-        default: return nt == 8 ? launch_slices<8, EPI_SWIGLU>(k_slices, *p, n_blocks, smem_budget, n_splits, scratch, tickets, st)
-                                : launch_slices<16, EPI_SWIGLU>(k_slices, *p, n_blocks, smem_budget, n_splits, scratch, tickets, st);
+        default: return nt == 8 ? launch_slices<8, EPI_SWIGLU>(k_slices, cluster != 0, *p, n_blocks, smem_budget, n_splits, scratch, tickets, st)
+                                : launch_slices<16, EPI_SWIGLU>(k_slices, cluster != 0, *p, n_blocks, smem_budget, n_splits, scratch, tickets, st);
     }
 #undef SPITE_STREAM_CASE
 }

@@ -202,6 +202,12 @@ class CudaKernels(KernelSet):
         self.stream_max_slices = 8             # 1: tiles of 128 rows only
         self.stream_slices_min_rows = 6        # products of fewer rows keep tiles of 128 rows (see stream_cut)
         self.stream_slices_grouped = False     # ... and so do grouped products
+        self.stream_cluster_max_rows = 3       # up to this many rows the k splits of a tile are a thread-block cluster (0: never)
+        # ... if they are no more than this (the hardware takes up to 8).  Measured in the decode step at one / two /
+        # three tokens: no clusters 2.780 / 3.348 / 4.114 ms, clusters of two (the gate/up products) 2.748 / 3.335 /
+        # 4.079, up to four 2.749 / 3.313 / 4.082, up to eight 2.753 / 3.316 / 4.083; clusters of seven (the 40 tiles of
+        # an output projection) are not all resident at once and are refused by the kernel's launcher
+        self.stream_cluster_max_splits = 4
         self.stream_force = None               # (k slices, k splits) for every call, for measurements
         # (shared memory per block, resident blocks) for up to 3 tokens and for more: measured in the decode step at
         # Scout shapes, one token 2.90 ms with (110 KiB, 2 per multiprocessor) against 3.01 with (74 KiB, 3), eight
@@ -399,6 +405,14 @@ class CudaKernels(KernelSet):
         slices, splits = self.stream_force or self._stream_cut(p.M, p.N, p.K, groups, swiglu, blocks, smem, nt, grouped)
         rows = 128 // slices
         tiles = -(-p.N // (rows // 2 if swiglu else rows)) * groups
+        lib = self._lib("gemm_stream")
+        stream = torch.cuda.current_stream().cuda_stream
+        if slices == 1 and 2 <= splits <= self.stream_cluster_max_splits and p.M <= self.stream_cluster_max_rows:
+            # the k splits of a tile as one thread-block cluster: their sums meet in shared memory
+            st = lib.spite_gemm_stream(C.byref(p), max_rows_per_group, 1, 1, blocks, smem, splits, None, C.c_longlong(0),
+                                       None, 0, C.c_void_p(stream))
+            if st != -2:
+                return st
         scratch, n_floats = None, 0
         if splits > 1:
             if tiles > self._tickets_n:
@@ -406,12 +420,11 @@ class CudaKernels(KernelSet):
             n_floats = tiles * splits * nt * rows
             scratch = torch.empty(n_floats, dtype=torch.float32, device=self.device)
         # the k splits' arrival counters: one set per stream, since calls that share a set must not overlap
-        stream = torch.cuda.current_stream().cuda_stream
         tickets = self._tickets.get(stream)
         if tickets is None and splits > 1:
             tickets = self._tickets[stream] = torch.zeros(self._tickets_n, dtype=torch.int32, device=self.device)
-        return self._lib("gemm_stream").spite_gemm_stream(
-            C.byref(p), max_rows_per_group, slices, blocks, smem, splits, C.c_void_p(_ptr(scratch)),
+        return lib.spite_gemm_stream(
+            C.byref(p), max_rows_per_group, slices, 0, blocks, smem, splits, C.c_void_p(_ptr(scratch)),
             C.c_longlong(n_floats), C.c_void_p(_ptr(tickets)), self._tickets_n, C.c_void_p(stream))
 
     def _stream_cut(self, M: int, N: int, K: int, groups: int, swiglu: bool, slots: int, smem: int, nt: int,

@@ -56,7 +56,7 @@ def gemm_calls(libs):
         ("gemm_simt", lambda p: libs["gemm_simt"].spite_gemm_simt(1, C.byref(p), None)),
         ("gemm_skinny", lambda p: libs["gemm_skinny"].spite_gemm_skinny(C.byref(p), max(p.M, 1), 148, None)),
         ("gemm_stream", lambda p: libs["gemm_stream"].spite_gemm_stream(
-            C.byref(p), min(max(p.M, 1), 16), 1, 296, 74 * 1024, 1, ptr(scratch), C.c_longlong(scratch.numel()),
+            C.byref(p), min(max(p.M, 1), 16), 1, 0, 296, 74 * 1024, 1, ptr(scratch), C.c_longlong(scratch.numel()),
             ptr(tickets), tickets.numel(), None)),
         ("gemm_tc", lambda p: libs["gemm_tc"].spite_gemm_tc(C.byref(p), 148, None)),
         ("gemm_tc_pair", lambda p: libs["gemm_tc_pair"].spite_gemm_tc_pair(C.byref(p), 74, None)),
@@ -101,7 +101,7 @@ def test_products_refuse_malformed_calls(libs, which):
     # a null parameter block
     fn = {"gemm_simt": lambda: libs["gemm_simt"].spite_gemm_simt(1, None, None),
           "gemm_skinny": lambda: libs["gemm_skinny"].spite_gemm_skinny(None, 1, 148, None),
-          "gemm_stream": lambda: libs["gemm_stream"].spite_gemm_stream(None, 1, 1, 296, 74 * 1024, 1, None, C.c_longlong(0), None, 0, None),
+          "gemm_stream": lambda: libs["gemm_stream"].spite_gemm_stream(None, 1, 1, 0, 296, 74 * 1024, 1, None, C.c_longlong(0), None, 0, None),
           "gemm_tc": lambda: libs["gemm_tc"].spite_gemm_tc(None, 148, None),
           "gemm_tc_pair": lambda: libs["gemm_tc_pair"].spite_gemm_tc_pair(None, 74, None)}[name]
     assert fn() == BAD_ARG
@@ -127,13 +127,13 @@ def test_tensor_core_products_refuse_sizes_outside_their_domain(libs, which):
 def test_streaming_product_refuses_too_many_rows_and_missing_scratch(libs):
     p, (a, w, c) = gemm_case(M=4, N=64, K=4096)
     lib = libs["gemm_stream"]
-    assert lib.spite_gemm_stream(C.byref(p), 17, 1, 296, 74 * 1024, 1, None, C.c_longlong(0), None, 0, None) == UNSUPPORTED
-    assert lib.spite_gemm_stream(C.byref(p), 4, 1, 296, 74 * 1024, 4, None, C.c_longlong(0), None, 0, None) == BAD_ARG
-    assert lib.spite_gemm_stream(C.byref(p), 4, 1, 0, 74 * 1024, 1, None, C.c_longlong(0), None, 0, None) == BAD_ARG
-    assert lib.spite_gemm_stream(C.byref(p), 4, 3, 296, 74 * 1024, 1, None, C.c_longlong(0), None, 0, None) == BAD_ARG       # k slices: 1, 2, 4, 8
+    assert lib.spite_gemm_stream(C.byref(p), 17, 1, 0, 296, 74 * 1024, 1, None, C.c_longlong(0), None, 0, None) == UNSUPPORTED
+    assert lib.spite_gemm_stream(C.byref(p), 4, 1, 0, 296, 74 * 1024, 4, None, C.c_longlong(0), None, 0, None) == BAD_ARG
+    assert lib.spite_gemm_stream(C.byref(p), 4, 1, 0, 0, 74 * 1024, 1, None, C.c_longlong(0), None, 0, None) == BAD_ARG
+    assert lib.spite_gemm_stream(C.byref(p), 4, 3, 0, 296, 74 * 1024, 1, None, C.c_longlong(0), None, 0, None) == BAD_ARG       # k slices: 1, 2, 4, 8
     assert untouched(c)
     p, (a, w, c) = gemm_case(M=4, N=64, K=320)                                     # 320 is no multiple of 64 x 2
-    assert lib.spite_gemm_stream(C.byref(p), 4, 2, 296, 74 * 1024, 1, None, C.c_longlong(0), None, 0, None) == UNSUPPORTED
+    assert lib.spite_gemm_stream(C.byref(p), 4, 2, 0, 296, 74 * 1024, 1, None, C.c_longlong(0), None, 0, None) == UNSUPPORTED
     assert untouched(c)
     p, (a, w, c) = gemm_case(M=600, N=64, K=128)
     assert libs["gemm_skinny"].spite_gemm_skinny(C.byref(p), 600, 148, None) == UNSUPPORTED and untouched(c)

@@ -98,15 +98,19 @@ def test_linear(ks, M, N, K):
         assert ks.gemm_tc_error() == 0, "a tensor-core block gave up waiting"
 
 
-@pytest.mark.parametrize("slices,splits", [(1, 1), (1, 3), (2, 1), (2, 2), (4, 1), (4, 2), (8, 1), (8, 2)])
+@pytest.mark.parametrize("slices,splits,cluster", [(1, 1, False), (1, 3, False), (2, 1, False), (2, 2, False), (4, 1, False),
+                                                   (4, 2, False), (8, 1, False), (8, 2, False),
+                                                   (1, 2, True), (1, 3, True), (1, 4, True)])
 @pytest.mark.parametrize("M", [1, 7, 13])
-def test_streaming_products_with_k_slices_and_k_splits(slices, splits, M):
+def test_streaming_products_with_k_slices_and_k_splits(slices, splits, cluster, M):
     """The weight-streaming kernel with every way of cutting its work: tiles of 128 / slices rows whose k slices
-    meet in shared memory, and k splits across blocks through the scratch; plain, SwiGLU, added into float32
-    with a row scale, and grouped by expert.  Widths that are no multiple of a tile; the same bits twice."""
+    meet in shared memory, and k splits across blocks, through the scratch in global memory or, as one thread-block
+    cluster a tile, through shared memory; plain, SwiGLU, added into float32 with a row scale, and grouped by
+    expert.  Widths that are no multiple of a tile; the same bits twice."""
     from spite_b200.kernels.cuda import CudaKernels
     ks = CudaKernels(torch.bfloat16, DEV)
     ks.stream_force = (slices, splits)
+    ks.stream_cluster_max_rows = 16 if cluster else 0
     if M > 8 and slices == 8:
         ks.stream_shape = [ks.stream_shape[0]] * 2            # stages of 16 tokens x 8 slices are 32 KiB: the deeper ring
     r = ref_set(torch.bfloat16)
