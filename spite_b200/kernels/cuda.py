@@ -100,7 +100,7 @@ def _check(status, what):
 
 def stream_cut(M: int, N: int, K: int, groups: int, swiglu: bool, slots: int, smem: int, nt: int, *,
                item_cost: float = 2.0, split_item_cost: float = 6.0, split_cost: float = 1.5, slice_cost: float = 1.0,
-               max_slices: int = 8, slices_min_rows: int = 4):
+               max_slices: int = 8, slices_min_rows: int = 4, cluster_max_splits: int = 0, cluster_cost: float = 0.0):
     """(k slices inside a block, k splits across blocks) of the weight-streaming kernel for a product of M rows,
     N output columns (per group) and depth K on `slots` resident blocks of `smem` bytes, `nt` token columns.
 
@@ -111,8 +111,9 @@ def stream_cut(M: int, N: int, K: int, groups: int, swiglu: bool, slots: int, sm
     splits across blocks (partial sums through global memory, a ticket, a second pass over as many partial
     tiles as there are splits).  The cost of a choice is its rounds of items times (stages an item + what an
     item costs besides, in stages of 16 KiB: `item_cost` for any item, `split_item_cost` + `split_cost` a split
-    if its sums cross blocks, `slice_cost` if its slices meet in shared memory); at least four stages stay
-    together.
+    if its sums cross blocks through global memory, `cluster_cost` if the splits, no more than
+    `cluster_max_splits`, can be one thread-block cluster with all clusters resident at once, `slice_cost` if
+    its slices meet in shared memory); at least four stages stay together.
 
     Measured on B200, us, (slices, splits) forced, each product alone.  Eight tokens (444 blocks): qkv 7168 x
     5120: (1, 5) 19.6, (2, 1) 20.9, (4, 1) 17.3, (8, 1) 21.3, (2, 2) 18.9; output projection 5120 x 5120: (1, 7)
@@ -141,7 +142,9 @@ def stream_cut(M: int, N: int, K: int, groups: int, swiglu: bool, slots: int, sm
         for s in range(1, max(1, min(32, stages // 4)) + 1):
             rounds = -(-tiles * s // slots)
             fixed = item_cost + (slice_cost if slices > 1 else 0.0)
-            if s > 1:
+            if s > 1 and slices == 1 and s <= cluster_max_splits and tiles * s <= slots:
+                fixed += cluster_cost                         # the splits as one cluster: their sums meet in shared memory
+            elif s > 1:
                 fixed += split_item_cost + split_cost * s
             cost = rounds * (-(-stages // s) + fixed)
             if best_cost is None or cost < best_cost:
@@ -208,6 +211,10 @@ class CudaKernels(KernelSet):
         # 4.079, up to four 2.749 / 3.313 / 4.082, up to eight 2.753 / 3.316 / 4.083; clusters of seven (the 40 tiles of
         # an output projection) are not all resident at once and are refused by the kernel's launcher
         self.stream_cluster_max_splits = 4
+        # what such an item costs besides its stages (see stream_cut).  9 (qkv in four splits as clusters, the output
+        # and down projections in seven through global memory) against 4, 2, 1 (all three in four): 2.714 against
+        # 2.738, 2.727, 2.726 ms at one token
+        self.stream_cluster_cost = 9.0
         self.stream_force = None               # (k slices, k splits) for every call, for measurements
         # (shared memory per block, resident blocks) for up to 3 tokens and for more: measured in the decode step at
         # Scout shapes, one token 2.90 ms with (110 KiB, 2 per multiprocessor) against 3.01 with (74 KiB, 3), eight
@@ -433,7 +440,9 @@ class CudaKernels(KernelSet):
                           split_item_cost=self.stream_split_item_cost, split_cost=self.stream_split_cost,
                           slice_cost=self.stream_slice_cost,
                           max_slices=self.stream_max_slices if self.stream_slices_grouped or not grouped else 1,
-                          slices_min_rows=self.stream_slices_min_rows)
+                          slices_min_rows=self.stream_slices_min_rows,
+                          cluster_max_splits=self.stream_cluster_max_splits if M <= self.stream_cluster_max_rows else 0,
+                          cluster_cost=self.stream_cluster_cost)
 
     def attention_tc_error(self) -> int:
         """Error code left by a tcgen05 attention block that gave up waiting (0: none); clears it. Synchronises."""

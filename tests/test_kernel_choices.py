@@ -48,6 +48,14 @@ def test_every_cut_is_one_the_kernel_takes(M, N, K, swiglu, groups):
     assert ring >= 2                                                   # a ring of at least two stages fits
 
 
+def test_splits_that_can_be_a_cluster_are_preferred_when_the_caller_offers_clusters():
+    assert cut(1, 7168, 5120, cluster_max_splits=4, cluster_cost=9.0) == (1, 4)      # qkv: 224 blocks, 56 clusters of four
+    assert cut(1, 5120, 5120, cluster_max_splits=4, cluster_cost=9.0) == (1, 7)      # too few blocks in fours
+    assert cut(1, 8192, 5120, swiglu=True, cluster_max_splits=4, cluster_cost=9.0) == (1, 2)
+    # never more blocks than are resident at once: 128 tiles in four splits are 512 blocks for 296 places
+    assert cut(1, 8192, 5120, swiglu=True, cluster_max_splits=4, cluster_cost=0.0) == (1, 2)
+
+
 def test_the_costs_move_the_choice():
     assert cut(8, 5120, 5120, max_slices=1)[0] == 1                    # tiles of 128 rows only: k splits again
     assert cut(8, 5120, 5120, max_slices=1)[1] > 1
