@@ -435,7 +435,7 @@ def run_ours(args):
     engine.check()
 
     line = {
-        "metric": "decode tok/s (Llama-4-Scout-shaped, batch 8, context 8192)",
+        "metric": f"decode tok/s (Llama-4-Scout-shaped, batch {B}, context {ctx})",
         "value": round(value, 2), "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic (random token ids, random weights N(0,0.02))",
