@@ -339,20 +339,43 @@ class ToyRoutedConfig:
                                                 position=PartSpec("toy_harmonic_rotation", {"head_dim": 12, "base": 0.37}),
                                                 window=("full", 0)))
         ffn = PartSpec("toy_top2_with_bypass", {"hidden_size": self.hidden, "num_experts": 3, "expert_size": 24})
-        blocks = (BlockSpec("prenorm_residual", {"mixer_norm": norm, "mixer": attn, "ffn_norm": norm, "ffn": ffn}),) * 2
+        centered = PartSpec("toy_centered_norm", {"size": self.hidden, "eps": 1e-4})
+        blocks = (BlockSpec("prenorm_residual", {"mixer_norm": norm, "mixer": attn, "ffn_norm": centered, "ffn": ffn}),) * 2
         return ModelPlan(self.hidden, self.vocab, blocks, tuple(LayerCall(i, i) for i in range(2)), norm,
                          tie_word_embeddings=True, max_positions=256)
 
 
 def test_a_toy_routed_feed_forward_and_a_toy_position_encoding_are_registered_built_and_stepped():
-    """Two more parts defined here, from the kernel set's operations alone: a feed-forward that sends every
-    token to its two best experts of three (sigmoid weights on the input, as the kernels apply them) beside
-    an ungated linear bypass, and a position encoding with harmonic frequencies base / (i + 1).  The model
-    is graph-safe, so its decode steps replay from CUDA graphs; whole prompts, portions and single tokens
-    agree with a plain computation of the same model."""
+    """Three more parts defined here: a feed-forward that sends every token to its two best experts of three
+    (sigmoid weights on the input, as the kernels apply them) beside an ungated linear bypass, from the kernel
+    set's operations alone; a position encoding with harmonic frequencies base / (i + 1); and a norm that
+    centres a row before it scales it and adds a bias (device operations of its own, which a CUDA graph takes as
+    well).  The model is graph-safe, so its decode steps replay from CUDA graphs; whole prompts, portions and
+    single tokens agree with a plain computation of the same model."""
     from spite_b200.config import config_from_dict, register_architecture
     from spite_b200.engine import Engine, Model
-    from spite_b200.parts import FeedForward, ParamSpec, PositionEncoding, register_feed_forward, register_position
+    from spite_b200.parts import (FeedForward, Norm, ParamSpec, PositionEncoding, register_feed_forward, register_norm,
+                                  register_position)
+
+    @register_norm("toy_centered_norm")
+    class ToyCenteredNorm(Norm):
+        graph_safe = True
+
+        def __init__(self, ctx, size, eps):
+            super().__init__(ctx)
+            self.size, self.eps = size, eps
+
+        def param_specs(self):
+            return {"weight": ParamSpec((self.size,), "ones"), "bias": ParamSpec((self.size,))}
+
+        def bind(self, params):
+            self.weight, self.bias = params["weight"].float().contiguous(), params["bias"].float().contiguous()
+
+        def forward(self, h, out, rows=None):
+            x = h if rows is None else h.index_select(0, rows.long())
+            x = x - x.mean(dim=1, keepdim=True)
+            out.copy_(x * torch.rsqrt((x * x).mean(dim=1, keepdim=True) + self.eps) * self.weight + self.bias)
+            return out
 
     @register_position("toy_harmonic_rotation")
     class ToyHarmonicRotation(PositionEncoding):
@@ -414,7 +437,8 @@ def test_a_toy_routed_feed_forward_and_a_toy_position_encoding_are_registered_bu
             q, k = plain.apply_rotary(q, pos, freq), plain.apply_rotary(k, pos, freq)
             mask = pos[None, :] <= pos[:, None]
             h = h + plain.attention(q, k, v, mask).reshape(T, 48) @ m.wo.float().cpu().T
-            x = plain.rms_norm(h, blk.ffn_norm.weight.cpu(), 1e-5)
+            x = h - h.mean(dim=1, keepdim=True)
+            x = x * torch.rsqrt((x * x).mean(dim=1, keepdim=True) + 1e-4) * blk.ffn_norm.weight.cpu() + blk.ffn_norm.bias.cpu()
             logits = x @ ff.router.cpu().T
             order = torch.sort(logits, dim=-1, descending=True, stable=True)
             y = x @ ff.bypass.float().cpu().T
