@@ -6,6 +6,7 @@ peak.  Also the small driver that `ncu` captures for the summaries under `profil
     python bench_kernels.py --only gemm_decode   # one family (for ncu: -k regex:...)
     python bench_kernels.py --small              # shapes a profiler can replay in seconds
     python bench_kernels.py --only gemm_decode --case "lm_head M=8"   # one case
+    python bench_kernels.py --only gemm_decode,moe_decode --rows 4,6   # the decode families at other token counts
 
 Families: gemm_decode (weight streaming, mma.sync), gemm_prefill (tcgen05/TMA),
 moe_decode, moe_prefill (grouped products), attention_decode, attention_prefill,
