@@ -105,13 +105,13 @@ struct Item {
     int split, kb0, kb1;          // k split and its range of stages (64 S wide each)
 };
 
-// NT: token columns (8 or 16).  S: k slices inside the block.  `n_splits` k splits per tile; `scratch` holds
+// NT: token columns (8, 16 or 32).  S: k slices inside the block.  `n_splits` k splits per tile; `scratch` holds
 // tiles x n_splits x NT x (128 / S) floats, `tickets` one zeroed int per tile (left zeroed).
 // CL (with S = 1): the k splits of a tile are the blocks of one thread-block cluster, the grid has one block per
 // (tile, split), and the splits' sums meet in the shared memory of the cluster's first block instead of in
 // global memory: no scratch, no fence, no ticket, no second pass through L2.
 template <int NT, int EPI, int S, bool CL>
-__global__ void __launch_bounds__(THREADS, 3)
+__global__ void __launch_bounds__(THREADS, NT <= 16 ? 3 : 2)
 gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const GemmParams p, const int n_stages,
                    const int n_splits, float* __restrict__ scratch, int* __restrict__ tickets, const WaitControl waits) {
     constexpr bool DUAL = (EPI == EPI_SWIGLU);
@@ -210,15 +210,21 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const GemmParams p
         const __nv_bfloat16* X = (const __nv_bfloat16*)p.A;
         for (int i = blockIdx.x; i < total && ok; i += gridDim.x) {
             const Item it = item_at(i);
-            // this lane's 16-byte chunks of a slice's token tile: chunk q = lane + 32 j, token q / 8, k chunk q % 8
-            const __nv_bfloat16* src[NT / 4];
-            unsigned off[NT / 4];
+            // this lane's 16-byte chunks of a slice's token tile: chunk q = lane + 32 j, token q / 8, k chunk q % 8.
+            // Up to 16 tokens their places are worked out once an item; with more (one-group products only, rows
+            // in place) they are cheap enough to work out again for every stage, and sixteen pointers would
+            // cost every thread of the block their registers.
+            constexpr int KEPT = NT <= 16 ? NT / 4 : 1;
+            const __nv_bfloat16* src[KEPT];
+            unsigned off[KEPT];
+            if (NT <= 16) {
 #pragma unroll
-            for (int j = 0; j < NT / 4; ++j) {
-                const int q = lane + 32 * j, t = q >> 3, c = q & 7;
-                const int li = it.lo + min(t, it.m - 1);         // rows past the group's tokens repeat its last one; never stored
-                src[j] = X + (size_t)(p.a_rows ? p.a_rows[li] : li) * p.lda + c * 8;
-                off[j] = W_BYTES + t * 128 + ((c ^ (t & 7)) << 4);
+                for (int j = 0; j < KEPT; ++j) {
+                    const int q = lane + 32 * j, t = q >> 3, c = q & 7;
+                    const int li = it.lo + min(t, it.m - 1);     // rows past the group's tokens repeat its last one; never stored
+                    src[j] = X + (size_t)(p.a_rows ? p.a_rows[li] : li) * p.lda + c * 8;
+                    off[j] = W_BYTES + t * 128 + ((c ^ (t & 7)) << 4);
+                }
             }
             const int wy = it.group * w_rows + it.n0;
             for (int kb = it.kb0; kb < it.kb1; ++kb, s = (s + 1 == n_stages ? 0 : s + 1), ph ^= (s == 0)) {
@@ -241,11 +247,24 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const GemmParams p
                         }
                     }
                 }
+                if (NT <= 16) {
 #pragma unroll
-                for (int sl = 0; sl < S; ++sl)
+                    for (int sl = 0; sl < S; ++sl)
 #pragma unroll
-                    for (int j = 0; j < NT / 4; ++j)
-                        cp_async16(dst + sl * X_BYTES + off[j], src[j] + ((size_t)kb * S + sl) * BK);
+                        for (int j = 0; j < KEPT; ++j)
+                            cp_async16(dst + sl * X_BYTES + off[j], src[j] + ((size_t)kb * S + sl) * BK);
+                } else {
+                    const int c = lane & 7;
+#pragma unroll
+                    for (int sl = 0; sl < S; ++sl)
+#pragma unroll 4
+                        for (int j = 0; j < NT / 4; ++j) {
+                            const int t = (lane >> 3) + 4 * j;
+                            const int li = it.lo + min(t, it.m - 1);
+                            cp_async16(dst + sl * X_BYTES + W_BYTES + t * 128 + ((c ^ (t & 7)) << 4),
+                                       X + (size_t)li * p.lda + c * 8 + ((size_t)kb * S + sl) * BK);
+                        }
+                }
                 cp_async_arrive(bar);
             }
         }
@@ -483,21 +502,31 @@ int launch_slices(int k_slices, bool cluster, const GemmParams& p, int n_blocks,
                   int* tickets, cudaStream_t st) {
     if (cluster) {
         if (k_slices != 1) return SPITE_BAD_ARG;
-        return launch<NT, EPI, 1, true>(p, n_blocks, smem_budget, n_splits, scratch, tickets, st);
+        if (NT > 16) return SPITE_UNSUPPORTED;
+        return launch<NT <= 16 ? NT : 8, EPI, 1, true>(p, n_blocks, smem_budget, n_splits, scratch, tickets, st);
+    }
+    if (NT > 16) {                                             // many tokens: tiles of 128 or 64 rows (more slices, more of a
+        switch (k_slices) {                                    // stage would be tokens than weights)
+            case 1: return launch<NT, EPI, 1, false>(p, n_blocks, smem_budget, n_splits, scratch, tickets, st);
+            case 2: return launch<NT, EPI, 2, false>(p, n_blocks, smem_budget, n_splits, scratch, tickets, st);
+            default: return SPITE_UNSUPPORTED;
+        }
     }
     switch (k_slices) {
         case 1: return launch<NT, EPI, 1, false>(p, n_blocks, smem_budget, n_splits, scratch, tickets, st);
         case 2: return launch<NT, EPI, 2, false>(p, n_blocks, smem_budget, n_splits, scratch, tickets, st);
-        case 4: return launch<NT, EPI, 4, false>(p, n_blocks, smem_budget, n_splits, scratch, tickets, st);
+        case 4: return launch<NT <= 16 ? NT : 8, EPI, 4, false>(p, n_blocks, smem_budget, n_splits, scratch, tickets, st);
         case 8: return EPI == EPI_SWIGLU ? SPITE_UNSUPPORTED       // (tiles of 8 gate and 8 up rows: nobody needs them)
-                                         : launch<NT, EPI == EPI_SWIGLU ? EPI_STORE : EPI, 8, false>(p, n_blocks, smem_budget, n_splits, scratch, tickets, st);
+                                         : launch<NT <= 16 ? NT : 8, EPI == EPI_SWIGLU ? EPI_STORE : EPI, 8, false>(p, n_blocks, smem_budget, n_splits, scratch, tickets, st);
         default: return SPITE_BAD_ARG;
     }
 }
 
 }  // namespace
 
-// `max_rows_per_group` <= 16.  `k_slices` (1, 2, 4 or 8; 8 not with SwiGLU): a tile has 128 / k_slices weight rows
+// `max_rows_per_group` <= 16, or <= 32 for a one-group product with its rows in place (with 64 token columns the
+// mma.sync path cannot keep up with the stream: 34 to 63 us for Scout's projections against 28 to 41 on tcgen05).
+// `k_slices` (1, 2, 4 or 8; 8 not with SwiGLU): a tile has 128 / k_slices weight rows
 // (SwiGLU: half of them gate, half up) and K must be a multiple of 64 k_slices.  `n_blocks`: resident blocks
 // (two per multiprocessor fit when `smem_budget`, the bytes of shared memory a block may take, is at most about
 // 110 KiB, three at 74 KiB).  `n_splits`: k splits per tile across blocks (1: no scratch needed).  `cluster`
@@ -515,13 +544,14 @@ SPITE_API int spite_gemm_stream(const GemmParams* p, int max_rows_per_group, int
     if (k_slices != 1 && k_slices != 2 && k_slices != 4 && k_slices != 8) return SPITE_BAD_ARG;
     if (p->K % (BK * k_slices) || p->lda % 8 || (((uintptr_t)p->A | (uintptr_t)p->W) & 15)) return SPITE_UNSUPPORTED;
     if (k_slices == 8 && p->epilogue == EPI_SWIGLU) return SPITE_UNSUPPORTED;
-    if (max_rows_per_group < 1 || max_rows_per_group > 16 || p->n_groups > MAX_GROUPS) return SPITE_UNSUPPORTED;
+    if (max_rows_per_group < 1 || max_rows_per_group > 32 || p->n_groups > MAX_GROUPS) return SPITE_UNSUPPORTED;
+    if (max_rows_per_group > 16 && (p->group_offsets || p->a_rows)) return SPITE_UNSUPPORTED;
     if (p->n_groups > 1 && p->w_group_stride != (long long)(p->epilogue == EPI_SWIGLU ? 2 : 1) * p->N * p->K)
         return SPITE_UNSUPPORTED;                              // groups must be stacked without gaps
     if (p->M == 0) return SPITE_OK;
     const int stages_k = p->K / (BK * k_slices);
     if (n_splits > stages_k) n_splits = stages_k;
-    const int nt = max_rows_per_group <= 8 ? 8 : 16;
+    const int nt = max_rows_per_group <= 8 ? 8 : max_rows_per_group <= 16 ? 16 : 32;
     const int tr = ROWS / k_slices;
     const int cols = p->epilogue == EPI_SWIGLU ? tr / 2 : tr;
     const long long tiles = (long long)((p->N + cols - 1) / cols) * (p->group_offsets ? (p->n_groups < p->M ? p->n_groups : p->M) : 1);
@@ -530,16 +560,17 @@ SPITE_API int spite_gemm_stream(const GemmParams* p, int max_rows_per_group, int
         if (!scratch || !tickets || tiles > n_tickets || tiles * n_splits * nt * tr > scratch_floats) return SPITE_BAD_ARG;
     }
     cudaStream_t st = (cudaStream_t)stream;
+#define SPITE_STREAM_NT(N_, E) launch_slices<N_, E>(k_slices, cluster != 0, *p, n_blocks, smem_budget, n_splits, scratch, tickets, st)
 #define SPITE_STREAM_CASE(E)                                                                                              \
     case E:                                                                                                               \
-        return nt == 8 ? launch_slices<8, E>(k_slices, cluster != 0, *p, n_blocks, smem_budget, n_splits, scratch, tickets, st)          \
-                       : launch_slices<16, E>(k_slices, cluster != 0, *p, n_blocks, smem_budget, n_splits, scratch, tickets, st);
+        return nt == 8 ? SPITE_STREAM_NT(8, E) : nt == 16 ? SPITE_STREAM_NT(16, E) : SPITE_STREAM_NT(32, E);
     switch (p->epilogue) {
         SPITE_STREAM_CASE(EPI_STORE)
         SPITE_STREAM_CASE(EPI_STORE_F32)
         SPITE_STREAM_CASE(EPI_ADD_F32)
-        default: return nt == 8 ? launch_slices<8, EPI_SWIGLU>(k_slices, cluster != 0, *p, n_blocks, smem_budget, n_splits, scratch, tickets, st)
-                                : launch_slices<16, EPI_SWIGLU>(k_slices, cluster != 0, *p, n_blocks, smem_budget, n_splits, scratch, tickets, st);
+        default: return nt == 8 ? SPITE_STREAM_NT(8, EPI_SWIGLU) : nt == 16 ? SPITE_STREAM_NT(16, EPI_SWIGLU)
+                                                                 : SPITE_STREAM_NT(32, EPI_SWIGLU);
     }
 #undef SPITE_STREAM_CASE
+#undef SPITE_STREAM_NT
 }

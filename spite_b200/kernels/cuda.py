@@ -215,6 +215,9 @@ class CudaKernels(KernelSet):
         # and down projections in seven through global memory) against 4, 2, 1 (all three in four): 2.714 against
         # 2.738, 2.727, 2.726 ms at one token
         self.stream_cluster_cost = 9.0
+        # one-group products of up to this many rows stream their weights too (16: never; the kernel takes up to 32).
+        # Decode step at 20 / 24 / 32 requests: 11.98 / 12.63 / 14.07 ms against 12.17 / 13.07 / 14.30 on tcgen05
+        self.stream_max_rows = 32
         self.stream_force = None               # (k slices, k splits) for every call, for measurements
         # (shared memory per block, resident blocks) for up to 3 tokens and for more: measured in the decode step at
         # Scout shapes, one token 2.90 ms with (110 KiB, 2 per multiprocessor) against 3.01 with (74 KiB, 3), eight
@@ -329,7 +332,9 @@ class CudaKernels(KernelSet):
             # tall matrices (output head), where the TMA pipeline of the tcgen05 kernel streams better
             few = p.M <= self.skinny_max_rows and not (not grouped and p.N >= 65536 and p.M > self.skinny_tall_rows)
             tc_ok = self.use_tcgen05 and p.K % 8 == 0 and p.lda % 8 == 0
-            if few and self.use_stream and p.K % 64 == 0 and max_rows_per_group <= 16:
+            # ... and a one-group product of up to 32 rows in place (the dense projections of a larger decode batch)
+            more = (not grouped and not p.a_rows and 16 < p.M <= self.stream_max_rows and p.N < 65536)
+            if (few or more) and self.use_stream and p.K % 64 == 0 and max_rows_per_group <= (32 if more else 16):
                 st = self._gemm_stream(p, int(max_rows_per_group), grouped)
                 if st != -2:
                     self._count("gemm_stream", 1)
@@ -407,8 +412,8 @@ class CudaKernels(KernelSet):
         scratch for the partial sums of the splits."""
         swiglu = p.epilogue == EPI_SWIGLU
         groups = min(p.n_groups, p.M) if grouped else 1
-        smem, blocks = self.stream_shape[p.M > 3]
-        nt = 8 if max_rows_per_group <= 8 else 16
+        smem, blocks = self.stream_shape[0 if p.M <= 3 or p.M > 16 else 1]      # (the tokens of many rows need the larger ring)
+        nt = 8 if max_rows_per_group <= 8 else 16 if max_rows_per_group <= 16 else 32
         slices, splits = self.stream_force or self._stream_cut(p.M, p.N, p.K, groups, swiglu, blocks, smem, nt, grouped)
         rows = 128 // slices
         tiles = -(-p.N // (rows // 2 if swiglu else rows)) * groups
@@ -439,7 +444,8 @@ class CudaKernels(KernelSet):
         return stream_cut(M, N, K, groups, swiglu, slots, smem, nt, item_cost=self.stream_item_cost,
                           split_item_cost=self.stream_split_item_cost, split_cost=self.stream_split_cost,
                           slice_cost=self.stream_slice_cost,
-                          max_slices=self.stream_max_slices if self.stream_slices_grouped or not grouped else 1,
+                          max_slices=(min(2, self.stream_max_slices) if nt > 16 else self.stream_max_slices)
+                          if self.stream_slices_grouped or not grouped else 1,
                           slices_min_rows=self.stream_slices_min_rows,
                           cluster_max_splits=self.stream_cluster_max_splits if M <= self.stream_cluster_max_rows else 0,
                           cluster_cost=self.stream_cluster_cost)

@@ -127,7 +127,7 @@ def test_tensor_core_products_refuse_sizes_outside_their_domain(libs, which):
 def test_streaming_product_refuses_too_many_rows_and_missing_scratch(libs):
     p, (a, w, c) = gemm_case(M=4, N=64, K=4096)
     lib = libs["gemm_stream"]
-    assert lib.spite_gemm_stream(C.byref(p), 17, 1, 0, 296, 74 * 1024, 1, None, C.c_longlong(0), None, 0, None) == UNSUPPORTED
+    assert lib.spite_gemm_stream(C.byref(p), 33, 1, 0, 296, 74 * 1024, 1, None, C.c_longlong(0), None, 0, None) == UNSUPPORTED
     assert lib.spite_gemm_stream(C.byref(p), 4, 1, 0, 296, 74 * 1024, 4, None, C.c_longlong(0), None, 0, None) == BAD_ARG
     assert lib.spite_gemm_stream(C.byref(p), 4, 1, 0, 0, 74 * 1024, 1, None, C.c_longlong(0), None, 0, None) == BAD_ARG
     assert lib.spite_gemm_stream(C.byref(p), 4, 3, 0, 296, 74 * 1024, 1, None, C.c_longlong(0), None, 0, None) == BAD_ARG       # k slices: 1, 2, 4, 8

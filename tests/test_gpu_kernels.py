@@ -174,6 +174,45 @@ def test_streaming_products_with_k_slices_and_k_splits(slices, splits, cluster, 
     assert ks.errors() == {}
 
 
+@pytest.mark.parametrize("slices,splits", [(1, 1), (1, 3), (2, 1), (2, 2)])
+@pytest.mark.parametrize("M", [17, 25, 32])
+def test_streaming_products_of_up_to_32_rows(slices, splits, M):
+    """One-group products of 17 to 32 rows (the dense projections of a larger decode batch) stream their weights
+    too, with 32 token columns a tile: plain, SwiGLU with a row scale, float32 out, added into float32."""
+    from spite_b200.kernels.cuda import CudaKernels
+    ks = CudaKernels(torch.bfloat16, DEV)
+    ks.stream_force = (slices, splits)
+    r = ref_set(torch.bfloat16)
+    N, K, F = 200, 1024, 104
+    x, w = rnd((M, K), torch.bfloat16, 4), rnd((N, K), torch.bfloat16, 5, 0.2)
+    before = ks.launches_by_library["gemm_stream"]
+    outs = []
+    for _ in range(2):
+        out = torch.full((M, N), 7.0, dtype=torch.bfloat16, device=DEV)
+        ks.linear(x.to(DEV), w.to(DEV), out)
+        outs.append(out)
+    assert torch.equal(outs[0], outs[1])
+    ref = torch.empty((M, N), dtype=torch.float64)
+    r.linear(x, w, ref)
+    close(outs[0], ref, TOL[torch.bfloat16], "linear")
+    h, scale = rnd((M, N), torch.float32, 6), rnd((M,), torch.float32, 7)
+    hd = h.to(DEV).clone()
+    ks.linear(x.to(DEV), w.to(DEV), hd, accumulate=True, row_scale=scale.to(DEV))
+    ref_h = h.double().clone()
+    r.linear(x, w, ref_h, accumulate=True, row_scale=scale)
+    close(hd, ref_h, 2e-5, "linear accumulate")
+    logits = torch.empty((M, N), dtype=torch.float32, device=DEV)
+    ks.linear(x.to(DEV), w.to(DEV), logits)
+    close(logits, ref, 1e-5 * K, "linear f32 out")
+    wg = rnd((2 * F, K), torch.bfloat16, 9, 0.3)
+    a = torch.empty((M, F), dtype=torch.bfloat16, device=DEV)
+    ks.linear_swiglu(x.to(DEV), wg.to(DEV), a, row_scale=(scale.abs() + 0.5).to(DEV))
+    a_ref = torch.empty((M, F), dtype=torch.float64)
+    r.linear_swiglu(x, wg, a_ref, row_scale=scale.abs() + 0.5)
+    close(a, a_ref, TOL[torch.bfloat16], "linear_swiglu")
+    assert ks.launches_by_library["gemm_stream"] == before + 5 and ks.errors() == {}
+
+
 @pytest.mark.parametrize("M,F,K", [(3, 24, 48), (70, 100, 96), (8, 40, 512), (40, 17, 96), (64, 72, 64), (129, 256, 192), (700, 136, 320), (1100, 1000, 128),
                                    (5, 100, 4096), (16, 72, 6144), (12, 200, 128)])
 def test_linear_swiglu(ks, M, F, K):
