@@ -1,5 +1,6 @@
 // Matrix product for the few tokens of a decode step, weights streamed through shared memory by TMA:
-//   y[M, N] = epilogue( x[M, K] W[N, K]^T ),  at most 16 rows per group, bfloat16 inputs, float32 sums.
+//   y[M, N] = epilogue( x[M, K] W[N, K]^T ),  at most 16 rows per group (32 for a one-group product),
+//   bfloat16 inputs, float32 sums.
 //
 // With few tokens the product is bound by reading W once from HBM, and what decides the speed is how
 // many bytes a multiprocessor keeps in flight and how quickly the stream starts again after the
@@ -7,7 +8,7 @@
 // box of 128 weight rows x 64 k (128-byte swizzle; for SwiGLU 64 gate and 64 up rows) and the
 // matching 64 k of the group's tokens (cp.async, same swizzle).  Eight consumer warps own 16 of the
 // 128 rows each and multiply with mma.sync.m16n8k16 (weights as the 16-row operand from ldmatrix,
-// tokens as the 8 columns), so no sums cross warps.  Registers stay few, and two blocks (of this
+// tokens as the 8, 16 or 32 columns), so no sums cross warps.  Registers stay few, and two blocks (of this
 // kernel, or the last of this and the first of the next) share a multiprocessor.
 //
 // Work items are (group with tokens, tile of weight rows, k split); blocks are persistent and
@@ -20,7 +21,9 @@
 // when the item ends, in the order of the slices: no traffic, no waiting for another block.  And k
 // splits across blocks: the partial tiles go through a float32 scratch in global memory, and the block
 // that arrives last at the tile's ticket adds them in the order of the splits (a fence, an atomic and
-// a second pass: about 2.7 us an item).  Either way a sum's order does not depend on timing.
+// a second pass: about 2.7 us an item); or, with up to eight splits and one block per (tile, split),
+// the splits of a tile are one thread-block cluster and their sums land in its first block's shared
+// memory between two cluster barriers.  Every way a sum's order does not depend on timing.
 // A one-group product knows its items without the step's earlier kernels: its producer requests the
 // first weights before griddepcontrol.wait.
 // (Dealing every block one equal run of k blocks across tile borders was measured too: faster alone,
