@@ -31,6 +31,9 @@
 // finish early make room for the next kernel's blocks to start and fetch.)
 #include "gemm.cuh"
 #include "tcgen05.cuh"
+#include <map>
+#include <mutex>
+#include <tuple>
 
 namespace {
 using namespace tc;
@@ -492,8 +495,22 @@ int launch(const GemmParams& p, int n_blocks, int smem_budget, int n_splits, flo
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    int fit = 0;
-    if (cudaOccupancyMaxActiveClusters(&fit, k, &cfg) != cudaSuccess) { (void)cudaGetLastError(); return SPITE_UNSUPPORTED; }
+    // how many clusters of this size are resident at once: asked once per (size, shared memory) and device
+    static std::mutex lock;
+    static std::map<std::tuple<int, int, size_t>, int> known;
+    int fit = 0, dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return SPITE_LAUNCH_FAILED;
+    {
+        std::lock_guard<std::mutex> hold(lock);
+        const auto key = std::make_tuple(dev, n_splits, smem);
+        const auto it = known.find(key);
+        if (it != known.end()) {
+            fit = it->second;
+        } else {
+            if (cudaOccupancyMaxActiveClusters(&fit, k, &cfg) != cudaSuccess) { (void)cudaGetLastError(); fit = 0; }
+            known[key] = fit;
+        }
+    }
     if ((long long)fit * n_splits < tiles) return SPITE_UNSUPPORTED;
     cfg.numAttrs = spite_pdl_enabled() ? 2 : 1;
     (void)cudaLaunchKernelEx(&cfg, k, mw, p, n_stages, n_splits, scratch, tickets, s_waits);
