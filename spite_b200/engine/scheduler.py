@@ -19,10 +19,12 @@ generator state is kept, so it samples what it would have sampled).  A request
 that is alone and still cannot get a page ends with reason `cache_full`.  The
 rule is deterministic.
 
-Decoding ahead.  On a GPU, when a step is made of decoded tokens only, all of them greedy, the
-scheduler does not wait for the sampled ids: it leaves the step in flight (argmax on the device, a
+Decoding ahead.  On a GPU, when a step is made of decoded tokens only, the scheduler does not wait
+for the sampled ids: it leaves the step in flight (argmax or the sampling kernel on the device, a
 copy to pinned memory under way) and launches the next step with the ids taken from the device,
-so the GPU never waits for the host between decode steps.  The ids are read one step late.  What
+so the GPU never waits for the host between decode steps.  A request's generator state advances on
+the host by the same rule as on the device, and a repetition penalty finds the one token the host
+has not read yet on the device.  The ids are read one step late.  What
 the late reading changes: a request that ends on an end-of-generation or stop token has one more
 step run for it, whose row is thrown away (its cache is freed as usual; rows of a batch do not
 depend on each other), and a waiting request is admitted one step later than it could have been.
@@ -153,9 +155,13 @@ class Scheduler:
         n = len(r.output) + 1
         return n >= r.params.max_tokens or len(r.prompt) + n >= self.ctx
 
-    def _leave_in_flight(self, requests, logits) -> _InFlight:
+    def _leave_in_flight(self, requests, logits, pending=None) -> _InFlight:
+        """Sample on the device and start the copy of the ids to the host; `pending`: see `Sampler.sample_on_device`."""
         import torch
-        ids = self.sampler.greedy_on_device(logits)
+        ids, states = self.sampler.sample_on_device(
+            logits, [SampleRow(r.params, r.all_tokens(), r.rng_state) for r in requests], pending)
+        for r, st in zip(requests, states):
+            r.rng_state = st
         if not self._pinned:                 # two buffers: one step is read while the next one's copy runs
             n = max(len(requests), self.engine.cache.slots.n_slots)
             self._pinned = [torch.empty(n, dtype=torch.int32) for _ in range(2)]
@@ -204,7 +210,8 @@ class Scheduler:
         self.counters["tokens"] += len(go_on)
         for r in go_on:
             r.n_fed += 1
-        return self._leave_in_flight(go_on, logits)
+        # the token a request got from the step in flight is still on the device: the repetition penalty reads it there
+        return self._leave_in_flight(go_on, logits, (cur.device_tokens, [cur.requests.index(r) for r in go_on]))
 
     # ------------------------------------------------------------------ planning
     def _fit(self, r: Request, n: int, wants: dict) -> int:
@@ -359,10 +366,9 @@ class Scheduler:
             self.counters["tokens"] += len(toks)
             if want:
                 sampled.append(r)
-        if (self.decode_ahead and len(sampled) == len(plan.entries) == len(self.running)
-                and all(is_plain_greedy(r.params) for r in sampled)):
-            # every running request gets a token from this step and none needs the host to sample:
-            # leave the ids on the device and let the next call launch the next step before reading them
+        if self.decode_ahead and len(sampled) == len(plan.entries) == len(self.running):
+            # every running request gets a token from this step, sampled on the device:
+            # leave the ids there and let the next call launch the next step before reading them
             self._in_flight = self._leave_in_flight(sampled, logits)
             return outputs
         tokens, states = self.sampler.sample(

@@ -227,11 +227,22 @@ def test_decoding_ahead_random_scenarios(model, seed):
     budget, slots = rng.choice([3, 16, 64, 2048]), rng.randint(1, 4)
     pages = rng.choice([96, 160, 512])
 
+    # every other scenario samples: a temperature, filters, a repetition penalty over the last few tokens (which
+    # has to find the token that the host has not read yet), one generator state per request; some rows greedy
+    from spite_b200.sampling import SamplingParams
+    def params(i):
+        if seed % 2 == 0 or rng_of[i] < 0.25:
+            return greedy(limits[i], stop_token_ids=stops[i])
+        return SamplingParams(temperature=0.5 + rng_of[i], top_p=0.9, top_k=40 if i % 2 else 0, min_p=0.0,
+                              repetition_penalty=1.0 if i % 3 == 0 else 1.3, repeat_last_n=4 + i, seed=1000 + 17 * i,
+                              max_tokens=limits[i], stop_token_ids=stops[i])
+    rng_of = [rng.random() for _ in range(n_req)]
+
     def run(ahead):
         s = make(model, max_batch_tokens=budget, cache_tokens=pages, max_requests=slots, eos_token_ids=eos,
                  decode_ahead=ahead)
         for i in range(n_req):
-            s.submit(Request(i, prompts[i], greedy(limits[i], stop_token_ids=stops[i])))
+            s.submit(Request(i, prompts[i], params(i)))
         s.run_until_done(max_steps=2000)
         assert not s.active_count() and s._in_flight is None
         s.engine.cache.check_invariants()
@@ -242,6 +253,8 @@ def test_decoding_ahead_random_scenarios(model, seed):
     for i in range(n_req):
         assert b.finished[i].output == a.finished[i].output, (seed, i)
         assert b.finished[i].finish_reason is a.finished[i].finish_reason, (seed, i)
+    if any(limits[i] > 2 for i in range(n_req)):
+        assert b.counters["steps_ahead"] > 0 or pages == 96 or budget == 3, seed
 
 
 def test_two_prompts_in_a_tight_pool_do_not_block_each_other(model):
