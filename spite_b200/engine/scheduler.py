@@ -44,7 +44,7 @@ from collections import deque
 from dataclasses import dataclass, field
 
 from ..kernels.api import KernelTimeout
-from ..sampling.sampler import SampleRow, SamplingParams, is_plain_greedy
+from ..sampling.sampler import SampleRow, SamplingParams, lcg_advance
 from .executor import ContextOverflow, StepEntry
 
 
@@ -338,6 +338,12 @@ class Scheduler:
         except KernelTimeout:
             self._in_flight = None
             for r in list(reversed(self.running)):
+                if r.params.temperature > 0:
+                    # a token that was in flight is lost with its draw: the generator goes back to one draw
+                    # for every token the request has
+                    r.rng_state = r.params.seed & ((1 << 64) - 1)
+                    for _ in r.output:
+                        r.rng_state = lcg_advance(r.rng_state)
                 self._preempt(r)
             raise
 

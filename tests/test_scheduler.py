@@ -361,3 +361,22 @@ def test_a_kernel_that_gave_up_waiting_stops_the_step_and_nothing_is_lost(model)
         done = s.run_until_done()
         for i in (1, 2):
             assert done[i].output == plain_greedy(model, PROMPTS[i], 6) and done[i].preemptions == 1
+    # sampled requests: the draw of a token that was in flight is lost with it, so that what follows is what an
+    # undisturbed run samples
+    from spite_b200.sampling import SamplingParams
+    sampled = lambda i: SamplingParams(temperature=0.9, top_p=0.9, repetition_penalty=1.2, seed=40 + i, max_tokens=7)
+    eng = Engine(m, cache_tokens=512, page_size=16, max_requests=4)
+    calm = Scheduler(eng, Sampler(kernels), max_batch_tokens=64, decode_ahead=True)
+    for i in (1, 2):
+        calm.submit(Request(i, PROMPTS[i], sampled(i)))
+    want = {i: r.output for i, r in calm.run_until_done().items()}
+    eng = Engine(m, cache_tokens=512, page_size=16, max_requests=4)
+    s = Scheduler(eng, Sampler(kernels), max_batch_tokens=64, decode_ahead=True)
+    for i in (1, 2):
+        s.submit(Request(i, PROMPTS[i], sampled(i)))
+    s.step(); s.step(); s.step(); s.step()
+    kernels.pending = {"gemm_stream": 1}
+    with pytest.raises(KernelTimeout):
+        while True:
+            s.step()
+    assert {i: r.output for i, r in s.run_until_done().items()} == want
