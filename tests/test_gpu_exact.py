@@ -131,8 +131,17 @@ def _cuts(requests):
             e.append({"id": "o", "tokens": o[50 + 4 * j:54 + 4 * j], "want": [0, 1, 2, 3]})
         mixed.append({"entries": e, "end": ["m"] if j == 7 else []})
     mixed.append({"entries": [], "end": ["o"]})
+    # portions of 6 to 40 tokens: the sizes of larger decode batches, which the weight-streaming products take with
+    # tiles of fewer rows (k slices) and with 16 or 32 token columns
+    medium, i = [], 0
+    for n in (8, 12, 24, 30, 6, 16, 32, 40):
+        medium.append({"entries": [{"id": "m", "tokens": m[i:i + n], "want": list(range(n))}], "end": []})
+        i += n
+    assert i == len(m)
+    medium[-1]["end"] = ["m"]
     cuts = {"whole": H.steps_whole(requests), "last 8 one by one": H.steps_last_decoded(requests, 8),
-            "portions 64/100/2/2": portions, "mixed beside a second request": mixed}
+            "portions 64/100/2/2": portions, "mixed beside a second request": mixed,
+            "portions of 6 to 40": medium}
     for steps in cuts.values():
         for k, s in enumerate(steps):
             s["step"] = k
